@@ -1,0 +1,151 @@
+// Embedding gather (token table + optional learned position table) and LayerNorm.
+//
+// The residual stream is float32 in every mode: the sum of the two embeddings,
+// every residual add and all norm statistics are 32-bit.
+//   embedding : h[t] = wte[id_t] + wpe[pos_t]      (reference: src/model/paged_decoder.py:306-314)
+//   layernorm : (x-mean)/sqrt(var+eps)*g+b, biased variance, two passes over registers
+//               (reference: src/kernels/triton_residual_layernorm.py:25-40)
+#include "common.cuh"
+
+namespace ps {
+
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
+                             const T* __restrict__ wte, const T* __restrict__ wpe,
+                             float* __restrict__ out, int H, int V, int P, int* __restrict__ status) {
+    int t = blockIdx.x;
+    int id = ids[t];
+    int p = pos ? pos[t] : 0;
+    bool bad = (id < 0 || id >= V) || (wpe && (p < 0 || p >= P));
+    if (bad) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 1);
+        for (int c = threadIdx.x; c < H; c += blockDim.x) out[(size_t)t * H + c] = 0.f;
+        return;
+    }
+    const T* e = wte + (size_t)id * H;
+    const T* q = wpe ? wpe + (size_t)p * H : nullptr;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = to_float(e[c]);
+        if (q) v += to_float(q[c]);
+        out[(size_t)t * H + c] = v;
+    }
+}
+
+// One CTA per row. Row kept in registers when H <= NT*MAXV, else re-read.
+template <typename TOut, int NT>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                                 float eps, TOut* __restrict__ out, int H, int has_mean) {
+    __shared__ float red[NT / 32];
+    __shared__ float bcast;
+    int r = blockIdx.x;
+    int src = rows ? rows[r] : r;
+    const float* xr = x + (size_t)src * H;
+    constexpr int MAXV = 8;
+    float vals[MAXV];
+    float sum = 0.f;
+    bool in_regs = H <= NT * MAXV;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        int c = threadIdx.x + i * NT;
+        vals[i] = (in_regs && c < H) ? xr[c] : 0.f;
+        sum += vals[i];
+    }
+    if (!in_regs) {
+        sum = 0.f;
+        for (int c = threadIdx.x; c < H; c += NT) sum += xr[c];
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float mean = 0.f;
+    if (has_mean) {
+        sum = warp_sum(sum);
+        if (lane == 0) red[warp] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = 0.f;
+            for (int w = 0; w < NT / 32; ++w) s += red[w];
+            bcast = s / (float)H;
+        }
+        __syncthreads();
+        mean = bcast;
+        __syncthreads();
+    }
+    float sq = 0.f;
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            int c = threadIdx.x + i * NT;
+            float d = (c < H) ? vals[i] - mean : 0.f;
+            sq += d * d;
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += NT) {
+            float d = xr[c] - mean;
+            sq += d * d;
+        }
+    }
+    sq = warp_sum(sq);
+    if (lane == 0) red[warp] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int w = 0; w < NT / 32; ++w) s += red[w];
+        bcast = rsqrtf(s / (float)H + eps);
+    }
+    __syncthreads();
+    float rstd = bcast;
+    TOut* o = out + (size_t)r * H;
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            int c = threadIdx.x + i * NT;
+            if (c < H) {
+                float v = (vals[i] - mean) * rstd * gamma[c];
+                if (beta) v += beta[c];
+                o[c] = from_float<TOut>(v);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += NT) {
+            float v = (xr[c] - mean) * rstd * gamma[c];
+            if (beta) v += beta[c];
+            o[c] = from_float<TOut>(v);
+        }
+    }
+}
+
+}  // namespace ps
+
+PS_EXPORT int ps_embed(const int* ids, const int* pos, const void* wte, const void* wpe, float* out,
+                       int T, int H, int V, int P, int dtype, int* status, void* stream) {
+    if (T <= 0) return PS_OK;
+    if (H <= 0 || V <= 0) return PS_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    int nt = H >= 256 ? 256 : 128;
+    if (dtype == PS_F32)
+        ps::embed_kernel<float><<<T, nt, 0, s>>>(ids, pos, (const float*)wte, (const float*)wpe, out, H, V, P, status);
+    else if (dtype == PS_BF16)
+        ps::embed_kernel<__nv_bfloat16><<<T, nt, 0, s>>>(ids, pos, (const __nv_bfloat16*)wte,
+                                                         (const __nv_bfloat16*)wpe, out, H, V, P, status);
+    else
+        return PS_ERR_UNSUPPORTED;
+    return ps::launch_status();
+}
+
+// out[r] = norm(x[rows ? rows[r] : r]); has_mean = 0 gives the RMS form; beta may be null.
+PS_EXPORT int ps_layernorm(const float* x, const int* rows, int n_rows, int H, const float* gamma,
+                           const float* beta, float eps, int has_mean, void* out, int out_dtype,
+                           void* stream) {
+    if (n_rows <= 0) return PS_OK;
+    if (H <= 0) return PS_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    constexpr int NT = 256;
+    if (out_dtype == PS_F32)
+        ps::layernorm_kernel<float, NT><<<n_rows, NT, 0, s>>>(x, rows, gamma, beta, eps, (float*)out, H, has_mean);
+    else if (out_dtype == PS_BF16)
+        ps::layernorm_kernel<__nv_bfloat16, NT><<<n_rows, NT, 0, s>>>(x, rows, gamma, beta, eps,
+                                                                      (__nv_bfloat16*)out, H, has_mean);
+    else
+        return PS_ERR_UNSUPPORTED;
+    return ps::launch_status();
+}

@@ -1,0 +1,74 @@
+// Sampling over float32 logits: greedy argmax and temperature sampling by the Gumbel-max rule.
+//
+// The reference samples greedily only (argmax on device then a host read:
+// src/scheduler/orca_scheduler.py:250). Temperature sampling here draws token
+//   argmax_i ( logit_i / T + g_i ),  g_i = -log(-log(u_i)),
+// with u_i from a counter-based generator keyed by (seed, position, i): the draw does not
+// depend on what else is in the batch or on the order in which rows are processed.
+//   key = mix(mix(seed) ^ position);  r = mix(key + i);  u = ((r >> 41) + 0.5) / 2^23
+// where mix is the splitmix64 finaliser. Ties go to the lowest index.
+#include "common.cuh"
+
+namespace ps {
+
+__host__ __device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__device__ __forceinline__ float gumbel(unsigned long long key, int i) {
+    unsigned long long r = mix64(key + (unsigned long long)i);
+    float u = ((float)(r >> 41) + 0.5f) * (1.0f / 8388608.0f);
+    return -logf(-logf(u));
+}
+
+template <int NT>
+__global__ void sample_kernel(const float* __restrict__ logits, int ld, int V,
+                              const float* __restrict__ temperature,
+                              const unsigned long long* __restrict__ seed, const int* __restrict__ position,
+                              int* __restrict__ out) {
+    __shared__ float best_v[NT / 32];
+    __shared__ int best_i[NT / 32];
+    int r = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    float temp = temperature ? temperature[r] : 0.f;
+    unsigned long long key = 0;
+    float inv_t = 1.f;
+    if (temp > 0.f) {
+        key = mix64(mix64(seed[r]) ^ (unsigned long long)(long long)position[r]);
+        inv_t = 1.0f / temp;
+    }
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += NT) {
+        float v = row[i];
+        if (temp > 0.f) v = v * inv_t + gumbel(key, i);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < NT / 32; ++w)
+            if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+        out[r] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+}
+
+}  // namespace ps
+
+PS_EXPORT int ps_sample(const float* logits, int ld, int R, int V, const float* temperature,
+                        const unsigned long long* seed, const int* position, int* out, void* stream) {
+    if (R <= 0) return PS_OK;
+    if (V <= 0 || ld < V) return PS_ERR_BAD_ARGUMENT;
+    ps::sample_kernel<256><<<R, 256, 0, (cudaStream_t)stream>>>(logits, ld, V, temperature, seed, position, out);
+    return ps::launch_status();
+}

@@ -1,0 +1,208 @@
+"""Python wrappers of the CUDA entry points.
+
+Every wrapper checks device, dtype, contiguity and sizes on the host, passes raw
+pointers and the current CUDA stream to the ``extern "C"`` function and raises
+:class:`KernelError` on a non-zero status.  There is no CPU fallback: a tensor
+that is not on a CUDA device, or a library that cannot be built or loaded, is
+an error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from pagedserve_b200.kernels import build as _build
+
+PS_F32, PS_BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: PS_F32, torch.bfloat16: PS_BF16}
+_ACT_CODE = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_STATUS = {1: "bad argument", 2: "unsupported size or dtype", 3: "kernel launch failed"}
+
+_c_void_p = ctypes.c_void_p
+_c_int = ctypes.c_int
+_c_float = ctypes.c_float
+_c_ll = ctypes.c_longlong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(tensor: Optional[torch.Tensor]):
+    return _c_void_p(tensor.data_ptr()) if tensor is not None else _c_void_p(0)
+
+
+def _stream():
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require(tensor: torch.Tensor, name: str, dtype=None):
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (there is no CPU path)")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+
+
+def _check(status: int, what: str):
+    if status != 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype not in _DTYPE_CODE:
+        raise KernelError(f"unsupported dtype {dtype}")
+    return _DTYPE_CODE[dtype]
+
+
+class Ops:
+    """The kernel set for one compute dtype (``torch.float32`` or ``torch.bfloat16``)."""
+
+    def __init__(self, dtype: torch.dtype):
+        if dtype not in _DTYPE_CODE:
+            raise KernelError(f"unsupported compute dtype {dtype}")
+        self.dtype = dtype
+        self.code = _DTYPE_CODE[dtype]
+        self.core = _build.load("core")
+        self.launches = 0            # count of kernel launches issued through this object
+
+    # ------------------------------------------------------------------ embedding
+    def embed(self, ids, positions, wte, wpe, out, status=None):
+        """out[t] = wte[ids[t]] (+ wpe[positions[t]]) as float32 [T, H]."""
+        T, H = out.shape
+        _require(out, "out", torch.float32)
+        _require(ids, "ids", torch.int32)
+        _require(wte, "wte", self.dtype)
+        if wpe is not None:
+            _require(wpe, "wpe", self.dtype)
+            _require(positions, "positions", torch.int32)
+            if wpe.shape[1] != H:
+                raise KernelError("wpe width does not match the hidden size")
+        if wte.shape[1] != H or ids.numel() != T:
+            raise KernelError("embed: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_embed(_ptr(ids), _ptr(positions if wpe is not None else None), _ptr(wte), _ptr(wpe),
+                                  _ptr(out), _c_int(T), _c_int(H), _c_int(wte.shape[0]),
+                                  _c_int(wpe.shape[0] if wpe is not None else 0), _c_int(self.code),
+                                  _ptr(status), _stream()), "embed")
+        return out
+
+    # ------------------------------------------------------------------ norm
+    def layernorm(self, x, gamma, beta, eps, out, rows=None, has_mean=True):
+        """out[r] = norm(x[rows[r]] or x[r]); x float32 [*, H]; out compute dtype or float32."""
+        _require(x, "x", torch.float32)
+        _require(gamma, "gamma", torch.float32)
+        H = x.shape[-1]
+        n_rows = out.shape[0]
+        if rows is not None:
+            _require(rows, "rows", torch.int32)
+            if rows.numel() != n_rows:
+                raise KernelError("layernorm: rows and out disagree")
+        elif x.shape[0] != n_rows:
+            raise KernelError("layernorm: x and out disagree")
+        if out.shape[-1] != H or gamma.numel() != H or (beta is not None and beta.numel() != H):
+            raise KernelError("layernorm: widths disagree")
+        if not x.is_contiguous() or not out.is_contiguous():
+            raise KernelError("layernorm: tensors must be contiguous")
+        self.launches += 1
+        _check(self.core.ps_layernorm(_ptr(x), _ptr(rows), _c_int(n_rows), _c_int(H), _ptr(gamma), _ptr(beta),
+                                      _c_float(eps), _c_int(1 if has_mean else 0), _ptr(out),
+                                      _c_int(dtype_code(out.dtype)), _stream()), "layernorm")
+        return out
+
+    # ------------------------------------------------------------------ matrix product
+    def linear_simt(self, a, w, bias, out, act=None, accumulate=False):
+        """out = act(a @ w.T + bias) on CUDA cores (float32 accumulation, fixed K order)."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError(f"linear: shapes do not match: a {tuple(a.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+        _require(a, "a")
+        _require(w, "w", a.dtype)
+        _require(out, "out")
+        if bias is not None:
+            _require(bias, "bias", torch.float32)
+            if bias.numel() != N:
+                raise KernelError("linear: bias length")
+        if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("linear: innermost stride must be 1")
+        if accumulate and out.dtype != torch.float32:
+            raise KernelError("linear: accumulate needs a float32 output")
+        self.launches += 1
+        _check(self.core.ps_gemm_simt(_ptr(a), _c_int(a.stride(0)), _ptr(w), _c_int(w.stride(0)), _ptr(bias),
+                                      _ptr(out), _c_int(out.stride(0)), _c_int(M), _c_int(N), _c_int(K),
+                                      _c_int(dtype_code(a.dtype)), _c_int(dtype_code(out.dtype)),
+                                      _c_int(_ACT_CODE[act]), _c_int(1 if accumulate else 0), _stream()),
+               "gemm_simt")
+        return out
+
+    def linear(self, a, w, bias, out, act=None, accumulate=False):
+        """The matrix product of the model: float32 runs on FFMA, bfloat16 on tensor cores."""
+        if self.dtype == torch.float32:
+            return self.linear_simt(a, w, bias, out, act, accumulate)
+        from pagedserve_b200.kernels import tensorcore
+
+        return tensorcore.linear(self, a, w, bias, out, act, accumulate)
+
+    # ------------------------------------------------------------------ cache + attention
+    def kv_append(self, k_src, v_src, token_item, positions, block_table, k_pool, v_pool, page_stride,
+                  n_kv_heads, head_dim, page_size):
+        """Copy this step's K/V rows ([T, n_kv_heads*head_dim] views) into their pages."""
+        T = k_src.shape[0]
+        _require(k_src, "k", self.dtype)
+        _require(v_src, "v", self.dtype)
+        _require(k_pool, "k_pool", self.dtype)
+        if k_src.stride(1) != 1 or v_src.stride(1) != 1 or k_src.stride(0) != v_src.stride(0):
+            raise KernelError("kv_append: k and v must be row views with equal row stride")
+        self.launches += 1
+        _check(self.core.ps_kv_append(_ptr(k_src), _ptr(v_src), _c_int(k_src.stride(0)), _ptr(token_item),
+                                      _ptr(positions), _ptr(block_table), _c_int(block_table.stride(0)),
+                                      _ptr(k_pool), _ptr(v_pool), _c_ll(page_stride), _c_int(T),
+                                      _c_int(n_kv_heads), _c_int(head_dim), _c_int(page_size),
+                                      _c_int(self.code), _stream()), "kv_append")
+
+    def paged_attention_simt(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
+                             n_heads, n_kv_heads, head_dim, page_size, window, scale):
+        """out[t, h] = softmax(q[t,h] . K[<=pos]) V over the request's pages; CUDA cores."""
+        T = q.shape[0]
+        _require(q, "q", self.dtype)
+        _require(out, "out", self.dtype)
+        if q.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("attention: innermost stride must be 1")
+        self.launches += 1
+        _check(self.core.ps_paged_attention_simt(
+            _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(k_pool), _ptr(v_pool),
+            _c_ll(page_stride), _ptr(token_item), _ptr(positions), _ptr(block_table),
+            _c_int(block_table.stride(0)), _c_int(T), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+            _c_int(page_size), _c_int(window or 0), _c_float(scale), _c_int(self.code), _stream()),
+            "paged_attention_simt")
+        return out
+
+    def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):
+        """Write the step's keys and values into the pages, then attend from the pages."""
+        self.kv_append(k, v, ctx.token_item, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
+                       layer.page_stride, n_kv_heads, head_dim, layer.page_size)
+        if self.dtype == torch.float32:
+            return self.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride,
+                                             ctx.token_item, ctx.positions, layer.block_table, n_heads,
+                                             n_kv_heads, head_dim, layer.page_size, window, scale)
+        from pagedserve_b200.kernels import tensorcore
+
+        return tensorcore.attention(self, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale)
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits, temperature, seed, position, out):
+        """out[r] = argmax (temperature 0) or a Gumbel-max draw; logits float32 [R, V]."""
+        R, V = logits.shape
+        _require(logits, "logits", torch.float32)
+        _require(out, "out", torch.int32)
+        if temperature is not None:
+            _require(temperature, "temperature", torch.float32)
+            _require(seed, "seed", torch.int64)
+            _require(position, "position", torch.int32)
+        self.launches += 1
+        _check(self.core.ps_sample(_ptr(logits), _c_int(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
+                                   _ptr(seed), _ptr(position), _ptr(out), _stream()), "sample")
+        return out

@@ -1,0 +1,20 @@
+"""The bfloat16 paths of the matrix product and of attention.
+
+``linear``    out = act(a @ w.T + bias) with bfloat16 operands and float32 accumulation.
+``attention`` causal attention over the paged cache for bfloat16 queries.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def linear(ops, a, w, bias, out, act=None, accumulate=False):
+    # first bfloat16 stage: exact float32 accumulation on CUDA cores
+    return ops.linear_simt(a, w, bias, out, act, accumulate)
+
+
+def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):
+    return ops.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.token_item,
+                                    ctx.positions, layer.block_table, n_heads, n_kv_heads, head_dim,
+                                    layer.page_size, window, scale)

@@ -1,0 +1,21 @@
+"""Arrangements of norms, mixer and feed-forward inside a layer."""
+
+from __future__ import annotations
+
+from pagedserve_b200.parts.base import Block, register_part
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Block):
+    """h += mixer(norm(h)); h += feed_forward(norm(h))
+    (reference: src/model/paged_decoder.py:181-189, 210-228).  The residual stream ``h``
+    is float32 and is updated in place; the adds happen in the epilogues of the
+    mixer's and the feed-forward's last matrix products."""
+
+    required_norms = ("pre_mixer", "pre_feed_forward")
+
+    def forward(self, hidden, ctx, layer):
+        normed = self.norms["pre_mixer"].forward(hidden)
+        self.mixer.forward(normed, hidden, ctx, layer)
+        normed = self.norms["pre_feed_forward"].forward(hidden, out=normed)
+        self.feed_forward.forward(normed, hidden, ctx)

@@ -1,0 +1,39 @@
+"""Norm parts."""
+
+from __future__ import annotations
+
+import torch
+
+from pagedserve_b200.parts.base import Norm, register_part
+from pagedserve_b200.weights.loader import ParamSpec
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * weight + bias over the last axis, in float32.
+
+    reference: nn.LayerNorm at src/model/paged_decoder.py:170-177, 291-294 and the
+    fused kernel src/kernels/triton_residual_layernorm.py:25-40.
+    params: width, eps, name, has_mean (False gives the RMS form), has_bias, init_std.
+    """
+
+    def param_specs(self):
+        p = self.params
+        specs = [(ParamSpec(self._n(p["name"] + ".weight"), (p["width"],), "vector"),
+                  ("ones_plus_normal", p.get("init_std", 0.0)))]
+        if p.get("has_bias", True):
+            specs.append((ParamSpec(self._n(p["name"] + ".bias"), (p["width"],), "vector"),
+                          ("normal", p.get("init_std", 0.0))))
+        return specs
+
+    def bind(self, tensors):
+        p = self.params
+        self.weight = tensors[self._n(p["name"] + ".weight")]
+        self.bias = tensors[self._n(p["name"] + ".bias")] if p.get("has_bias", True) else None
+
+    def forward(self, x, out=None, rows=None, out_dtype=None):
+        n_rows = rows.numel() if rows is not None else x.shape[0]
+        if out is None:
+            out = torch.empty((n_rows, x.shape[1]), dtype=out_dtype or self.env.dtype, device=x.device)
+        return self.env.ops.layernorm(x, self.weight, self.bias, float(self.params["eps"]), out, rows=rows,
+                                      has_mean=self.params.get("has_mean", True))
