@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-from pagedserve_b200.kernels import build as _build
+from pagedserve_b200.kernels.build import load as _load_library
 
 PS_F32, PS_BF16 = 0, 1
 _DTYPE_CODE = {torch.float32: PS_F32, torch.bfloat16: PS_BF16}
@@ -65,7 +65,7 @@ class Ops:
             raise KernelError(f"unsupported compute dtype {dtype}")
         self.dtype = dtype
         self.code = _DTYPE_CODE[dtype]
-        self.core = _build.load("core")
+        self.core = _load_library("core")
         self.launches = 0            # count of kernel launches issued through this object
 
     # ------------------------------------------------------------------ embedding
