@@ -1,0 +1,90 @@
+"""Compare the plain implementation once with the reference's own model code on the CPU.
+
+Run from the repository root, with the reference checkout on ``sys.path``:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+For each tiny configuration it writes a model folder with the package's random-weights
+mode, loads the tensors into the reference's ``PagedDecoderLM`` the way its adapter does
+(Conv1D ``[in, out]`` transposed into ``nn.Linear``; reference: src/model/gpt2.py:14-17,
+48-78), runs the reference's dense ``prefill`` (src/model/paged_decoder.py:316-331) and the
+plain implementation (tests/plain_gpt2.py) on the same token ids in float32, checks that they
+agree, and stores the reference's logits under ``tests/golden/`` as
+``<name>_tokens.json`` and ``<name>_logits.f32`` (little-endian float32 ``[T, V]``).
+
+``tests/test_plain.py`` then checks the plain implementation against these files on every
+run, without needing the reference.
+"""
+
+import json
+import os
+import sys
+import tempfile
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.normpath(os.path.join(HERE, "..", ".."))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import plain_gpt2  # noqa: E402
+from helpers import TINY, random_tokens  # noqa: E402
+
+
+def reference_logits(reference_root, config, weights, token_ids):
+    sys.path.insert(0, reference_root)
+    from src.model.paged_decoder import PagedDecoderLM, TransformerConfig
+
+    hidden, heads, head_dim, inner = plain_gpt2.sizes(config)
+    activation = {"gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu": "gelu"}[
+        config["activation_function"]]
+    model = PagedDecoderLM(TransformerConfig(
+        vocab_size=config["vocab_size"], hidden_size=hidden, num_layers=config["n_layer"], num_heads=heads,
+        head_dim=head_dim, mlp_hidden_size=inner, max_sequence_length=config["n_positions"],
+        activation_function=activation, layer_norm_epsilon=config["layer_norm_epsilon"],
+        tie_word_embeddings=True, lm_head_bias=False)).eval()
+    with torch.no_grad():
+        model.embedding_table.weight.copy_(weights["wte.weight"])
+        model.position_embeddings.weight.copy_(weights["wpe.weight"])
+        for index, layer in enumerate(model.layers):
+            prefix = f"h.{index}."
+            layer.input_layernorm.weight.copy_(weights[prefix + "ln_1.weight"])
+            layer.input_layernorm.bias.copy_(weights[prefix + "ln_1.bias"])
+            layer.post_attention_layernorm.weight.copy_(weights[prefix + "ln_2.weight"])
+            layer.post_attention_layernorm.bias.copy_(weights[prefix + "ln_2.bias"])
+            for target, name in ((layer.self_attn.qkv_linear, "attn.c_attn"),
+                                 (layer.self_attn.output_linear, "attn.c_proj"),
+                                 (layer.mlp_up_proj, "mlp.c_fc"), (layer.mlp_down_proj, "mlp.c_proj")):
+                target.weight.copy_(weights[prefix + name + ".weight"].transpose(0, 1))
+                target.bias.copy_(weights[prefix + name + ".bias"])
+        model.final_layernorm.weight.copy_(weights["ln_f.weight"])
+        model.final_layernorm.bias.copy_(weights["ln_f.bias"])
+        logits, _ = model.prefill(torch.tensor([token_ids], dtype=torch.long))
+    return logits[0].numpy()
+
+
+def main():
+    reference_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    from pagedserve_b200.config.gpt2 import GPT2Config
+    from pagedserve_b200.weights.random_init import write_random_model
+
+    for which, (values, seed, _) in TINY.items():
+        with tempfile.TemporaryDirectory() as folder:
+            write_random_model(folder, GPT2Config(**values), seed)
+            config, weights = plain_gpt2.read_folder(folder, dtype=torch.float32)
+        tokens = random_tokens(values["vocab_size"], 11, seed=40 + seed)
+        theirs = reference_logits(reference_root, config, weights, tokens)
+        ours = plain_gpt2.forward_logits(config, weights, tokens).numpy()
+        error = float(np.abs(theirs - ours).max())
+        scale = float(np.abs(theirs).max())
+        print(f"tiny {which}: max |reference - plain| = {error:.3e} (largest logit {scale:.3e})")
+        assert error <= 2e-5 * max(scale, 1.0), "the plain implementation disagrees with the reference"
+        with open(os.path.join(HERE, f"tiny_{which}_tokens.json"), "w") as handle:
+            json.dump({"config": values, "seed": seed, "tokens": tokens}, handle)
+        theirs.astype("<f4").tofile(os.path.join(HERE, f"tiny_{which}_logits.f32"))
+
+
+if __name__ == "__main__":
+    main()

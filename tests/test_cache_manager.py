@@ -1,0 +1,155 @@
+"""Cache manager: no page lost, held twice or freed twice, under random orders of requests."""
+
+import random
+
+import numpy as np
+import pytest
+
+from pagedserve_b200.cache import CacheError, CacheFull, CacheManager, KVNeed, PageAllocator, StateNeed
+
+
+def manager(pages=16, page=4, window=None, slots=4, max_len=64, mixed=False):
+    needs = [KVNeed(2, 16, None), KVNeed(2, 16, window)] if mixed else [KVNeed(2, 16, window)] * 2
+    return CacheManager(needs, [None, None], page, pages, slots, max_len)
+
+
+def test_allocator_lifo_and_double_free():
+    pool = PageAllocator(4)
+    assert [pool.allocate() for _ in range(4)] == [3, 2, 1, 0]      # highest id first
+    with pytest.raises(CacheFull, match="KV cache full"):
+        pool.allocate()
+    pool.release(2)
+    assert pool.allocate() == 2                                       # the page just freed comes back first
+    pool.release(1)
+    with pytest.raises(CacheError, match="freed twice"):
+        pool.release(1)
+    with pytest.raises(CacheError):
+        pool.release(9)
+    assert pool.peak_used == 4
+
+
+def test_extend_commit_free_cycle():
+    cache = manager()
+    assert cache.admit("a") == 0
+    cache.extend("a", 5)
+    assert cache.groups[0].tables["a"] == [15, 14]
+    with pytest.raises(CacheError, match="not committed"):
+        cache.extend("a", 1)
+    assert cache.commit("a") == 5
+    cache.extend("a", 3)                       # positions 5..7 fit in the second page
+    assert cache.groups[0].tables["a"] == [15, 14]
+    cache.commit("a")
+    cache.extend("a", 1)                       # position 8 opens a third page
+    assert cache.groups[0].tables["a"] == [15, 14, 13]
+    with pytest.raises(CacheError, match="uncommitted"):
+        cache.free("a")
+    cache.commit("a")
+    row = np.zeros(16, dtype=np.int32)
+    cache.table_row(0, "a", row)
+    assert row.tolist() == [15, 14, 13] + [-1] * 13
+    cache.free("a")
+    cache.check_invariants()
+    assert cache.free_pages() == 16 and cache.free_slots == 4
+    with pytest.raises(CacheError, match="unknown request"):
+        cache.free("a")
+    with pytest.raises(CacheError, match="nothing to commit"):
+        cache.admit("b")
+        cache.commit("b")
+
+
+def test_extend_is_all_or_nothing_and_rollback():
+    cache = manager(pages=4, page=4)
+    cache.admit("a"); cache.extend("a", 9); cache.commit("a")      # 3 pages
+    cache.admit("b")
+    with pytest.raises(CacheFull):
+        cache.extend("b", 6)                                         # needs 2, only 1 left
+    assert cache.free_pages() == 1 and cache.groups[0].tables["b"] == []
+    cache.check_invariants()
+    cache.extend("b", 4)
+    cache.rollback("b")                                              # the step failed
+    assert cache.free_pages() == 1 and cache.length("b") == 0
+    cache.check_invariants()
+    with pytest.raises(CacheError, match="maximum length"):
+        cache.extend("b", 65)
+
+
+def test_slots_run_out_and_are_reused():
+    cache = manager(slots=2)
+    cache.admit("a"); cache.admit("b")
+    with pytest.raises(CacheFull, match="slot"):
+        cache.admit("c")
+    with pytest.raises(CacheError, match="already live"):
+        cache.admit("a")
+    cache.free("a")
+    assert cache.admit("c") == 0
+
+
+def test_window_group_gives_pages_back_while_full_group_keeps_them():
+    cache = manager(pages=8, page=4, window=6, mixed=True)
+    full, windowed = cache.groups
+    assert full.need.window is None and windowed.need.window == 6
+    cache.admit("a")
+    for _ in range(5):
+        cache.extend("a", 4)
+        cache.commit("a")
+    # 20 tokens: the next token (position 20) needs keys 15..20 -> pages 0..2 (positions < 12) passed
+    assert windowed.tables["a"] == [-1, -1, -1, 7, 6]      # pages 7 and 6 were passed, freed and handed out again
+    assert full.tables["a"] == [7, 6, 5, 4, 3]
+    assert windowed.allocator.free_pages == 6 and full.allocator.free_pages == 3
+    cache.check_invariants()
+    cache.extend("a", 4); cache.commit("a")
+    assert windowed.tables["a"][5] == 5           # a page the window had passed is handed out again
+    cache.free("a")
+    cache.check_invariants()
+    assert windowed.allocator.free_pages == 8 and full.allocator.free_pages == 8
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("window", [None, 7])
+def test_random_orders_keep_every_page_accounted_for(seed, window):
+    rng = random.Random(seed)
+    cache = manager(pages=24, page=4, window=window, slots=5, max_len=48, mixed=window is not None)
+    live = {}
+    counter = 0
+    for _ in range(600):
+        action = rng.random()
+        if action < 0.25 and cache.free_slots:
+            name = f"r{counter}"; counter += 1
+            cache.admit(name); live[name] = 0
+        elif action < 0.8 and live:
+            name = rng.choice(list(live))
+            count = rng.randint(1, 9)
+            if live[name] + count > 48:
+                continue
+            try:
+                cache.extend(name, count)
+            except CacheFull:
+                cache.check_invariants()
+                continue
+            if rng.random() < 0.1:
+                cache.rollback(name)
+            else:
+                live[name] = cache.commit(name)
+                assert live[name] == cache.length(name)
+        elif live:
+            name = rng.choice(list(live))
+            cache.free(name); del live[name]
+        cache.check_invariants()
+        for group in cache.groups:
+            for name, length in live.items():
+                table = group.tables[name]
+                first = group.first_needed_position(length) // 4
+                needed = -(-length // 4)
+                assert all(page >= 0 for page in table[first:needed]), "a page still in use was given back"
+    for name in list(live):
+        cache.free(name)
+    cache.check_invariants()
+    assert all(g.allocator.free_pages == g.num_pages for g in cache.groups)
+
+
+def test_state_slots_are_declared_per_layer():
+    cache = CacheManager([None, KVNeed(1, 16)], [StateNeed((3, 4)), None], 8, 4, 2, 32)
+    assert cache.state == {}                        # no device: bookkeeping only
+    assert cache.state_needs[0].shape == (3, 4) and cache.group_of_layer == {1: 0}
+    with pytest.raises(CacheError):
+        CacheManager([KVNeed(1, 16)], [None], 12, 4, 2, 32)

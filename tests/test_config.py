@@ -1,0 +1,81 @@
+"""Configuration and the architecture registry."""
+
+import json
+import os
+
+import pytest
+
+from pagedserve_b200.config import (
+    ConfigError,
+    EngineConfig,
+    GPT2Config,
+    architecture_names,
+    load_model_config,
+    resolve_architecture,
+)
+from pagedserve_b200.config.gpt2 import named_config
+
+
+def write_config(tmp_path, values):
+    (tmp_path / "config.json").write_text(json.dumps(values))
+    return str(tmp_path)
+
+
+def test_reads_architecture_keys(tmp_path):
+    values = {"architectures": ["GPT2LMHeadModel"], "n_layer": 3, "n_embd": 96, "n_head": 2, "n_inner": 320,
+              "n_positions": 256, "vocab_size": 1000, "layer_norm_epsilon": 1e-6, "activation_function": "gelu",
+              "resid_pdrop": 0.1, "bos_token_id": 1}
+    config = load_model_config(write_config(tmp_path, values))
+    assert isinstance(config, GPT2Config)
+    assert (config.n_layer, config.n_embd, config.n_head, config.head_dim) == (3, 96, 2, 48)
+    assert config.inner_dim == 320 and config.activation == "gelu_erf"
+    assert config.layer_norm_epsilon == 1e-6 and config.max_model_len == 256
+
+
+def test_defaults_and_null_inner():
+    config = GPT2Config.from_dict({"n_embd": 128, "n_head": 4, "n_inner": None})
+    assert config.inner_dim == 512 and config.activation == "gelu_tanh" and config.tie_word_embeddings
+
+
+def test_model_type_fallback_and_unknown(tmp_path):
+    name, cls, _ = resolve_architecture({"model_type": "gpt2"})
+    assert name == "GPT2LMHeadModel" and cls is GPT2Config
+    assert "GPT2LMHeadModel" in architecture_names()
+    with pytest.raises(ConfigError, match="unknown architecture"):
+        resolve_architecture({"architectures": ["LlamaForCausalLM"]})
+    with pytest.raises(ConfigError, match="names no architecture"):
+        resolve_architecture({"hidden_size": 4})
+    with pytest.raises(ConfigError, match="no config.json"):
+        load_model_config(str(tmp_path))
+
+
+@pytest.mark.parametrize("bad", [
+    {"n_embd": 100, "n_head": 3},
+    {"activation_function": "relu"},
+    {"add_cross_attention": True},
+    {"scale_attn_by_inverse_layer_idx": True},
+    {"scale_attn_weights": False},
+    {"n_layer": 0},
+    {"vocab_size": -1},
+    {"n_positions": 64, "n_ctx": 32},
+])
+def test_refuses_what_it_does_not_compute(bad):
+    with pytest.raises(ConfigError):
+        GPT2Config.from_dict(bad)
+
+
+def test_round_trip_and_named():
+    config = named_config("tiny-b")
+    again = GPT2Config.from_dict(config.to_dict())
+    assert again == config
+    assert named_config("gpt2-124m").head_dim == 64
+    with pytest.raises(ConfigError):
+        named_config("gpt5")
+
+
+def test_engine_config_checks():
+    assert EngineConfig().block_size == 16
+    for bad in (dict(dtype="float16"), dict(block_size=12), dict(block_size=128), dict(max_num_seqs=0),
+                dict(strategy="fifo"), dict(prefill_chunk_size=0), dict(num_blocks=0), dict(kv_cache_memory_mb=0)):
+        with pytest.raises(ConfigError):
+            EngineConfig(**bad)

@@ -1,0 +1,140 @@
+"""The scheduler's decisions, with a fake engine (no GPU): admission, portions under a token
+budget, decode priority, finishing and freeing, and what happens when pages run out."""
+
+import numpy as np
+import pytest
+
+from pagedserve_b200.cache import CacheManager, KVNeed
+from pagedserve_b200.engine.scheduler import Scheduler
+
+
+class FakeLogits:
+    def __init__(self, rows):
+        self.shape = (rows, 50)
+
+
+class FakeEngine:
+    """Keeps a real cache manager (bookkeeping only) and emits token = position % vocab."""
+
+    vocab_size = 50
+    max_model_len = 64
+
+    def __init__(self, pages=16, page=4, slots=8):
+        self.cache = CacheManager([KVNeed(1, 16)], [None], page, pages, slots, self.max_model_len)
+        self.steps = []
+
+    def step(self, entries):
+        self.steps.append([(e.request, len(e.tokens), list(e.want)) for e in entries])
+        for entry in entries:
+            if entry.request not in self.cache:
+                self.cache.admit(entry.request)
+            self.cache.extend(entry.request, len(entry.tokens))
+        for entry in entries:
+            self.cache.commit(entry.request)
+        self.cache.check_invariants()
+        return FakeLogits(sum(len(e.want) for e in entries))
+
+    def sample(self, logits, temperatures, seeds, positions):
+        return [p % self.vocab_size for p in positions]
+
+    def finish(self, request):
+        self.cache.free(request)
+
+
+def test_orca_runs_whole_prompts_then_decodes():
+    engine = FakeEngine()
+    sched = Scheduler(engine, max_num_seqs=4, strategy="orca")
+    a = sched.add_token_request([1, 2, 3, 4, 5], max_new_tokens=3)
+    b = sched.add_token_request([6, 7], max_new_tokens=2)
+    first = sched.step()
+    assert engine.steps[0] == [(a, 5, [4]), (b, 2, [1])]
+    assert first == {a: 5, b: 2}                       # token = position of the sampled token
+    sched.step()
+    assert engine.steps[1] == [(a, 1, [0]), (b, 1, [0])]
+    assert b in sched.finished and sched.finished[b].generated_token_ids == [2, 3]
+    results = sched.run_until_complete()
+    assert results == {a: [5, 6, 7], b: [2, 3]}
+    assert sched.reserved_blocks == 0 and engine.cache.free_pages() == 16 and engine.cache.live_requests == 0
+
+
+def test_sarathi_cuts_prompts_and_decodes_first():
+    engine = FakeEngine()
+    sched = Scheduler(engine, max_num_seqs=4, strategy="sarathi", prefill_chunk_size=4)
+    a = sched.add_token_request(list(range(10)), max_new_tokens=4)
+    sched.step(); sched.step()
+    assert engine.steps[:2] == [[(a, 4, [])], [(a, 4, [])]]          # no logits before the prompt ends
+    b = sched.add_token_request(list(range(6)), max_new_tokens=2)
+    sched.step()
+    assert engine.steps[2] == [(a, 2, [1])]                            # last portion produces the first token
+    sched.step()
+    assert engine.steps[3] == [(a, 1, [0]), (b, 4, [])]                # decode first, one portion beside it
+    sched.step()
+    assert engine.steps[4] == [(a, 1, [0]), (b, 2, [1])]
+    sched.run_until_complete()
+    assert sched.reserved_blocks == 0 and engine.cache.free_pages() == 16
+
+
+def test_token_budget_cuts_portions_and_several_prefills():
+    engine = FakeEngine(pages=64)
+    sched = Scheduler(engine, max_num_seqs=8, max_num_batched_tokens=10, strategy="sarathi",
+                      prefill_chunk_size=8, max_prefills_per_step=0)
+    a = sched.add_token_request(list(range(12)), max_new_tokens=2)
+    b = sched.add_token_request(list(range(9)), max_new_tokens=2)
+    sched.step()
+    assert engine.steps[0] == [(a, 8, []), (b, 2, [])]                 # 8 + 2 = budget
+    sched.step()
+    assert engine.steps[1] == [(a, 4, [3]), (b, 6, [])]
+    sched.step()
+    assert engine.steps[2] == [(a, 1, [0]), (b, 1, [0])]
+    # orca is cut by the budget too
+    engine2 = FakeEngine(pages=64)
+    orca = Scheduler(engine2, max_num_seqs=8, max_num_batched_tokens=10, strategy="orca")
+    c = orca.add_token_request(list(range(14)), max_new_tokens=1)
+    orca.step(); orca.step()
+    assert engine2.steps == [[(c, 10, [])], [(c, 4, [3])]]
+
+
+def test_pages_run_out_requests_wait_and_nothing_is_preempted():
+    engine = FakeEngine(pages=6, page=4)                                # 24 tokens of cache
+    sched = Scheduler(engine, max_num_seqs=4, strategy="orca")
+    a = sched.add_token_request(list(range(10)), max_new_tokens=6)      # reserves 4 pages
+    b = sched.add_token_request(list(range(6)), max_new_tokens=6)       # needs 3: must wait
+    c = sched.add_token_request([1], max_new_tokens=1)                  # behind b: head of line
+    sched.step()
+    assert engine.steps[0] == [(a, 10, [9])] and sched.reserved_blocks == 4
+    while a not in sched.finished:
+        assert all(entry[0] == a for entry in engine.steps[-1])
+        sched.step()
+    sched.step()
+    assert [entry[0] for entry in engine.steps[-1]] == [b, c]          # admitted once a gave its pages back
+    sched.run_until_complete()
+    assert set(sched.finished) == {a, b, c} and engine.cache.free_pages() == 6
+    with pytest.raises(ValueError, match="can never fit"):
+        sched.add_token_request(list(range(20)), max_new_tokens=8)      # 7 pages > pool
+
+
+def test_submit_checks_and_eos():
+    engine = FakeEngine()
+    sched = Scheduler(engine, eos_token_id=4)
+    for bad in ([], [1, 99], [1, -1], [1.5]):
+        with pytest.raises(ValueError):
+            sched.add_token_request(bad, max_new_tokens=2)
+    with pytest.raises(ValueError, match="context limit"):
+        sched.add_token_request([1] * 60, max_new_tokens=10)
+    with pytest.raises(ValueError):
+        sched.add_token_request([1], max_new_tokens=0)
+    with pytest.raises(ValueError, match="Unknown scheduling strategy"):
+        Scheduler(engine, strategy="fifo")
+    r = sched.add_token_request([1, 2, 3], max_new_tokens=9)            # emits 3, then 4 == eos
+    assert sched.run_until_complete() == {r: [3, 4]}
+    assert sched.step() == {}
+
+
+def test_max_num_seqs_limits_a_step():
+    engine = FakeEngine(pages=64)
+    sched = Scheduler(engine, max_num_seqs=2, strategy="orca")
+    ids = [sched.add_token_request([1, 2], max_new_tokens=2) for _ in range(3)]
+    sched.step()
+    assert [entry[0] for entry in engine.steps[0]] == ids[:2]
+    sched.run_until_complete()
+    assert set(sched.finished) == set(ids)
