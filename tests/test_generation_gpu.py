@@ -1,0 +1,130 @@
+"""Generation through the Python entry point and the command line, compared with the plain
+implementation: greedy (exact tokens in float32) and temperature sampling."""
+
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_gpt2
+
+pytestmark = pytest.mark.gpu
+
+PROMPT_LENGTHS = {"a": [5, 17, 33], "b": [1, 9, 40, 64, 100]}
+
+
+def make_engine(which, dtype, **options):
+    from pagedserve_b200.config.engine_config import EngineConfig
+    from pagedserve_b200.engine.engine import Engine
+
+    block = helpers.TINY[which][2]
+    defaults = dict(dtype=dtype, block_size=block, num_blocks=512 // block, max_num_seqs=8)
+    defaults.update(options)
+    return Engine.from_folder(helpers.model_folder(which), EngineConfig(**defaults))
+
+
+def prompts_of(which):
+    vocab = helpers.TINY[which][0]["vocab_size"]
+    return [helpers.random_tokens(vocab, length, seed=11 + length) for length in PROMPT_LENGTHS[which]]
+
+
+@pytest.mark.parametrize("strategy,chunk", [("orca", 16), ("sarathi", 24)])
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_greedy_generation_equals_plain(which, strategy, chunk):
+    from pagedserve_b200.engine.engine import generate
+
+    config, weights = helpers.plain_model(which)
+    prompts = prompts_of(which)
+    want = [plain_gpt2.generate(config, weights, prompt, 8) for prompt in prompts]
+    engine = make_engine(which, "float32")
+    got = generate(engine, prompts, max_new_tokens=8, strategy=strategy, prefill_chunk_size=chunk)
+    assert got == want
+    assert engine.cache.live_requests == 0 and engine.cache.free_pages() == engine.cache.total_pages()
+    engine.cache.check_invariants()
+
+
+def test_temperature_sampling_follows_the_keyed_noise():
+    """Tiny B, mixed batch with 24-token portions beside decodes, 12 tokens at T = 0.8:
+    every sampled token must (nearly) maximise logit/T + gumbel(seed, position, i) under the
+    plain model, whatever else was in its batch."""
+    from pagedserve_b200.engine.engine import generate
+
+    config, weights = helpers.plain_model("b")
+    prompts = prompts_of("b")
+    engine = make_engine("b", "float32")
+    got = generate(engine, prompts, max_new_tokens=12, temperature=0.8, seed=1234, strategy="sarathi",
+                   prefill_chunk_size=24, max_num_seqs=4)
+    again = generate(make_engine("b", "float32"), prompts, max_new_tokens=12, temperature=0.8, seed=1234,
+                     strategy="orca")
+    assert got == again, "sampled tokens depend on the batching"
+    for index, (prompt, produced) in enumerate(zip(prompts, got)):
+        tokens = list(prompt)
+        for token in produced:
+            logits = plain_gpt2.forward_logits(config, weights, tokens)[-1]
+            scores = plain_gpt2.temperature_scores(logits, 0.8, 1234 + index, len(tokens))
+            assert scores[token] >= scores.max() - 1e-4, f"request {index}: token {token} is not the draw"
+            tokens.append(token)
+    greedy = generate(make_engine("b", "float32"), prompts, max_new_tokens=12)
+    assert greedy != got
+
+
+def test_bfloat16_generation_tracks_plain_logits():
+    """In bfloat16 a near-tie may flip a greedy token; each chosen token must be within the
+    bfloat16 tolerance of the plain model's best logit along the engine's own path."""
+    from pagedserve_b200.engine.engine import generate
+
+    config, weights = helpers.plain_model("a")
+    prompts = prompts_of("a")
+    got = generate(make_engine("a", "bfloat16"), prompts, max_new_tokens=8)
+    for prompt, produced in zip(prompts, got):
+        tokens = list(prompt)
+        for token in produced:
+            logits = plain_gpt2.forward_logits(config, weights, tokens)[-1]
+            slack = helpers.TOLERANCE["bfloat16"] * float(logits.abs().max()) * 2
+            assert float(logits[token]) >= float(logits.max()) - slack
+            tokens.append(token)
+
+
+def test_sampler_kernel_alone():
+    from pagedserve_b200.kernels.ops import Ops
+    from pagedserve_b200.sampling.sampler import Sampler
+
+    ops = Ops(torch.float32)
+    sampler = Sampler(ops, "cuda:0", max_rows=4)
+    generator = torch.Generator().manual_seed(5)
+    logits = torch.randn(7, 1003, generator=generator)
+    logits[2, 17] = logits[2, 900] = 9.0                    # a tie: lowest index wins
+    device_logits = logits.cuda()
+    assert sampler.sample(device_logits, [0.0] * 7, [0] * 7, [0] * 7) == [
+        17 if r == 2 else int(torch.argmax(logits[r])) for r in range(7)]
+    temperatures = [0.0, 0.5, 1.0, 2.0, 0.0, 1.3, 0.7]
+    seeds = [1, 2, 3, 2 ** 63 + 5, 5, 6, 7]
+    positions = [0, 3, 900, 12, 5, 1, 77]
+    got = sampler.sample(device_logits, temperatures, seeds, positions)
+    for r in range(7):
+        if temperatures[r] == 0:
+            assert got[r] == (17 if r == 2 else int(torch.argmax(logits[r])))
+        else:
+            scores = plain_gpt2.temperature_scores(logits[r], temperatures[r], seeds[r], positions[r])
+            assert scores[got[r]] >= scores.max() - 1e-4
+    # the draw is a sample of softmax(logits / T): empirical frequencies over many positions
+    row = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).cuda().repeat(4000, 1)
+    draws = sampler.sample(row, [1.0] * 4000, [9] * 4000, list(range(4000)))
+    freq = np.bincount(draws, minlength=4) / 4000.0
+    want = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0).numpy()
+    assert np.abs(freq - want).max() < 0.03
+
+
+def test_command_line_runs():
+    out = subprocess.run([sys.executable, "-m", "pagedserve_b200", "--model", helpers.model_folder("a"),
+                          "--dtype", "float32", "--strategy", "sarathi", "--prefill-chunk-size", "4",
+                          "--max-new-tokens", "5", "--prompt-ids", "5 17 3 200", "--prompt-ids", "9,8,7"],
+                         capture_output=True, text=True, cwd=helpers.os.path.dirname(helpers.__file__) + "/..")
+    assert out.returncode == 0, out.stderr
+    lines = [line for line in out.stdout.splitlines() if line.startswith("request ")]
+    config, weights = helpers.plain_model("a")
+    assert lines == [f"request 0: {plain_gpt2.generate(config, weights, [5, 17, 3, 200], 5)!r}",
+                     f"request 1: {plain_gpt2.generate(config, weights, [9, 8, 7], 5)!r}"]
