@@ -33,6 +33,7 @@ NVCC_FLAGS = [
 # library name -> sources (relative to csrc/)
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["embed_norm.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu"],
+    "bf16": ["gemm_skinny.cu", "attention_decode.cu"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

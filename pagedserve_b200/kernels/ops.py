@@ -66,6 +66,8 @@ class Ops:
         self.dtype = dtype
         self.code = _DTYPE_CODE[dtype]
         self.core = _load_library("core")
+        self.fast = _load_library("bf16") if dtype == torch.bfloat16 else None
+        self._counters = None        # zeroed int32 scratch of the split attention kernel
         self.launches = 0            # count of kernel launches issued through this object
 
     # ------------------------------------------------------------------ embedding
@@ -138,6 +140,32 @@ class Ops:
                "gemm_simt")
         return out
 
+    def linear_skinny(self, a, w, bias, out, act=None, accumulate=False):
+        """Weight-streaming product for at most 64 rows of ``a`` (bfloat16 operands)."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError("linear_skinny: shapes do not match")
+        _require(a, "a", torch.bfloat16)
+        _require(w, "w", torch.bfloat16)
+        _require(out, "out")
+        if bias is not None:
+            _require(bias, "bias", torch.float32)
+        if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("linear_skinny: innermost stride must be 1")
+        self.launches += 1
+        _check(self.fast.ps_gemm_skinny(_ptr(a), _c_int(a.stride(0)), _ptr(w), _c_int(w.stride(0)), _ptr(bias),
+                                        _ptr(out), _c_int(out.stride(0)), _c_int(M), _c_int(N), _c_int(K),
+                                        _c_int(dtype_code(out.dtype)), _c_int(_ACT_CODE[act]),
+                                        _c_int(1 if accumulate else 0), _stream()), "gemm_skinny")
+        return out
+
+    @staticmethod
+    def skinny_ok(a, w):
+        K = a.shape[1]
+        return (a.shape[0] <= 64 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
     def linear(self, a, w, bias, out, act=None, accumulate=False):
         """The matrix product of the model: float32 runs on FFMA, bfloat16 on tensor cores."""
         if self.dtype == torch.float32:
@@ -178,6 +206,34 @@ class Ops:
             _c_int(block_table.stride(0)), _c_int(T), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
             _c_int(page_size), _c_int(window or 0), _c_float(scale), _c_int(self.code), _stream()),
             "paged_attention_simt")
+        return out
+
+    def paged_attention_decode(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
+                               n_heads, n_kv_heads, head_dim, page_size, window, scale, max_kv_len,
+                               target_ctas=296):
+        """Split-key attention for few query tokens (bfloat16).  ``max_kv_len`` bounds the context of
+        every token in the call; it fixes the grid, so a CUDA graph passes the model's maximum."""
+        T = q.shape[0]
+        _require(q, "q", torch.bfloat16)
+        _require(out, "out", torch.bfloat16)
+        tiles = max(1, -(-int(max_kv_len) // 32))
+        wanted = max(1, target_ctas // max(1, T * n_heads))
+        split_tiles = max(2, -(-tiles // wanted))
+        n_splits = -(-tiles // split_tiles)
+        part_acc = part_ml = counters = None
+        if n_splits > 1:
+            if self._counters is None or self._counters.numel() < T * n_heads:
+                self._counters = torch.zeros(max(1024, T * n_heads), dtype=torch.int32, device=q.device)
+            counters = self._counters
+            part_acc = torch.empty((T * n_heads * n_splits, head_dim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((T * n_heads * n_splits, 2), dtype=torch.float32, device=q.device)
+        self.launches += 1
+        _check(self.fast.ps_paged_attention_decode(
+            _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(k_pool), _ptr(v_pool),
+            _c_ll(page_stride), _ptr(token_item), _ptr(positions), _ptr(block_table),
+            _c_int(block_table.stride(0)), _c_int(T), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+            _c_int(page_size), _c_int(window or 0), _c_float(scale), _c_int(split_tiles), _c_int(n_splits),
+            _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()), "paged_attention_decode")
         return out
 
     def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):

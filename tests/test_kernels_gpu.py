@@ -1,0 +1,274 @@
+"""Each kernel alone against a plain float64 reference, at sizes other than the engine's."""
+
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def ops_for(dtype):
+    from pagedserve_b200.kernels.ops import Ops
+
+    return Ops(dtype)
+
+
+def rel_err(got, want):
+    want = want.double().cpu()
+    return float((got.double().cpu() - want).abs().max() / max(1e-30, float(want.abs().max())))
+
+
+# ------------------------------------------------------------------ embedding, norm
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [48, 200, 768])
+def test_embed(dtype, H):
+    ops = ops_for(dtype)
+    g = torch.Generator().manual_seed(1)
+    wte = torch.randn(301, H, generator=g).to(dtype)
+    wpe = torch.randn(77, H, generator=g).to(dtype)
+    ids = torch.randint(0, 301, (53,), generator=g, dtype=torch.int32)
+    pos = torch.randint(0, 77, (53,), generator=g, dtype=torch.int32)
+    out = torch.empty(53, H, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed(ids.to(DEV), pos.to(DEV), wte.to(DEV), wpe.to(DEV), out, status)
+    want = wte.float()[ids.long()] + wpe.float()[pos.long()]
+    assert torch.equal(out.cpu(), want) and int(status.item()) == 0
+    ops.embed(ids.to(DEV), pos.to(DEV), wte.to(DEV), None, out, status)
+    assert torch.equal(out.cpu(), wte.float()[ids.long()])
+    bad = ids.clone(); bad[7] = 301
+    ops.embed(bad.to(DEV), pos.to(DEV), wte.to(DEV), wpe.to(DEV), out, status)
+    assert int(status.item()) == 1 and float(out[7].abs().max()) == 0.0      # flagged, not read out of range
+
+
+@pytest.mark.parametrize("H", [16, 96, 200, 768, 1600, 2500])
+@pytest.mark.parametrize("eps", [1e-5, 1e-6])
+def test_layernorm(H, eps):
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(H)
+    x = (torch.randn(37, H, generator=g) * 3 + 1.5)
+    gamma, beta = torch.randn(H, generator=g), torch.randn(H, generator=g)
+    want = plain_gpt2.layer_norm(x.double(), gamma.double(), beta.double(), eps)
+    out32 = torch.empty(37, H, dtype=torch.float32, device=DEV)
+    ops.layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, out32)
+    assert rel_err(out32, want) < 2e-6
+    out16 = torch.empty(37, H, dtype=torch.bfloat16, device=DEV)
+    ops.layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, out16)
+    assert rel_err(out16, want) < 5e-3
+    rows = torch.tensor([36, 0, 5], dtype=torch.int32)
+    picked = torch.empty(3, H, dtype=torch.float32, device=DEV)
+    ops.layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, picked, rows=rows.to(DEV))
+    assert torch.equal(picked.cpu(), out32.cpu()[rows.long()])
+    rms = torch.empty(37, H, dtype=torch.float32, device=DEV)
+    ops.layernorm(x.to(DEV), gamma.to(DEV), None, eps, rms, has_mean=False)
+    want_rms = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * gamma.double()
+    assert rel_err(rms, want_rms) < 2e-6
+
+
+# ------------------------------------------------------------------ matrix products
+def gemm_reference(a, w, bias, act, base):
+    y = a.double() @ w.double().T
+    if bias is not None:
+        y = y + bias.double()
+    if act == "gelu_tanh":
+        y = plain_gpt2.activation(y, "gelu_new")
+    elif act == "gelu_erf":
+        y = plain_gpt2.activation(y, "gelu")
+    if base is not None:
+        y = y + base.double()
+    return y
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 17, 8), (5, 130, 72), (70, 257, 100), (200, 96, 333)])
+@pytest.mark.parametrize("act", [None, "gelu_tanh", "gelu_erf"])
+def test_gemm_simt_float32(M, N, K, act):
+    ops = ops_for(torch.float32)
+    g = torch.Generator().manual_seed(M * N)
+    a, w, bias = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(N, generator=g)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_simt(a.to(DEV), w.to(DEV), bias.to(DEV), out, act=act)
+    assert rel_err(out, gemm_reference(a, w, bias, act, None)) < 3e-6
+    base = torch.randn(M, N, generator=g)
+    stream = base.clone().to(DEV)
+    ops.linear_simt(a.to(DEV), w.to(DEV), None, stream, accumulate=True)
+    assert rel_err(stream, gemm_reference(a, w, None, None, base)) < 3e-6
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    ops.linear_simt(a[M - 1:].to(DEV), w.to(DEV), bias.to(DEV), alone, act=act)
+    assert torch.equal(alone[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 40, 64])
+@pytest.mark.parametrize("N,K", [(48, 64), (1003, 96), (300, 320), (2304, 768), (770, 3072), (33, 4104)])
+def test_gemm_skinny(M, N, K):
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    for act, out_dtype, tol in ((None, torch.float32, 2e-5), ("gelu_tanh", torch.bfloat16, 6e-3),
+                                ("gelu_erf", torch.bfloat16, 6e-3)):
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        ops.linear_skinny(a.to(DEV), w.to(DEV), bias.to(DEV), out, act=act)
+        assert rel_err(out, gemm_reference(a, w, bias, act, None)) < tol, (act, out_dtype)
+    base = torch.randn(M, N, generator=g)
+    stream = base.clone().to(DEV)
+    ops.linear_skinny(a.to(DEV), w.to(DEV), bias.to(DEV), stream, accumulate=True)
+    assert rel_err(stream, gemm_reference(a, w, bias, None, base)) < 2e-5
+    # against the CUDA-core product with the same bfloat16 inputs: float32 sums in another order
+    simt = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    fast = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_simt(a.to(DEV), w.to(DEV), None, simt)
+    ops.linear_skinny(a.to(DEV), w.to(DEV), None, fast)
+    assert rel_err(fast, simt) < 1e-5
+
+
+def test_gemm_skinny_refuses_what_it_cannot_take():
+    from pagedserve_b200.kernels.ops import KernelError
+
+    ops = ops_for(torch.bfloat16)
+    a = torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="unsupported"):
+        ops.linear_skinny(a, w, None, torch.empty(65, 32, dtype=torch.float32, device=DEV))
+    a = torch.zeros(4, 36, dtype=torch.bfloat16, device=DEV)          # K not a multiple of 8
+    w = torch.zeros(32, 36, dtype=torch.bfloat16, device=DEV)
+    assert not ops.skinny_ok(a, w)
+    out = torch.empty(4, 32, dtype=torch.float32, device=DEV)
+    ops.linear(a, w, None, out)                                       # falls to the CUDA-core kernel
+    assert float(out.abs().max()) == 0.0
+
+
+# ------------------------------------------------------------------ paged cache + attention
+class PagedCase:
+    """Sequences with their own q, k, v; a fragmented page pool filled through kv_append."""
+
+    def __init__(self, ops, dtype, lengths, n_heads, n_kv_heads, head_dim, page_size, seed, spike=None):
+        g = torch.Generator().manual_seed(seed)
+        self.ops, self.dtype = ops, dtype
+        self.n_heads, self.n_kv_heads, self.head_dim, self.page_size = n_heads, n_kv_heads, head_dim, page_size
+        self.lengths = lengths
+        T = sum(lengths)
+        self.q = torch.randn(T, n_heads * head_dim, generator=g).to(dtype)
+        self.k = torch.randn(T, n_kv_heads * head_dim, generator=g).to(dtype)
+        self.v = torch.randn(T, n_kv_heads * head_dim, generator=g).to(dtype)
+        if spike is not None:
+            # make one far key dominate the last query of sequence 0: a kernel that skips it shows
+            far, head = spike
+            last = lengths[0] - 1
+            group = head // (n_heads // n_kv_heads)
+            direction = torch.randn(head_dim, generator=g)
+            direction = direction / direction.norm()
+            self.q[last, head * head_dim:(head + 1) * head_dim] = (direction * 12).to(dtype)
+            self.k[far, group * head_dim:(group + 1) * head_dim] = (direction * 12).to(dtype)
+        max_pages = max(-(-length // page_size) for length in lengths)
+        total_pages = sum(-(-length // page_size) for length in lengths) + 3
+        order = list(range(total_pages))
+        random.Random(seed).shuffle(order)                      # fragmented tables
+        table = torch.full((len(lengths), max_pages + 2), -1, dtype=torch.int32)
+        cursor = 0
+        token_item, positions = [], []
+        for item, length in enumerate(lengths):
+            pages = -(-length // page_size)
+            table[item, :pages] = torch.tensor(order[cursor:cursor + pages], dtype=torch.int32)
+            cursor += pages
+            token_item += [item] * length
+            positions += list(range(length))
+        self.table = table.to(DEV)
+        self.token_item = torch.tensor(token_item, dtype=torch.int32, device=DEV)
+        self.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+        # pool [pages, 1 layer, 2, kv heads, page, hd], poisoned so that a stale read shows
+        self.pool = torch.full((total_pages, 1, 2, n_kv_heads, page_size, head_dim), float("nan"),
+                               dtype=dtype, device=DEV)
+        self.page_stride = 2 * n_kv_heads * page_size * head_dim
+        self.k_pool, self.v_pool = self.pool[:, 0, 0], self.pool[:, 0, 1]
+        ops.kv_append(self.k.to(DEV), self.v.to(DEV), self.token_item, self.positions, self.table, self.k_pool,
+                      self.v_pool, self.page_stride, n_kv_heads, head_dim, page_size)
+
+    def reference(self, window=None):
+        rows = []
+        start = 0
+        rep = self.n_heads // self.n_kv_heads
+        for length in self.lengths:
+            sl = slice(start, start + length)
+            q = self.q[sl].double().reshape(length, self.n_heads, self.head_dim)
+            k = self.k[sl].double().reshape(length, self.n_kv_heads, self.head_dim).repeat_interleave(rep, 1)
+            v = self.v[sl].double().reshape(length, self.n_kv_heads, self.head_dim).repeat_interleave(rep, 1)
+            rows.append(plain_gpt2.causal_attention(q, k, v, window=window))
+            start += length
+        return torch.cat(rows)
+
+
+def test_kv_append_places_every_row():
+    ops = ops_for(torch.float32)
+    case = PagedCase(ops, torch.float32, [5, 17, 40], 4, 2, 16, 8, seed=3)
+    pool = case.pool.cpu()
+    start = 0
+    for item, length in enumerate(case.lengths):
+        for p in range(length):
+            page = int(case.table[item, p // 8])
+            got_k = pool[page, 0, 0, :, p % 8, :].reshape(-1)
+            got_v = pool[page, 0, 1, :, p % 8, :].reshape(-1)
+            assert torch.equal(got_k, case.k[start + p]) and torch.equal(got_v, case.v[start + p])
+        start += length
+    assert int(torch.isnan(pool).sum()) > 0          # untouched slots stay untouched
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (2, 2, 48, 8), (6, 2, 64, 16),
+                                                          (3, 1, 128, 32), (2, 2, 256, 4)])
+@pytest.mark.parametrize("window", [None, 19])
+def test_attention_simt_float32(heads, kv_heads, head_dim, page, window):
+    ops = ops_for(torch.float32)
+    lengths = [1, 15, 16, 17, 31, 32, 33, 128, 200]
+    case = PagedCase(ops, torch.float32, lengths, heads, kv_heads, head_dim, page, seed=head_dim + page)
+    out = torch.empty(sum(lengths), heads * head_dim, dtype=torch.float32, device=DEV)
+    ops.paged_attention_simt(case.q.to(DEV), out, case.k_pool, case.v_pool, case.page_stride, case.token_item,
+                             case.positions, case.table, heads, kv_heads, head_dim, page, window,
+                             head_dim ** -0.5)
+    assert torch.isfinite(out).all()
+    assert rel_err(out, case.reference(window)) < 3e-6
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (2, 2, 48, 8), (12, 12, 64, 16),
+                                                          (8, 2, 128, 32), (2, 1, 256, 64)])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("target_ctas", [1, 296, 100000])
+def test_attention_decode_bfloat16(heads, kv_heads, head_dim, page, window, target_ctas):
+    """Contexts around page and tile edges, fragmented tables, one split up to a split per 64 keys."""
+    ops = ops_for(torch.bfloat16)
+    lengths = [1, 15, 16, 17, 31, 32, 33, 64, 65, 128, 512, 1024]
+    case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=7 + head_dim)
+    out = torch.empty(sum(lengths), heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_decode(case.q.to(DEV), out, case.k_pool, case.v_pool, case.page_stride, case.token_item,
+                               case.positions, case.table, heads, kv_heads, head_dim, page, window,
+                               head_dim ** -0.5, max(lengths), target_ctas=target_ctas)
+    assert torch.isfinite(out.float()).all()
+    assert rel_err(out, case.reference(window)) < 8e-3
+    assert int(ops._counters.abs().sum()) == 0 if ops._counters is not None else True
+
+
+@pytest.mark.parametrize("far", [0, 31, 32, 255, 256, 600])
+def test_attention_finds_a_far_key(far):
+    """One key among a thousand carries almost all the weight: the output must be its value."""
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 8e-3)):
+        ops = ops_for(dtype)
+        case = PagedCase(ops, dtype, [1000, 40], 4, 2, 64, 16, seed=far, spike=(far, 3))
+        out = torch.empty(1040, 4 * 64, dtype=dtype, device=DEV)
+        if dtype == torch.float32:
+            ops.paged_attention_simt(case.q.to(DEV), out, case.k_pool, case.v_pool, case.page_stride,
+                                     case.token_item, case.positions, case.table, 4, 2, 64, 16, None, 0.125)
+        else:
+            ops.paged_attention_decode(case.q.to(DEV), out, case.k_pool, case.v_pool, case.page_stride,
+                                       case.token_item, case.positions, case.table, 4, 2, 64, 16, None, 0.125,
+                                       1000, target_ctas=100000)
+        want = case.reference()
+        got_row = out[999, 3 * 64:4 * 64].double().cpu()
+        value_row = case.v[far, 64:128].double()
+        assert float((got_row - value_row).abs().max()) < 0.05          # the spike's value came through
+        assert rel_err(out, want) < tol
