@@ -28,7 +28,7 @@ template <int NT>
 __global__ void sample_kernel(const float* __restrict__ logits, int ld, int V,
                               const float* __restrict__ temperature,
                               const unsigned long long* __restrict__ seed, const int* __restrict__ position,
-                              int* __restrict__ out) {
+                              int pos_offset, int* __restrict__ out) {
     __shared__ float best_v[NT / 32];
     __shared__ int best_i[NT / 32];
     int r = blockIdx.x;
@@ -37,7 +37,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int V,
     unsigned long long key = 0;
     float inv_t = 1.f;
     if (temp > 0.f) {
-        key = mix64(mix64(seed[r]) ^ (unsigned long long)(long long)position[r]);
+        key = mix64(mix64(seed[r]) ^ (unsigned long long)(long long)(position[r] + pos_offset));
         inv_t = 1.0f / temp;
     }
     float bv = -INFINITY;
@@ -63,12 +63,43 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int V,
     }
 }
 
+// After a decode step that sampled on the device: feed the sampled token back as the next input,
+// move every request one position on, and append the tokens to the history of the run.
+__global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids,
+                               int* __restrict__ positions, int* __restrict__ kv_len,
+                               int* __restrict__ history, int* __restrict__ step_counter, int B, int max_steps) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    int step = *step_counter;
+    if (i < B) {
+        int token = sampled[i];
+        token_ids[i] = token;
+        positions[i] += 1;
+        kv_len[i] += 1;
+        if (step < max_steps) history[(size_t)step * B + i] = token;
+    }
+    __syncthreads();
+    if (i == 0) *step_counter = step + 1;
+}
+
 }  // namespace ps
 
+// position[r] + pos_offset keys the noise of row r (the index of the token being drawn).
 PS_EXPORT int ps_sample(const float* logits, int ld, int R, int V, const float* temperature,
-                        const unsigned long long* seed, const int* position, int* out, void* stream) {
+                        const unsigned long long* seed, const int* position, int pos_offset, int* out,
+                        void* stream) {
     if (R <= 0) return PS_OK;
     if (V <= 0 || ld < V) return PS_ERR_BAD_ARGUMENT;
-    ps::sample_kernel<256><<<R, 256, 0, (cudaStream_t)stream>>>(logits, ld, V, temperature, seed, position, out);
+    ps::sample_kernel<256><<<R, 256, 0, (cudaStream_t)stream>>>(logits, ld, V, temperature, seed, position,
+                                                                pos_offset, out);
+    return ps::launch_status();
+}
+
+// One block: B <= 1024.
+PS_EXPORT int ps_advance(const int* sampled, int* token_ids, int* positions, int* kv_len, int* history,
+                         int* step_counter, int B, int max_steps, void* stream) {
+    if (B <= 0) return PS_OK;
+    if (B > 1024) return PS_ERR_UNSUPPORTED;
+    ps::advance_kernel<<<1, ((B + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(sampled, token_ids, positions, kv_len,
+                                                                            history, step_counter, B, max_steps);
     return ps::launch_status();
 }

@@ -54,6 +54,8 @@ class BatchLayout:
     q_start: int = 0
     kv_len: int = 0
     logit_rows: int = 0
+    temperature: int = 0          # float32 bits, one per item
+    seed: int = 0                 # 64-bit, two words per item
     tables: List[int] = field(default_factory=list)
     total: int = 0
 
@@ -62,7 +64,8 @@ class BatchLayout:
         for name, count in (("token_ids", self.num_tokens), ("positions", self.num_tokens),
                             ("token_item", self.num_tokens), ("item_slot", self.num_items),
                             ("q_start", self.num_items + 1), ("kv_len", self.num_items),
-                            ("logit_rows", max(self.num_rows, 1))):
+                            ("logit_rows", max(self.num_rows, 1)), ("temperature", self.num_items),
+                            ("seed", 2 * self.num_items)):
             setattr(self, name, cursor)
             cursor += _pad4(count)
         self.tables = []
@@ -116,6 +119,8 @@ class StepContext:
         self.q_start = buf[layout.q_start:layout.q_start + I + 1]
         self.kv_len = buf[layout.kv_len:layout.kv_len + I]
         self.logit_rows = buf[layout.logit_rows:layout.logit_rows + R]
+        self.temperature = buf[layout.temperature:layout.temperature + I].view(torch.float32)
+        self.seed = buf[layout.seed:layout.seed + 2 * I].view(torch.int64)
         self.block_tables = [
             buf[offset:offset + I * width].view(I, width)
             for offset, width in zip(layout.tables, layout.table_widths)

@@ -48,7 +48,8 @@ class Engine:
             raise ValueError("an engine needs a model folder or tensors")
         self.cache = self._make_cache()
         self.runner = ModelRunner(self.model, self.cache, self.device,
-                                  max_step_tokens=engine_config.max_num_batched_tokens)
+                                  max_step_tokens=engine_config.max_num_batched_tokens,
+                                  enable_cuda_graphs=engine_config.enable_cuda_graphs)
         self.sampler = Sampler(self.ops, self.device, max_rows=max(64, engine_config.max_num_seqs))
 
     # ------------------------------------------------------------------ construction
@@ -109,6 +110,11 @@ class Engine:
     def step(self, entries: Sequence) -> torch.Tensor:
         """Run (request, tokens, want) entries as one batch; float32 logits at the wanted places."""
         return self.runner.step(entries)
+
+    def decode(self, entries: Sequence, temperatures, seeds, steps: int = 1):
+        """Run ``steps`` decode steps of single-token entries on the device (sampling included);
+        returns the sampled tokens as an int32 array ``[steps, batch]``."""
+        return self.runner.decode(entries, temperatures, seeds, steps)
 
     def finish(self, request: Hashable) -> None:
         self.runner.finish(request)

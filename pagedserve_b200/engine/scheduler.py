@@ -197,21 +197,33 @@ class Scheduler:
             if want:
                 sampling.append(request)
             entries.append(StepEntry(request.request_id, tokens, want))
+        decode_only = all(request.pending_token_id is not None for request, _ in selected)
+        fused_decode = getattr(self.engine, "decode", None) if decode_only else None
         try:
-            logits = self.engine.step(entries)
+            if fused_decode is not None:
+                # every entry is one decoded token: forward and sampling run as one device step
+                tokens = fused_decode(
+                    entries,
+                    [request.temperature for request in sampling],
+                    [request.seed for request in sampling],
+                    1,
+                )[0].tolist()
+            else:
+                logits = self.engine.step(entries)
         except Exception:
             for request in new_requests:                      # reference: :243-247
                 self.reserved_blocks -= request.reserved_blocks
                 request.reserved_blocks = 0
             raise
-        if logits.shape[0] != len(sampling):
-            raise RuntimeError("Model returned the wrong number of logits rows")   # reference: :260-263
-        tokens = self.engine.sample(
-            logits,
-            [request.temperature for request in sampling],
-            [request.seed for request in sampling],
-            [len(request.prompt_token_ids) + len(request.generated_token_ids) for request in sampling],
-        )
+        if fused_decode is None:
+            if logits.shape[0] != len(sampling):
+                raise RuntimeError("Model returned the wrong number of logits rows")   # reference: :260-263
+            tokens = self.engine.sample(
+                logits,
+                [request.temperature for request in sampling],
+                [request.seed for request in sampling],
+                [len(request.prompt_token_ids) + len(request.generated_token_ids) for request in sampling],
+            )
         emitted: Dict[int, int] = {}
         completed_prefill = set()
         produced = iter(tokens)

@@ -23,12 +23,28 @@ class StepError(ValueError):
     pass
 
 
+class _DecodeGraph:
+    """A captured decode-only step of one batch size: static logits and the number of kernels."""
+
+    def __init__(self, graph, logits, kernels):
+        self.graph = graph
+        self.logits = logits
+        self.kernels = kernels
+
+    def replay(self):
+        self.graph.replay()
+
+
 class ModelRunner:
     """Owns the device metadata buffers and drives ``model.forward`` for one step."""
 
     STAGING_BUFFERS = 4
 
-    def __init__(self, model, cache: CacheManager, device, max_step_tokens: int = 8192):
+    MAX_DEVICE_STEPS = 1024          # most decode steps one ``decode`` call runs without the host
+    MAX_GRAPHS = 96
+
+    def __init__(self, model, cache: CacheManager, device, max_step_tokens: int = 8192,
+                 enable_cuda_graphs: bool = True):
         self.model = model
         self.cache = cache
         self.device = torch.device(device)
@@ -45,11 +61,21 @@ class ModelRunner:
                                min(max_step_tokens, 4 * cache.max_slots), self.table_widths).total)
         self.steps = 0
         self.tokens_run = 0
+        self.enable_cuda_graphs = enable_cuda_graphs
+        self.ops = model.env.ops
+        self._graphs = {}                 # (batch size, kind) -> _DecodeGraph
+        self.graph_replays = 0
+        self._sampled = torch.zeros(cache.max_slots, dtype=torch.int32, device=self.device)
+        self._history = torch.zeros(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32,
+                                    device=self.device)
+        self._history_host = torch.empty(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32).pin_memory()
+        self._step_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def _grow(self, needed: int) -> None:
         if needed <= self._capacity:
             return
         torch.cuda.synchronize(self.device)
+        self._graphs = {}                 # captured graphs point into the old buffer
         self._capacity = int(needed * 1.25) + 64
         self._device_buffer = torch.empty(self._capacity, dtype=torch.int32, device=self.device)
         self._staging = [torch.empty(self._capacity, dtype=torch.int32).pin_memory()
@@ -57,8 +83,11 @@ class ModelRunner:
         self._staging_events = [None] * self.STAGING_BUFFERS
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Validate, take pages for the new positions, build and upload the metadata."""
+    def prepare(self, entries: Sequence[StepEntry], extra_tokens: int = 0, sampling=None) -> StepContext:
+        """Validate, take pages for the new positions, build and upload the metadata.
+
+        ``extra_tokens`` more positions per request get pages too (a run of several decode steps on
+        the device); ``sampling`` = (temperatures, seeds) per entry is uploaded with the batch."""
         if not entries:
             raise StepError("a step cannot be empty")                 # reference: iteration.py:50-51
         cache = self.cache
@@ -79,11 +108,11 @@ class ModelRunner:
                     cache.admit(entry.request)
                     admitted.append(entry.request)
                 start = cache.length(entry.request)
-                if start + len(entry.tokens) > self.max_model_len:
+                if start + len(entry.tokens) + extra_tokens > self.max_model_len:
                     # reference: src/model/paged_decoder.py:521-522
                     raise StepError(f"request {entry.request!r} would pass the model's maximum length "
                                     f"{self.max_model_len}")
-                cache.extend(entry.request, len(entry.tokens))
+                cache.extend(entry.request, len(entry.tokens) + extra_tokens)
                 extended.append(entry.request)
         except Exception:
             for request in extended:
@@ -132,6 +161,12 @@ class ModelRunner:
             max_kv = max(max_kv, start + count)
             cursor += count
         q_start[I] = cursor
+        if sampling is not None:
+            temperatures, seeds = sampling
+            host[layout.temperature:layout.temperature + I].view(np.float32)[:] = np.asarray(
+                temperatures, dtype=np.float32)
+            host[layout.seed:layout.seed + 2 * I].view(np.uint64)[:] = np.asarray(
+                [int(seed) & 0xFFFFFFFFFFFFFFFF for seed in seeds], dtype=np.uint64)
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
             table = host[offset:offset + I * width].reshape(I, width)
             for index, entry in enumerate(entries):
@@ -147,17 +182,24 @@ class ModelRunner:
         self.h2d_bytes = layout.total * 4
         return StepContext(layout, self._device_buffer, host_batch, cache, self._status, max_q, max_kv)
 
+    def _abandon(self, entries) -> None:
+        for entry in entries:
+            self.cache.rollback(entry.request)
+        for request in self._admitted_in_step:
+            self.cache.free(request)
+
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one step; returns float32 logits ``[R, V]`` (R may be 0)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         ctx = self.prepare(entries)
+        decode_only = ctx.decode_only and all(entry.want == [0] for entry in entries)
         try:
-            logits = self.model.forward(ctx)
+            if decode_only and self.enable_cuda_graphs:
+                logits = self._run_decode_graph(ctx, "logits").logits.clone()
+            else:
+                logits = self.model.forward(ctx)
         except Exception:
-            for entry in entries:
-                self.cache.rollback(entry.request)
-            for request in self._admitted_in_step:
-                self.cache.free(request)
+            self._abandon(entries)
             raise
         for entry in entries:
             self.cache.commit(entry.request)
@@ -168,6 +210,84 @@ class ModelRunner:
             # reference: src/scheduler/orca_scheduler.py:260-263, 281-286
             raise StepError(f"model returned {logits.shape[0]} logits rows, expected {expected}")
         return logits
+
+    # ------------------------------------------------------------------ decode-only steps
+    def decode(self, entries: Sequence[StepEntry], temperatures, seeds, steps: int = 1) -> np.ndarray:
+        """Run ``steps`` decode steps of a batch of single tokens without the host in between.
+
+        Every entry holds the one next token of a request whose prompt is already in the cache.
+        Each step samples on the device (greedy or temperature), feeds the token back as the next
+        input and moves the request one position on.  Returns the sampled tokens ``[steps, B]``.
+        The step is replayed as a CUDA graph (reference: decode-only fast path with CUDA graphs,
+        src/model/paged_decoder.py:385-496) unless graphs are disabled.
+        """
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries or any(len(entry.tokens) != 1 for entry in entries):
+            raise StepError("decode takes exactly one token per request")
+        if not (1 <= steps <= self.MAX_DEVICE_STEPS):
+            raise StepError(f"steps must be between 1 and {self.MAX_DEVICE_STEPS}")
+        for entry in entries:
+            entry.want = [0]
+        ctx = self.prepare(entries, extra_tokens=steps - 1, sampling=(temperatures, seeds))
+        B = ctx.num_items
+        try:
+            self._step_counter.zero_()
+            if self.enable_cuda_graphs:
+                graph = self._run_decode_graph(ctx, "sample")
+                for _ in range(steps - 1):
+                    graph.replay()
+                    self.graph_replays += 1
+            else:
+                for _ in range(steps):
+                    self._forward_and_sample(ctx)
+            self._history_host[:steps * B].copy_(self._history[:steps * B], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        except Exception:
+            self._abandon(entries)
+            raise
+        for entry in entries:
+            self.cache.commit(entry.request)
+        self.steps += steps
+        self.tokens_run += steps * B
+        return self._history_host[:steps * B].numpy().reshape(steps, B).copy()
+
+    def _forward_and_sample(self, ctx: StepContext) -> torch.Tensor:
+        logits = self.model.forward(ctx)
+        B = ctx.num_items
+        sampled = self._sampled[:B]
+        # the token drawn now will sit at position (input position + 1)
+        self.ops.sample(logits, ctx.temperature, ctx.seed, ctx.positions, sampled, pos_offset=1)
+        self.ops.advance(sampled, ctx.token_ids, ctx.positions, ctx.kv_len, self._history, self._step_counter,
+                         self.MAX_DEVICE_STEPS)
+        return logits
+
+    def _run_decode_graph(self, ctx: StepContext, kind: str):
+        """Run the decode-only step ``ctx`` once: eagerly the first time a batch size is seen
+        (then capture it), by graph replay afterwards."""
+        ctx.max_kv_len = self.max_model_len          # the graph's grid must cover any context
+        key = (ctx.num_items, kind)
+        graph = self._graphs.get(key)
+        if graph is not None:
+            graph.replay()
+            self.graph_replays += 1
+            return graph
+        if len(self._graphs) >= self.MAX_GRAPHS:
+            self._graphs.pop(next(iter(self._graphs)))
+        # warm-up run (this is the step's real execution), then capture for the next time
+        if kind == "sample":
+            self._forward_and_sample(ctx)
+        else:
+            warm = self.model.forward(ctx)
+        torch.cuda.current_stream().synchronize()
+        launches_before = self.ops.launches
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            logits = self._forward_and_sample(ctx) if kind == "sample" else self.model.forward(ctx)
+        graph = _DecodeGraph(captured, logits, self.ops.launches - launches_before)
+        self._graphs[key] = graph
+        if kind == "logits":
+            logits.copy_(warm)                       # this call's result
+        return graph
 
     def finish(self, request: Hashable) -> None:
         """The request is done: its pages and its slot are given back."""

@@ -249,8 +249,9 @@ class Ops:
         return tensorcore.attention(self, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale)
 
     # ------------------------------------------------------------------ sampling
-    def sample(self, logits, temperature, seed, position, out):
-        """out[r] = argmax (temperature 0) or a Gumbel-max draw; logits float32 [R, V]."""
+    def sample(self, logits, temperature, seed, position, out, pos_offset=0):
+        """out[r] = argmax (temperature 0) or a Gumbel-max draw keyed by (seed[r], position[r] + pos_offset);
+        logits float32 [R, V]."""
         R, V = logits.shape
         _require(logits, "logits", torch.float32)
         _require(out, "out", torch.int32)
@@ -260,5 +261,14 @@ class Ops:
             _require(position, "position", torch.int32)
         self.launches += 1
         _check(self.core.ps_sample(_ptr(logits), _c_int(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
-                                   _ptr(seed), _ptr(position), _ptr(out), _stream()), "sample")
+                                   _ptr(seed), _ptr(position), _c_int(pos_offset), _ptr(out), _stream()),
+               "sample")
         return out
+
+    def advance(self, sampled, token_ids, positions, kv_len, history, step_counter, max_steps):
+        """Feed sampled tokens back as the next inputs of a decode-only batch and move it one position on."""
+        B = sampled.numel()
+        self.launches += 1
+        _check(self.core.ps_advance(_ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(kv_len), _ptr(history),
+                                    _ptr(step_counter), _c_int(B), _c_int(max_steps), _stream()),
+               "advance")

@@ -128,3 +128,46 @@ def test_command_line_runs():
     config, weights = helpers.plain_model("a")
     assert lines == [f"request 0: {plain_gpt2.generate(config, weights, [5, 17, 3, 200], 5)!r}",
                      f"request 1: {plain_gpt2.generate(config, weights, [9, 8, 7], 5)!r}"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_equals_eager_and_device_loop_equals_stepwise(dtype):
+    """The captured decode step gives the logits of the eager step, and a run of several decode
+    steps on the device gives the tokens of step-by-step generation."""
+    from pagedserve_b200.engine.batch import StepEntry
+
+    vocab = helpers.TINY["b"][0]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=n) for n in (7, 30, 64)]
+    results = {}
+    for graphs in (False, True):
+        engine = make_engine("b", dtype, enable_cuda_graphs=graphs)
+        first = engine.step([StepEntry(i, p, [len(p) - 1]) for i, p in enumerate(prompts)])
+        tokens = [int(t) for t in first.argmax(-1).tolist()]
+        rows = []
+        for _ in range(5):        # first call runs eagerly and captures, later calls replay
+            logits = engine.step([StepEntry(i, [tokens[i]], [0]) for i in range(3)])
+            rows.append(logits.cpu())
+            tokens = [int(t) for t in logits.argmax(-1).tolist()]
+        # then 6 steps in one call, sampling on the device at temperature 0.7
+        run = engine.decode([StepEntry(i, [tokens[i]]) for i in range(3)], [0.7, 0.0, 0.7], [5, 6, 7], steps=6)
+        results[graphs] = (torch.stack(rows), run, engine.runner.graph_replays)
+        assert [engine.cache.length(i) for i in range(3)] == [len(p) + 11 for p in prompts]
+    eager, graph = results[False], results[True]
+    assert graph[2] > 0 and eager[2] == 0
+    scale = float(eager[0].abs().max())
+    assert float((eager[0] - graph[0]).abs().max()) <= helpers.TOLERANCE[dtype] * scale
+    if dtype == "float32":
+        assert np.array_equal(eager[1], graph[1])
+        # the device loop follows the keyed noise of the plain sampler
+        config, weights = helpers.plain_model("b")
+        sequence = list(prompts[0])
+        engine = make_engine("b", dtype)
+        first = engine.step([StepEntry(0, prompts[0], [len(prompts[0]) - 1])])
+        token = int(first.argmax(-1).item())
+        run = engine.decode([StepEntry(0, [token])], [0.9], [42], steps=8)[:, 0].tolist()
+        sequence.append(token)
+        for drawn in run:
+            logits = plain_gpt2.forward_logits(config, weights, sequence)[-1]
+            scores = plain_gpt2.temperature_scores(logits, 0.9, 42, len(sequence))
+            assert scores[drawn] >= scores.max() - 1e-4
+            sequence.append(drawn)
