@@ -1,0 +1,285 @@
+"""Benchmark of the engine's decode step (and prefill) for GPT-2 124M layer sizes, random weights.
+
+    python bench.py --gpus 1 --steps K --warmup W            # this engine
+    python bench.py --impl reference --gpus 1 ...            # the unmodified reference, if installed
+
+A "step" is one decode step of the whole batch.  The default run: layer sizes of GPT-2 124M,
+bfloat16, batch 8, 512-token prompts of uniform-random token ids, then K decode steps.
+
+value     decoded tokens per second over K steps timed on the device (CUDA events): the captured
+          decode step replayed K times, sampling and token feedback on the device.
+e2e       the same through the Python entry point (``Scheduler.step``): every step the host builds
+          the batch, copies it from pinned memory to the device and reads the sampled tokens back.
+prefill   one step of 2,048 prompt tokens (2 prompts of 1,024).
+roofline  bytes the decode step has to read (every weight once + the cache of the live requests)
+          divided by its time, against the measured copy bandwidth.
+points    decode tokens per second at batch 1 and 64.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as handle:
+                data = json.load(handle)
+            flat = {}
+
+            def walk(node):
+                if isinstance(node, dict):
+                    for key, value in node.items():
+                        if isinstance(value, (int, float)) and key not in flat:
+                            flat[key] = float(value)
+                        else:
+                            walk(value)
+
+            walk(data)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return {"hbm_gbs": flat["hbm_gbs"], "bf16_tflops": flat["bf16_tflops"],
+                        "bf16_tflops_sustained": flat.get("bf16_tflops_sustained"), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                parts = [p.strip() for p in out.stdout.strip().splitlines()[0].split(",")]
+                self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        clocks = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        maxes = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples for i in range(4)
+                          if len(s) > 2 + i and s[2 + i].lower().startswith("active")})
+        return {"sm_mhz": int(statistics.median(clocks)) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "reasons": reasons, "samples": len(clocks)}
+
+
+def reference_arm(args):
+    """The unmodified reference from baseline/_ref, if it could be installed offline."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    reason = None
+    if not os.path.isdir(ref) or not os.listdir(ref):
+        reason = ("jainalphin/pagedserve has no setup.py/pyproject.toml: pip install --no-index --target "
+                  "baseline/_ref fails, and its GPT-2 loader needs a checkpoint download (no network)")
+    print(json.dumps({"impl": "reference", "unavailable": reason or "reference install is empty"}))
+    return 0
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=256)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--model", default="gpt2-124m")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--prompt-len", type=int, default=512)
+    parser.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
+    parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--small", action="store_true", help="profiling aid: only the default decode measurement")
+    args = parser.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 or world > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"error": "pagedserve_b200 is a single-GPU engine: bench.py runs at --gpus 1 only",
+                              "n_gpus": max(args.gpus, world)}))
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import numpy as np
+    import torch
+
+    from pagedserve_b200.config.engine_config import EngineConfig
+    from pagedserve_b200.config.gpt2 import GPT2Config, NAMED_CONFIGS
+    from pagedserve_b200.engine.batch import StepEntry
+    from pagedserve_b200.engine.engine import Engine
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    sizes = dict(NAMED_CONFIGS[args.model])
+    full_layers = sizes["n_layer"]
+    if args.layers:
+        sizes["n_layer"] = args.layers
+    config = GPT2Config(**sizes)
+    context_len = config.n_positions
+    if args.prompt_len + warmup + steps + 1 > context_len:
+        steps = context_len - args.prompt_len - warmup - 1
+    peaks = load_peaks()
+
+    max_batch = max(64, args.batch)
+    pages = max_batch * (context_len // 16) + 64
+    engine = Engine.random(config, 0, EngineConfig(dtype=args.dtype, block_size=16, num_blocks=pages,
+                                                   max_num_seqs=max_batch, max_num_batched_tokens=2048))
+    rng = np.random.default_rng(0)
+    width = 2 if args.dtype == "bfloat16" else 4
+    kv_bytes_per_token = 2 * config.n_layer * config.n_embd * width
+    tensors = engine.model.tensors
+    weight_bytes = sum(t.numel() * t.element_size() for name, t in tensors.items() if name != "wpe.weight")
+
+    def prefill(batch, prompt_len, first_id):
+        prompts = [rng.integers(0, config.vocab_size, prompt_len).tolist() for _ in range(batch)]
+        tokens = []
+        per_step = max(1, 2048 // prompt_len)
+        for start in range(0, batch, per_step):
+            chunk = range(start, min(batch, start + per_step))
+            logits = engine.step([StepEntry(first_id + i, prompts[i], [prompt_len - 1]) for i in chunk])
+            tokens += logits.argmax(-1).tolist()
+        return tokens
+
+    def measure_decode(batch, k_steps):
+        ids = list(range(batch))
+        tokens = prefill(batch, args.prompt_len, 0)
+        entries = [StepEntry(i, [tokens[i]]) for i in ids]
+        warm = engine.decode(entries, [0.0] * batch, [0] * batch, steps=warmup)
+        entries = [StepEntry(i, [int(warm[-1, i])]) for i in ids]
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches_before = engine.ops.launches
+        with ClockSampler() as clocks:
+            torch.cuda.synchronize()
+            start.record()
+            out = engine.decode(entries, [0.0] * batch, [0] * batch, steps=k_steps)
+            end.record()
+            torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        graph = engine.runner._graphs.get((batch, "sample"))
+        launches = (graph.kernels * k_steps) if graph else (engine.ops.launches - launches_before)
+        mean_context = args.prompt_len + warmup + (k_steps + 1) / 2.0
+        for i in ids:
+            engine.finish(i)
+        assert out.shape == (k_steps, batch)
+        return {"ms": ms, "tok_s": batch * k_steps / (ms / 1e3), "launches": launches,
+                "bytes_per_step": weight_bytes + batch * mean_context * kv_bytes_per_token,
+                "clocks": clocks.summary()}
+
+    def measure_e2e(batch, k_steps):
+        scheduler = engine.make_scheduler(strategy="orca", max_num_seqs=batch, max_num_batched_tokens=2048)
+        for _ in range(batch):
+            scheduler.add_token_request(rng.integers(0, config.vocab_size, args.prompt_len).tolist(),
+                                        max_new_tokens=warmup + k_steps + 2)
+        while scheduler.waiting:
+            scheduler.step()                       # prefill (untimed)
+        for _ in range(warmup):
+            scheduler.step()
+        torch.cuda.synchronize()
+        began = time.perf_counter()
+        produced = 0
+        for _ in range(k_steps):
+            produced += len(scheduler.step())
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - began
+        h2d = engine.runner.h2d_bytes
+        scheduler.run_until_complete()
+        return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": batch * 4, "ms_per_step": seconds * 1e3 / k_steps}
+
+    def measure_prefill(tokens_total=2048, repeats=5):
+        prompt_len = min(1024, context_len)
+        count = tokens_total // prompt_len
+        times = []
+        for repeat in range(repeats + 2):
+            prompts = [rng.integers(0, config.vocab_size, prompt_len).tolist() for _ in range(count)]
+            entries = [StepEntry(1000 + i, prompts[i], [prompt_len - 1]) for i in range(count)]
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.step(entries)
+            end.record()
+            torch.cuda.synchronize()
+            if repeat >= 2:
+                times.append(start.elapsed_time(end))
+            for i in range(count):
+                engine.finish(1000 + i)
+        ms = statistics.median(times)
+        T = count * prompt_len
+        H, I, L = config.n_embd, config.inner_dim, config.n_layer
+        gemm = 2.0 * T * L * (3 * H * H + H * H + 2 * H * I) + 2.0 * count * H * config.vocab_size
+        attention = L * count * 4.0 * H * (prompt_len * (prompt_len + 1) / 2.0)
+        flops = gemm + attention
+        peak = peaks["bf16_tflops"] * 1e12 if args.dtype == "bfloat16" else 75e12
+        return {"value": T / (ms / 1e3), "tokens": T, "ms": ms, "frac": flops / (ms / 1e3) / peak,
+                "gflop": flops / 1e9}
+
+    main_run = measure_decode(args.batch, steps)
+    e2e = measure_e2e(args.batch, steps)
+    result = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (GPT-2 124M)",
+        "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": main_run["ms"] / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": args.model, "weights": "random(seed 0)", "n_layer": config.n_layer,
+            "n_layer_full": full_layers, "n_embd": config.n_embd, "n_head": config.n_head,
+            "n_inner": config.inner_dim, "vocab_size": config.vocab_size, "n_positions": config.n_positions,
+            "global_batch": args.batch, "seq_len": context_len, "prompt_len": args.prompt_len,
+            "generated": steps, "block_size": 16, "parallelism": "single-gpu",
+            "tokens": "uniform-random ids", "l2": "working set per step exceeds L2 (no flush)",
+            "peaks": peaks["source"],
+        },
+        "clocks": {k: main_run["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+        "e2e": e2e,
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": main_run["bytes_per_step"] / (main_run["ms"] / steps / 1e3) / 1e9,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s"},
+    }
+    result["roofline"]["frac"] = result["roofline"]["achieved"] / result["roofline"]["peak"]
+    if not args.small and not args.skip_prefill:
+        result["prefill"] = measure_prefill()
+    if not args.small and not args.skip_points:
+        result["points"] = {"decode_b1": measure_decode(1, steps)["tok_s"],
+                            "decode_b64": measure_decode(64, steps)["tok_s"]}
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
