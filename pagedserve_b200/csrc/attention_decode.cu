@@ -205,3 +205,88 @@ PS_EXPORT int ps_paged_attention_decode(const void* q, int q_stride, void* out, 
         part_ml, counters);
     return ps::launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_decode_noalloc.h for who needs it and the rules).
+// ------------------------------------------------------------------------------------------------
+#include <stdio.h>
+
+#include "attention_decode_noalloc.h"
+
+// The scratch of the split kernel, inside the library image: counters | (max, sum) pairs | partial
+// accumulators. In host code this name is only a stand-in for the symbol; the address a kernel can
+// use comes from cudaGetSymbolAddress, looked up once per device below.
+static __device__ __align__(256) unsigned char ps_noalloc_scratch[PS_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_base[kMaxDevices] = {nullptr};
+
+int refuse(char* message, int capacity, int code, const char* format, long long a, long long b) {
+    if (message && capacity > 0) snprintf(message, (size_t)capacity, format, a, b);
+    return code;
+}
+
+// Device address of the scratch array for the current device (first call on a device looks it up).
+int noalloc_scratch(void** base, char* message, int capacity) {
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess || device < 0 || device >= kMaxDevices)
+        return refuse(message, capacity, PS_ERR_SETUP, "cannot identify the current device (cuda error %lld, device %lld)",
+                      (long long)err, (long long)device);
+    if (!g_noalloc_base[device]) {
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, ps_noalloc_scratch);
+        if (err != cudaSuccess || !ptr)
+            return refuse(message, capacity, PS_ERR_SETUP,
+                          "cudaGetSymbolAddress failed for the scratch array (cuda error %lld) on device %lld",
+                          (long long)err, (long long)device);
+        g_noalloc_base[device] = ptr;
+    }
+    *base = g_noalloc_base[device];
+    return PS_OK;
+}
+
+}  // namespace
+
+PS_EXPORT int ps_paged_attention_decode_noalloc(const void* q, int q_stride, void* out, int out_stride,
+                                                const void* k_pool, const void* v_pool, long long page_stride,
+                                                const int* token_item, const int* positions,
+                                                const int* block_table, int bt_stride, int T, int n_heads,
+                                                int n_kv_heads, int head_dim, int page_size, int window,
+                                                float scale, int split_tiles, int n_splits, void* stream,
+                                                char* message, int message_capacity) {
+    if (message && message_capacity > 0) message[0] = 0;
+    if (T <= 0) return PS_OK;
+    if (n_heads <= 0 || n_splits < 1)
+        return refuse(message, message_capacity, PS_ERR_BAD_ARGUMENT, "n_heads (%lld) and n_splits (%lld) must be positive",
+                      n_heads, n_splits);
+    const long long rows = (long long)T * n_heads;
+    const long long partials = rows * n_splits;
+    if (head_dim > PS_NOALLOC_MAX_HEAD_DIM)
+        return refuse(message, message_capacity, PS_ERR_SCRATCH_LIMIT,
+                      "head_dim %lld exceeds the fixed scratch's limit of %lld", head_dim, PS_NOALLOC_MAX_HEAD_DIM);
+    if (rows > PS_NOALLOC_MAX_ROWS)
+        return refuse(message, message_capacity, PS_ERR_SCRATCH_LIMIT,
+                      "T * n_heads = %lld exceeds the fixed scratch's limit of %lld rows", rows, PS_NOALLOC_MAX_ROWS);
+    if (partials > PS_NOALLOC_MAX_PARTIALS)
+        return refuse(message, message_capacity, PS_ERR_SCRATCH_LIMIT,
+                      "T * n_heads * n_splits = %lld exceeds the fixed scratch's limit of %lld partial states",
+                      partials, PS_NOALLOC_MAX_PARTIALS);
+    void* base = nullptr;
+    int rc = noalloc_scratch(&base, message, message_capacity);
+    if (rc != PS_OK) return rc;
+    int* counters = reinterpret_cast<int*>(base);
+    float* part_ml = reinterpret_cast<float*>(static_cast<unsigned char*>(base) + PS_NOALLOC_MAX_ROWS * 4);
+    float* part_acc = part_ml + PS_NOALLOC_MAX_PARTIALS * 2;
+    // the counters must start at zero whatever an earlier call left behind
+    if (cudaMemsetAsync(counters, 0, (size_t)rows * sizeof(int), (cudaStream_t)stream) != cudaSuccess)
+        return refuse(message, message_capacity, PS_ERR_LAUNCH, "clearing the counters failed (%lld rows, %lld)", rows, 0);
+    rc = ps_paged_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
+                                   block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window,
+                                   scale, split_tiles, n_splits, part_acc, part_ml, counters, stream);
+    if (rc != PS_OK)
+        return refuse(message, message_capacity, rc, "the attention kernel refused its arguments (status %lld, %lld)", rc, 0);
+    return PS_OK;
+}
