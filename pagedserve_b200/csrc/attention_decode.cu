@@ -2,14 +2,19 @@
 //
 // One CTA per (token, head, key split). The reference launches one program per (request, head) that
 // walks the whole context (src/kernels/triton_paged_attention.py:225-320, grid at :530): at batch 1
-// that is 12 programs for 148 SMs. Here the keys of a token are cut into splits of `split_tiles`
-// tiles of 32 keys, aligned to absolute positions; every split is a CTA of 4 warps, the warps take
-// the split's tiles in turn, and the last CTA of a (token, head) to finish merges the partial
+// that is 12 programs for 148 SMs. Here the keys of a token are cut into chunks of `chunk_keys` keys
+// aligned to absolute positions (128 keys at head size 64); a split is a whole number of chunks and
+// is one CTA of 4 warps; the last CTA of a (token, head) to finish merges the partial
 // (max, sum, acc) states in split order. With one split the output is written directly.
 //
-// Inside a tile lane j owns key j for the scores (its whole K row, 16-byte loads, no shuffles in the
-// dot product), then lanes own head dims for p.V (coalesced 4-byte loads, p broadcast by shuffle).
-// Softmax state and accumulators are float32 (reference: triton_paged_attention.py:219-223, 275-320).
+// A chunk's K and V blocks are brought into shared memory page by page with bulk asynchronous copies
+// (cp.async.bulk, completion on an mbarrier): a page's keys of one head are contiguous, so a chunk is
+// 2 * chunk_keys / page_size copies and all of them are in flight at once. Thread j then owns key j
+// for the scores (16-byte reads of its row in an order rotated by j, which keeps the reads free of
+// bank conflicts), the four warps share the keys for p.V with lanes on head dims. Softmax state and
+// accumulators are float32 (reference: triton_paged_attention.py:219-223, 275-320).
+//
+// Every wait on the mbarrier is bounded; a wait that runs out sets *status and the CTA stops waiting.
 //
 // Scratch (only when splits > 1): part_acc[T][H][S][hd] f32, part_ml[T][H][S][2] f32, counters[T*H] int32
 // (zero before the first use; the merging CTA sets its counter back to zero).
@@ -18,68 +23,133 @@
 namespace ps {
 
 constexpr int DEC_WARPS = 4;
+constexpr int DEC_THREADS = DEC_WARPS * 32;
+
+__host__ __device__ inline int attention_chunk_keys(int head_dim, int page_size) {
+    int keys = (8192 / head_dim) & ~31;
+    if (keys > DEC_THREADS) keys = DEC_THREADS;
+    if (keys < page_size) keys = page_size;
+    if (keys < 32) keys = 32;
+    return keys;
+}
 
 __device__ __forceinline__ float ldcg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
     return v;
 }
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// false if the wait ran out
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (int spin = 0; spin < (1 << 22); ++spin)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
 
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+__global__ void __launch_bounds__(DEC_THREADS)
 paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               __nv_bfloat16* __restrict__ out, int out_stride,
                               const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                               long long page_stride, const int* __restrict__ token_item,
                               const int* __restrict__ positions, const int* __restrict__ block_table,
                               int bt_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                              int window, float scale_log2, int split_tiles, int n_splits,
+                              int window, float scale_log2, int chunk_keys, int split_chunks, int n_splits,
                               float* __restrict__ part_acc, float* __restrict__ part_ml,
-                              int* __restrict__ counters) {
-    extern __shared__ float smem[];
-    float* q_s = smem;                       // [head_dim]
-    float* acc_s = smem + head_dim;          // [DEC_WARPS][head_dim]
-    __shared__ float m_s[DEC_WARPS], l_s[DEC_WARPS];
+                              int* __restrict__ counters, int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [chunk_keys][head_dim]
+    __nv_bfloat16* v_s = k_s + (size_t)chunk_keys * head_dim;                        // [chunk_keys][head_dim]
+    float* q_s = reinterpret_cast<float*>(v_s + (size_t)chunk_keys * head_dim);      // [head_dim]
+    float* p_s = q_s + head_dim;                                                     // [chunk_keys]
+    float* acc_s = p_s + chunk_keys;                                                 // [DEC_WARPS][head_dim]
+    __shared__ float red_a[DEC_WARPS], red_b[DEC_WARPS];
+    __shared__ __align__(8) uint64_t bar;
     __shared__ int last_flag;
 
+    pdl_prologue();
     const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int p = positions[t];
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int first_tile = lo >> 5, last_tile = p >> 5;
-    const int first_split = first_tile / split_tiles, last_split = last_tile / split_tiles;
+    const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
+    const int first_split = first_chunk / split_chunks, last_split = last_chunk / split_chunks;
     if (split < first_split || split > last_split) return;          // no keys here
     const int n_active = last_split - first_split + 1;
-    const int tile_lo = max(first_tile, split * split_tiles);
-    const int tile_hi = min(last_tile, (split + 1) * split_tiles - 1);
+    const int chunk_lo = max(first_chunk, split * split_chunks);
+    const int chunk_hi = min(last_chunk, (split + 1) * split_chunks - 1);
 
     const int g = h / (n_heads / n_kv_heads);
     const int* bt = block_table + (size_t)token_item[t] * bt_stride;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x)
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int d = tid; d < head_dim; d += DEC_THREADS)
         q_s[d] = __bfloat162float(q[(size_t)t * q_stride + h * head_dim + d]) * scale_log2;
     __syncthreads();
 
     float acc[4][2];
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    const int chunks = head_dim >> 3;
+    float m_run = -INFINITY, l_run = 0.f;
+    const int row_chunks = head_dim >> 3;                      // 16-byte pieces of a key row
+    const int pages_per_chunk = chunk_keys / page_size;
+    const uint32_t block_bytes = (uint32_t)page_size * head_dim * 2;
+    uint32_t phase = 0;
+    bool ok = true;
 
-    for (int tile = tile_lo + warp; tile <= tile_hi; tile += DEC_WARPS) {
-        const int kpos = (tile << 5) + lane;
-        const bool valid = kpos >= lo && kpos <= p;
-        long long row = 0;
+    for (int chunk = chunk_lo; chunk <= chunk_hi; ++chunk) {
+        const int key0 = chunk * chunk_keys;
+        // pages of this chunk that hold keys in [lo, p]
+        const int pg_first = max(lo, key0) / page_size - key0 / page_size;
+        const int pg_last = min(p, key0 + chunk_keys - 1) / page_size - key0 / page_size;
+        if (tid == 0) mbar_expect_tx(&bar, 2u * block_bytes * (uint32_t)(pg_last - pg_first + 1));
+        if (tid >= pg_first && tid <= pg_last && tid < pages_per_chunk) {
+            const int page = bt[key0 / page_size + tid];
+            const long long base = (long long)page * page_stride + (long long)g * page_size * head_dim;
+            bulk_copy_g2s(k_s + (size_t)tid * page_size * head_dim, k_pool + base, block_bytes, &bar);
+            bulk_copy_g2s(v_s + (size_t)tid * page_size * head_dim, v_pool + base, block_bytes, &bar);
+        }
+        if (ok && !mbar_wait_bounded(&bar, phase)) {
+            ok = false;
+            if (status) atomicExch(status, 2);
+        }
+        phase ^= 1;
+        // scores: thread j owns key j of the chunk
+        const int kpos = key0 + tid;
+        const bool valid = ok && tid < chunk_keys && kpos >= lo && kpos <= p;
         float s = -INFINITY;
         if (valid) {
-            int page = bt[kpos / page_size];
-            row = (long long)page * page_stride + ((long long)g * page_size + (kpos % page_size)) * head_dim;
-            const uint4* kr = reinterpret_cast<const uint4*>(k_pool + row);
+            const __nv_bfloat16* kr = k_s + (size_t)tid * head_dim;
             float dot = 0.f;
-#pragma unroll 4
-            for (int c = 0; c < chunks; ++c) {
-                uint4 kv = kr[c];
+            const int rot = tid % row_chunks;
+            for (int c = 0; c < row_chunks; ++c) {
+                int cc = c + rot;                               // (c + j) mod row_chunks
+                if (cc >= row_chunks) cc -= row_chunks;
+                const uint4 kv = *reinterpret_cast<const uint4*>(kr + 8 * cc);
                 const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
-                const float4 qa = *reinterpret_cast<const float4*>(q_s + 8 * c);
-                const float4 qb = *reinterpret_cast<const float4*>(q_s + 8 * c + 4);
+                const float4 qa = *reinterpret_cast<const float4*>(q_s + 8 * cc);
+                const float4 qb = *reinterpret_cast<const float4*>(q_s + 8 * cc + 4);
                 float2 f0 = __bfloat1622float2(k2[0]), f1 = __bfloat1622float2(k2[1]);
                 float2 f2 = __bfloat1622float2(k2[2]), f3 = __bfloat1622float2(k2[3]);
                 dot = fmaf(qa.x, f0.x, dot); dot = fmaf(qa.y, f0.y, dot);
@@ -87,34 +157,44 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 dot = fmaf(qb.x, f2.x, dot); dot = fmaf(qb.y, f2.y, dot);
                 dot = fmaf(qb.z, f3.x, dot); dot = fmaf(qb.w, f3.y, dot);
             }
-            s = dot;                                   // already in log2 units
+            s = dot;                                           // already in log2 units
         }
-        const float m_new = fmaxf(m, warp_max(s));
-        const float corr = exp2f(m - m_new);
+        float wmax = warp_max(s);
+        if (lane == 0) red_a[warp] = wmax;
+        __syncthreads();
+        float cmax = fmaxf(fmaxf(red_a[0], red_a[1]), fmaxf(red_a[2], red_a[3]));
+        const float m_new = fmaxf(m_run, cmax);
         const float pr = valid ? exp2f(s - m_new) : 0.f;
-        l = l * corr + warp_sum(pr);
+        if (tid < chunk_keys) p_s[tid] = pr;
+        float wsum = warp_sum(pr);
+        if (lane == 0) red_b[warp] = wsum;
+        __syncthreads();
+        const float csum = (red_b[0] + red_b[1]) + (red_b[2] + red_b[3]);
+        const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
+        l_run = l_run * corr + csum;
+        m_run = m_new;
 #pragma unroll
         for (int i = 0; i < 4; ++i) { acc[i][0] *= corr; acc[i][1] *= corr; }
-        m = m_new;
-        const unsigned mask = __ballot_sync(0xffffffffu, valid);
-        const int first = __ffs(mask) - 1, count = __popc(mask);      // valid keys are one contiguous run
-#pragma unroll 8
-        for (int j = first; j < first + count; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, pr, j);
-            const long long rj = __shfl_sync(0xffffffffu, row, j);
-            const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(v_pool + rj);
+        // p.V: warp w takes keys j = w (mod 4); lanes own pairs of head dims
+        const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;
+        int j = j_lo + ((warp - j_lo) & (DEC_WARPS - 1));
+        if (ok)
+            for (; j <= j_hi; j += DEC_WARPS) {
+                const float pj = p_s[j];
+                const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(v_s + (size_t)j * head_dim);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                int d2 = lane + 32 * i;                // index of the bf16 pair
-                if (2 * d2 < head_dim) {
-                    float2 v = __bfloat1622float2(vr[d2]);
-                    acc[i][0] = fmaf(pj, v.x, acc[i][0]);
-                    acc[i][1] = fmaf(pj, v.y, acc[i][1]);
+                for (int i = 0; i < 4; ++i) {
+                    int d2 = lane + 32 * i;
+                    if (2 * d2 < head_dim) {
+                        float2 v = __bfloat1622float2(vr[d2]);
+                        acc[i][0] = fmaf(pj, v.x, acc[i][0]);
+                        acc[i][1] = fmaf(pj, v.y, acc[i][1]);
+                    }
                 }
             }
-        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();                                      // the buffers may be overwritten now
     }
-    if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         int d = 2 * (lane + 32 * i);
@@ -124,38 +204,23 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     }
     __syncthreads();
-    float big = m_s[0];
-#pragma unroll
-    for (int w = 1; w < DEC_WARPS; ++w) big = fmaxf(big, m_s[w]);
-    float wgt[DEC_WARPS];
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) {
-        wgt[w] = (m_s[w] == -INFINITY) ? 0.f : exp2f(m_s[w] - big);
-        total += l_s[w] * wgt[w];
-    }
     if (n_splits == 1 || n_active == 1) {
-        const float inv = 1.f / total;
-        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-            float o = 0.f;
-#pragma unroll
-            for (int w = 0; w < DEC_WARPS; ++w) o += acc_s[w * head_dim + d] * wgt[w];
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        for (int d = tid; d < head_dim; d += DEC_THREADS) {
+            float o = (acc_s[d] + acc_s[head_dim + d]) + (acc_s[2 * head_dim + d] + acc_s[3 * head_dim + d]);
             out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
         }
         return;
     }
     // several splits hold keys of this token: publish the partial state
     const size_t slot = ((size_t)t * n_heads + h) * n_splits + split;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float o = 0.f;
-#pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) o += acc_s[w * head_dim + d] * wgt[w];
-        part_acc[slot * head_dim + d] = o;
-    }
-    if (threadIdx.x == 0) { part_ml[slot * 2] = big; part_ml[slot * 2 + 1] = total; }
+    for (int d = tid; d < head_dim; d += DEC_THREADS)
+        part_acc[slot * head_dim + d] =
+            (acc_s[d] + acc_s[head_dim + d]) + (acc_s[2 * head_dim + d] + acc_s[3 * head_dim + d]);
+    if (tid == 0) { part_ml[slot * 2] = m_run; part_ml[slot * 2 + 1] = l_run; }
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         int prev = atomicAdd(&counters[t * n_heads + h], 1);
         last_flag = (prev == n_active - 1);
         if (last_flag) counters[t * n_heads + h] = 0;
@@ -169,8 +234,8 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float L = 0.f;
     for (int sidx = first_split; sidx <= last_split; ++sidx)
         L += ldcg_f32(part_ml + (base + sidx) * 2 + 1) * exp2f(ldcg_f32(part_ml + (base + sidx) * 2) - M);
-    const float inv = 1.f / L;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d = tid; d < head_dim; d += DEC_THREADS) {
         float o = 0.f;
         for (int sidx = first_split; sidx <= last_split; ++sidx)
             o += ldcg_f32(part_acc + (base + sidx) * head_dim + d) * exp2f(ldcg_f32(part_ml + (base + sidx) * 2) - M);
@@ -180,14 +245,22 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 
 }  // namespace ps
 
-// split_tiles: tiles of 32 keys per split; n_splits: grid depth = ceil(max tiles / split_tiles).
-// With n_splits == 1 the scratch pointers may be null.
-PS_EXPORT int ps_paged_attention_decode(const void* q, int q_stride, void* out, int out_stride,
-                                        const void* k_pool, const void* v_pool, long long page_stride,
-                                        const int* token_item, const int* positions, const int* block_table,
-                                        int bt_stride, int T, int n_heads, int n_kv_heads, int head_dim,
-                                        int page_size, int window, float scale, int split_tiles, int n_splits,
-                                        float* part_acc, float* part_ml, int* counters, void* stream) {
+// Keys per chunk for a head size and page size: splits are whole numbers of chunks.
+PS_EXPORT int ps_attention_chunk_keys(int head_dim, int page_size) {
+    if (head_dim <= 0 || page_size <= 0) return 0;
+    return ps::attention_chunk_keys(head_dim, page_size);
+}
+
+// split_tiles: tiles of 32 keys per split (split_tiles * 32 must be a multiple of the chunk size);
+// n_splits: grid depth, at least ceil(longest context / split length).
+// With n_splits == 1 the scratch pointers may be null. status (may be null) is set non-zero if a
+// bounded wait ran out.
+static int launch_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                   const void* v_pool, long long page_stride, const int* token_item,
+                                   const int* positions, const int* block_table, int bt_stride, int T, int n_heads,
+                                   int n_kv_heads, int head_dim, int page_size, int window, float scale,
+                                   int split_tiles, int n_splits, float* part_acc, float* part_ml, int* counters,
+                                   int* status, void* stream) {
     if (T <= 0) return PS_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return PS_ERR_BAD_ARGUMENT;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return PS_ERR_UNSUPPORTED;
@@ -196,14 +269,50 @@ PS_EXPORT int ps_paged_attention_decode(const void* q, int q_stride, void* out, 
     if (n_splits > 1 && (!part_acc || !part_ml || !counters)) return PS_ERR_BAD_ARGUMENT;
     if (q_stride % 8 != 0 || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || page_stride % 8 != 0)
         return PS_ERR_UNSUPPORTED;
+    const int chunk_keys = ps::attention_chunk_keys(head_dim, page_size);
+    if ((split_tiles * 32) % chunk_keys != 0) return PS_ERR_BAD_ARGUMENT;
+    const int split_chunks = split_tiles * 32 / chunk_keys;
     dim3 grid(T, n_heads, n_splits);
-    size_t smem = (size_t)(1 + ps::DEC_WARPS) * head_dim * sizeof(float);
-    ps::paged_attention_decode_kernel<<<grid, ps::DEC_WARPS * 32, smem, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
-        (const __nv_bfloat16*)v_pool, page_stride, token_item, positions, block_table, bt_stride, n_heads,
-        n_kv_heads, head_dim, page_size, window, scale * 1.4426950408889634f, split_tiles, n_splits, part_acc,
-        part_ml, counters);
-    return ps::launch_status();
+    size_t smem = (size_t)chunk_keys * head_dim * 2 * 2 + (size_t)(head_dim + chunk_keys + ps::DEC_WARPS * head_dim) * 4;
+    if (smem > 48 * 1024) {
+        static bool raised = false;
+        if (!raised) {
+            if (cudaFuncSetAttribute(ps::paged_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     96 * 1024) != cudaSuccess)
+                return PS_ERR_LAUNCH;
+            raised = true;
+        }
+    }
+    return ps::launch_pdl(ps::paged_attention_decode_kernel, grid, dim3(ps::DEC_THREADS), smem, (cudaStream_t)stream,
+                          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+                          (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride, token_item,
+                          positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim, page_size, window,
+                          scale * 1.4426950408889634f, chunk_keys, split_chunks, n_splits, part_acc, part_ml,
+                          counters, status);
+}
+
+PS_EXPORT int ps_paged_attention_decode(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_pool, const void* v_pool, long long page_stride,
+                                        const int* token_item, const int* positions, const int* block_table,
+                                        int bt_stride, int T, int n_heads, int n_kv_heads, int head_dim,
+                                        int page_size, int window, float scale, int split_tiles, int n_splits,
+                                        float* part_acc, float* part_ml, int* counters, void* stream) {
+    return launch_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
+                                   block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window, scale,
+                                   split_tiles, n_splits, part_acc, part_ml, counters, nullptr, stream);
+}
+
+// The same with a device status word that a bounded wait sets when it runs out.
+PS_EXPORT int ps_paged_attention_decode_checked(const void* q, int q_stride, void* out, int out_stride,
+                                                const void* k_pool, const void* v_pool, long long page_stride,
+                                                const int* token_item, const int* positions,
+                                                const int* block_table, int bt_stride, int T, int n_heads,
+                                                int n_kv_heads, int head_dim, int page_size, int window,
+                                                float scale, int split_tiles, int n_splits, float* part_acc,
+                                                float* part_ml, int* counters, int* status, void* stream) {
+    return launch_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
+                                   block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window, scale,
+                                   split_tiles, n_splits, part_acc, part_ml, counters, status, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

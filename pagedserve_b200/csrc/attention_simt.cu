@@ -24,6 +24,7 @@ __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restric
                                  const int* __restrict__ block_table, int bt_stride,
                                  T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride,
                                  int n_kv_heads, int head_dim, int page_size) {
+    pdl_prologue();
     int t = blockIdx.x;
     int item = token_item[t];
     int p = positions[t];
@@ -54,6 +55,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     float* acc_s = smem + head_dim;                      // [ATT_WARPS][head_dim]
     __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
 
+    pdl_prologue();
     int t = blockIdx.x, h = blockIdx.y;
     int g = h / (n_heads / n_kv_heads);
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -150,16 +152,15 @@ PS_EXPORT int ps_kv_append(const void* k_src, const void* v_src, int src_stride,
     cudaStream_t s = (cudaStream_t)stream;
     int nt = n_kv_heads * head_dim >= 256 ? 256 : 128;
     if (dtype == PS_F32)
-        ps::kv_append_kernel<float><<<T, nt, 0, s>>>((const float*)k_src, (const float*)v_src, src_stride,
-            token_item, positions, block_table, bt_stride, (float*)k_pool, (float*)v_pool, page_stride,
-            n_kv_heads, head_dim, page_size);
-    else if (dtype == PS_BF16)
-        ps::kv_append_kernel<__nv_bfloat16><<<T, nt, 0, s>>>((const __nv_bfloat16*)k_src,
-            (const __nv_bfloat16*)v_src, src_stride, token_item, positions, block_table, bt_stride,
-            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride, n_kv_heads, head_dim, page_size);
-    else
-        return PS_ERR_UNSUPPORTED;
-    return ps::launch_status();
+        return ps::launch_pdl(ps::kv_append_kernel<float>, dim3(T), dim3(nt), 0, s, (const float*)k_src,
+                              (const float*)v_src, src_stride, token_item, positions, block_table, bt_stride,
+                              (float*)k_pool, (float*)v_pool, page_stride, n_kv_heads, head_dim, page_size);
+    if (dtype == PS_BF16)
+        return ps::launch_pdl(ps::kv_append_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, s,
+                              (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, src_stride, token_item,
+                              positions, block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                              page_stride, n_kv_heads, head_dim, page_size);
+    return PS_ERR_UNSUPPORTED;
 }
 
 PS_EXPORT int ps_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride,
@@ -175,16 +176,15 @@ PS_EXPORT int ps_paged_attention_simt(const void* q, int q_stride, void* out, in
     dim3 grid(T, n_heads);
     size_t smem = (size_t)(1 + ps::ATT_WARPS) * head_dim * sizeof(float);
     if (dtype == PS_F32)
-        ps::paged_attention_simt_kernel<float><<<grid, ps::ATT_WARPS * 32, smem, s>>>(
-            (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
-            page_stride, token_item, positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim,
-            page_size, window, scale);
-    else if (dtype == PS_BF16)
-        ps::paged_attention_simt_kernel<__nv_bfloat16><<<grid, ps::ATT_WARPS * 32, smem, s>>>(
-            (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
-            (const __nv_bfloat16*)v_pool, page_stride, token_item, positions, block_table, bt_stride,
-            n_heads, n_kv_heads, head_dim, page_size, window, scale);
-    else
-        return PS_ERR_UNSUPPORTED;
-    return ps::launch_status();
+        return ps::launch_pdl(ps::paged_attention_simt_kernel<float>, grid, dim3(ps::ATT_WARPS * 32), smem, s,
+                              (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool,
+                              (const float*)v_pool, page_stride, token_item, positions, block_table, bt_stride,
+                              n_heads, n_kv_heads, head_dim, page_size, window, scale);
+    if (dtype == PS_BF16)
+        return ps::launch_pdl(ps::paged_attention_simt_kernel<__nv_bfloat16>, grid, dim3(ps::ATT_WARPS * 32), smem, s,
+                              (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+                              (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride, token_item,
+                              positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim, page_size, window,
+                              scale);
+    return PS_ERR_UNSUPPORTED;
 }

@@ -13,6 +13,7 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const T* __restrict__ wte, const T* __restrict__ wpe,
                              float* __restrict__ out, int H, int V, int P, int* __restrict__ status) {
+    pdl_prologue();
     int t = blockIdx.x;
     int id = ids[t];
     int p = pos ? pos[t] : 0;
@@ -38,6 +39,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
                                  float eps, TOut* __restrict__ out, int H, int has_mean) {
     __shared__ float red[NT / 32];
     __shared__ float bcast;
+    pdl_prologue();
     int r = blockIdx.x;
     int src = rows ? rows[r] : r;
     const float* xr = x + (size_t)src * H;
@@ -123,13 +125,12 @@ PS_EXPORT int ps_embed(const int* ids, const int* pos, const void* wte, const vo
     cudaStream_t s = (cudaStream_t)stream;
     int nt = H >= 256 ? 256 : 128;
     if (dtype == PS_F32)
-        ps::embed_kernel<float><<<T, nt, 0, s>>>(ids, pos, (const float*)wte, (const float*)wpe, out, H, V, P, status);
-    else if (dtype == PS_BF16)
-        ps::embed_kernel<__nv_bfloat16><<<T, nt, 0, s>>>(ids, pos, (const __nv_bfloat16*)wte,
-                                                         (const __nv_bfloat16*)wpe, out, H, V, P, status);
-    else
-        return PS_ERR_UNSUPPORTED;
-    return ps::launch_status();
+        return ps::launch_pdl(ps::embed_kernel<float>, dim3(T), dim3(nt), 0, s, ids, pos, (const float*)wte,
+                              (const float*)wpe, out, H, V, P, status);
+    if (dtype == PS_BF16)
+        return ps::launch_pdl(ps::embed_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, s, ids, pos,
+                              (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, H, V, P, status);
+    return PS_ERR_UNSUPPORTED;
 }
 
 // out[r] = norm(x[rows ? rows[r] : r]); has_mean = 0 gives the RMS form; beta may be null.
@@ -141,11 +142,10 @@ PS_EXPORT int ps_layernorm(const float* x, const int* rows, int n_rows, int H, c
     cudaStream_t s = (cudaStream_t)stream;
     constexpr int NT = 256;
     if (out_dtype == PS_F32)
-        ps::layernorm_kernel<float, NT><<<n_rows, NT, 0, s>>>(x, rows, gamma, beta, eps, (float*)out, H, has_mean);
-    else if (out_dtype == PS_BF16)
-        ps::layernorm_kernel<__nv_bfloat16, NT><<<n_rows, NT, 0, s>>>(x, rows, gamma, beta, eps,
-                                                                      (__nv_bfloat16*)out, H, has_mean);
-    else
-        return PS_ERR_UNSUPPORTED;
-    return ps::launch_status();
+        return ps::launch_pdl(ps::layernorm_kernel<float, NT>, dim3(n_rows), dim3(NT), 0, s, x, rows, gamma, beta,
+                              eps, (float*)out, H, has_mean);
+    if (out_dtype == PS_BF16)
+        return ps::launch_pdl(ps::layernorm_kernel<__nv_bfloat16, NT>, dim3(n_rows), dim3(NT), 0, s, x, rows, gamma,
+                              beta, eps, (__nv_bfloat16*)out, H, has_mean);
+    return PS_ERR_UNSUPPORTED;
 }

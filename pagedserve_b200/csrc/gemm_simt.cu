@@ -21,6 +21,7 @@ gemm_simt_kernel(const TIn* __restrict__ A, int lda, const TIn* __restrict__ W, 
                  int M, int N, int K, int act, int accumulate) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_prologue();
     int tid = threadIdx.x;
     int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, 4x4 outputs each
@@ -76,9 +77,8 @@ template <typename TIn, typename TOut>
 int launch_gemm_simt(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo,
                      int M, int N, int K, int act, int accumulate, cudaStream_t s) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TIn, TOut><<<grid, 256, 0, s>>>((const TIn*)A, lda, (const TIn*)W, ldw, bias,
-                                                     (TOut*)out, ldo, M, N, K, act, accumulate);
-    return launch_status();
+    return launch_pdl(gemm_simt_kernel<TIn, TOut>, grid, dim3(256), 0, s, (const TIn*)A, lda, (const TIn*)W, ldw, bias,
+                      (TOut*)out, ldo, M, N, K, act, accumulate);
 }
 
 }  // namespace ps

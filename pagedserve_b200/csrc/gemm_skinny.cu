@@ -38,6 +38,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
                    int act, int accumulate) {
     extern __shared__ float red[];                 // [WARPS][16][8*MT]
     constexpr int UNROLL = 4;
+    pdl_prologue();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -124,9 +125,8 @@ int launch_skinny(const void* A, int lda, const void* W, int ldw, const float* b
             raised = true;
         }
     }
-    kernel<<<(N + 15) / 16, WARPS * 32, smem, s>>>((const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, bias,
-                                                   (TOut*)out, ldo, M, N, K, act, accumulate);
-    return launch_status();
+    return launch_pdl(kernel, dim3((N + 15) / 16), dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)A, lda,
+                      (const __nv_bfloat16*)W, ldw, bias, (TOut*)out, ldo, M, N, K, act, accumulate);
 }
 
 template <int MT, typename TOut>

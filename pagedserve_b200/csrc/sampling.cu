@@ -31,6 +31,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int V,
                               int pos_offset, int* __restrict__ out) {
     __shared__ float best_v[NT / 32];
     __shared__ int best_i[NT / 32];
+    pdl_prologue();
     int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     float temp = temperature ? temperature[r] : 0.f;
@@ -68,6 +69,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int V,
 __global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids,
                                int* __restrict__ positions, int* __restrict__ kv_len,
                                int* __restrict__ history, int* __restrict__ step_counter, int B, int max_steps) {
+    pdl_prologue();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     int step = *step_counter;
     if (i < B) {
@@ -89,9 +91,11 @@ PS_EXPORT int ps_sample(const float* logits, int ld, int R, int V, const float* 
                         void* stream) {
     if (R <= 0) return PS_OK;
     if (V <= 0 || ld < V) return PS_ERR_BAD_ARGUMENT;
-    ps::sample_kernel<256><<<R, 256, 0, (cudaStream_t)stream>>>(logits, ld, V, temperature, seed, position,
-                                                                pos_offset, out);
-    return ps::launch_status();
+    if (V >= 8192)
+        return ps::launch_pdl(ps::sample_kernel<1024>, dim3(R), dim3(1024), 0, (cudaStream_t)stream, logits, ld, V,
+                              temperature, seed, position, pos_offset, out);
+    return ps::launch_pdl(ps::sample_kernel<256>, dim3(R), dim3(256), 0, (cudaStream_t)stream, logits, ld, V,
+                          temperature, seed, position, pos_offset, out);
 }
 
 // One block: B <= 1024.
@@ -99,7 +103,6 @@ PS_EXPORT int ps_advance(const int* sampled, int* token_ids, int* positions, int
                          int* step_counter, int B, int max_steps, void* stream) {
     if (B <= 0) return PS_OK;
     if (B > 1024) return PS_ERR_UNSUPPORTED;
-    ps::advance_kernel<<<1, ((B + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(sampled, token_ids, positions, kv_len,
-                                                                            history, step_counter, B, max_steps);
-    return ps::launch_status();
+    return ps::launch_pdl(ps::advance_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, (cudaStream_t)stream, sampled,
+                          token_ids, positions, kv_len, history, step_counter, B, max_steps);
 }

@@ -208,18 +208,33 @@ class Ops:
             "paged_attention_simt")
         return out
 
+    @staticmethod
+    def attention_chunk_keys(head_dim, page_size):
+        """Keys per shared-memory chunk of the split attention kernel (mirrors the CUDA side)."""
+        keys = min(128, (8192 // head_dim) & ~31)
+        return max(keys, page_size, 32)
+
+    def attention_split_plan(self, T, n_heads, head_dim, page_size, max_kv_len, target_ctas=1184):
+        """(split_tiles, n_splits): how the keys of a token are cut over CTAs.
+
+        A split is a whole number of chunks; splits are made as short as one chunk while the grid
+        stays below ``target_ctas`` CTAs (8 per SM), so that small batches still fill the GPU."""
+        chunk = self.attention_chunk_keys(head_dim, page_size)
+        chunks = max(1, -(-int(max_kv_len) // chunk))
+        wanted = max(1, target_ctas // max(1, T * n_heads))
+        split_chunks = max(1, -(-chunks // wanted))
+        n_splits = -(-chunks // split_chunks)
+        return split_chunks * chunk // 32, n_splits
+
     def paged_attention_decode(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
                                n_heads, n_kv_heads, head_dim, page_size, window, scale, max_kv_len,
-                               target_ctas=296):
+                               target_ctas=1184, status=None):
         """Split-key attention for few query tokens (bfloat16).  ``max_kv_len`` bounds the context of
         every token in the call; it fixes the grid, so a CUDA graph passes the model's maximum."""
         T = q.shape[0]
         _require(q, "q", torch.bfloat16)
         _require(out, "out", torch.bfloat16)
-        tiles = max(1, -(-int(max_kv_len) // 32))
-        wanted = max(1, target_ctas // max(1, T * n_heads))
-        split_tiles = max(2, -(-tiles // wanted))
-        n_splits = -(-tiles // split_tiles)
+        split_tiles, n_splits = self.attention_split_plan(T, n_heads, head_dim, page_size, max_kv_len, target_ctas)
         part_acc = part_ml = counters = None
         if n_splits > 1:
             if self._counters is None or self._counters.numel() < T * n_heads:
@@ -228,12 +243,12 @@ class Ops:
             part_acc = torch.empty((T * n_heads * n_splits, head_dim), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((T * n_heads * n_splits, 2), dtype=torch.float32, device=q.device)
         self.launches += 1
-        _check(self.fast.ps_paged_attention_decode(
+        _check(self.fast.ps_paged_attention_decode_checked(
             _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(k_pool), _ptr(v_pool),
             _c_ll(page_stride), _ptr(token_item), _ptr(positions), _ptr(block_table),
             _c_int(block_table.stride(0)), _c_int(T), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
             _c_int(page_size), _c_int(window or 0), _c_float(scale), _c_int(split_tiles), _c_int(n_splits),
-            _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()), "paged_attention_decode")
+            _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(status), _stream()), "paged_attention_decode")
         return out
 
     def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):

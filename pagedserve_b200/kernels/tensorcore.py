@@ -21,4 +21,4 @@ def linear(ops, a, w, bias, out, act=None, accumulate=False):
 def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):
     return ops.paged_attention_decode(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.token_item,
                                       ctx.positions, layer.block_table, n_heads, n_kv_heads, head_dim,
-                                      layer.page_size, window, scale, ctx.max_kv_len)
+                                      layer.page_size, window, scale, ctx.max_kv_len, status=ctx.status)

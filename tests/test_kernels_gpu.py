@@ -238,11 +238,11 @@ def test_attention_simt_float32(heads, kv_heads, head_dim, page, window):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (2, 2, 48, 8), (12, 12, 64, 16),
                                                           (8, 2, 128, 32), (2, 1, 256, 64)])
 @pytest.mark.parametrize("window", [None, 70])
-@pytest.mark.parametrize("target_ctas", [1, 296, 100000])
+@pytest.mark.parametrize("target_ctas", [1, 1184, 10 ** 7])
 def test_attention_decode_bfloat16(heads, kv_heads, head_dim, page, window, target_ctas):
-    """Contexts around page and tile edges, fragmented tables, one split up to a split per 64 keys."""
+    """Contexts around page and chunk edges, fragmented tables, one split up to a split per chunk."""
     ops = ops_for(torch.bfloat16)
-    lengths = [1, 15, 16, 17, 31, 32, 33, 64, 65, 128, 512, 1024]
+    lengths = [1, 15, 16, 17, 31, 32, 33, 64, 65, 127, 128, 129, 512, 1024]
     case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=7 + head_dim)
     out = torch.empty(sum(lengths), heads * head_dim, dtype=torch.bfloat16, device=DEV)
     ops.paged_attention_decode(case.q.to(DEV), out, case.k_pool, case.v_pool, case.page_stride, case.token_item,
@@ -266,7 +266,7 @@ def test_attention_finds_a_far_key(far):
         else:
             ops.paged_attention_decode(case.q.to(DEV), out, case.k_pool, case.v_pool, case.page_stride,
                                        case.token_item, case.positions, case.table, 4, 2, 64, 16, None, 0.125,
-                                       1000, target_ctas=100000)
+                                       1000, target_ctas=10 ** 7)
         want = case.reference()
         got_row = out[999, 3 * 64:4 * 64].double().cpu()
         value_row = case.v[far, 64:128].double()

@@ -51,8 +51,8 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     ops = Ops(torch.bfloat16)
     lib = load("bf16")
     assert hasattr(lib, "ps_paged_attention_decode_noalloc")
-    shapes = [([150, 17, 70], 4, 2, 64, 16, 2, 3),           # (lengths, heads, kv, hd, page, split_tiles, n_splits)
-              ([1, 33, 120], 6, 6, 48, 8, 2, 2)]
+    shapes = [([200, 17, 70], 4, 2, 64, 16, 4, 2),           # (lengths, heads, kv, hd, page, split_tiles, n_splits)
+              ([1, 33, 250], 3, 3, 48, 8, 4, 2)]                 # a split is a whole number of 128-key chunks
     for call, (lengths, heads, kv_heads, head_dim, page, split_tiles, n_splits) in enumerate(shapes):
         case = _case(ops, lengths, heads, kv_heads, head_dim, page, seed=90 + call)
         total = sum(lengths)
@@ -94,10 +94,10 @@ def test_no_alloc_entry_point_refuses_sizes_beyond_its_scratch():
     lib = load("bf16")
     case = _case(ops, [700], 8, 8, 64, 16, seed=3)              # 700 tokens x 8 heads = 5600 rows > 4096
     out = torch.zeros(700, 8 * 64, dtype=torch.bfloat16, device=DEV)
-    rc, message = _call_noalloc(lib, case, out, 2, 1, 0.125)
+    rc, message = _call_noalloc(lib, case, out, 4, 1, 0.125)
     assert rc == 4 and "exceeds the fixed scratch's limit" in message
     assert float(out.abs().max()) == 0.0                         # nothing ran
     small = _case(ops, [100], 8, 8, 64, 16, seed=4)              # 800 rows x 8 splits = 6400 partial states
     out = torch.zeros(100, 8 * 64, dtype=torch.bfloat16, device=DEV)
-    rc, message = _call_noalloc(lib, small, out, 1, 8, 0.125)
+    rc, message = _call_noalloc(lib, small, out, 4, 8, 0.125)
     assert rc == 4 and "partial states" in message
