@@ -1,0 +1,379 @@
+// Tensor-core GEMM for sm_100a: out[M,N] = epilogue(A[M,K] W[N,K]^T + bias), bfloat16 in, float32 accumulate.
+//
+//   TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast)  ->  shared memory ring of STAGES k-blocks
+//   tcgen05.mma.cta_group::1.kind::f16 (M=128, N=BN, K=16), issued by one thread, accumulating in TMEM
+//   tcgen05.ld 32x32b -> registers -> bias / GELU / residual-accumulate epilogue -> global memory
+//
+// The kernel is persistent: one CTA per SM walks the output tiles (n fastest, so neighbouring CTAs share
+// the same rows of A in L2). TMEM holds two accumulators of BN columns; while the four epilogue warps
+// drain one, the MMA warp fills the other.
+//   warp 0: TMA producer (one lane)          warp 1: TMEM allocation + MMA issue (one lane)
+//   warps 2..5: epilogue, warp w owns TMEM lanes 32*(w%4) .. +31 (= rows of the tile)
+// A k-block is 64 bf16 = one 128-byte swizzle row; the K loop of an output element runs in one fixed
+// order whatever M is, so a row's result does not depend on the rows beside it.
+// Every mbarrier wait is bounded: when one runs out the CTA sets *status, stops, frees its TMEM and returns.
+//
+// Replaces the cuBLAS nn.Linear calls of the reference (src/model/paged_decoder.py:49-50, 178-179, 295-299)
+// with their bias add, GELU (:273-280) and residual add (:184, :188) fused into the epilogue.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace ps {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // bf16 elements per k-block = 128 bytes
+constexpr int THREADS = 192;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr uint64_t WAIT_LIMIT_NS = 200ull * 1000 * 1000;      // 0.2 s: far beyond any legitimate wait here
+// false: the wait ran out, or another role of this CTA gave up (abort flag set)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    while (true) {
+#pragma unroll 1
+        for (int spin = 0; spin < 64; ++spin)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - start > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t desc = (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    desc |= (uint64_t)1 << 16;                     // leading byte offset (unused with swizzle), 16-byte units
+    desc |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset between 8-row groups
+    desc |= (uint64_t)1 << 46;                     // descriptor version of sm_100
+    desc |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+    return desc;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <int BN> struct Config {
+    static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+template <int BN, typename TOut>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K, int act,
+               int accumulate, int* __restrict__ status) {
+    using Cfg = Config<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full = bars;                     // [STAGES]  TMA -> MMA
+    uint64_t* empty = bars + STAGES;           // [STAGES]  MMA -> TMA
+    uint64_t* acc_full = bars + 2 * STAGES;    // [2]       MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;        // [2]       epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    pdl_prologue();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; atomicExch(status, 11); break; }
+                    unsigned char* a_dst = tiles + (size_t)s * Cfg::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
+                    tma_load_2d(a_dst + BM * BK * 2, &map_w, kb * BK, n0, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = bf16, both K-major, N = BN, M = 128
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) { ok = false; atomicExch(status, 12); break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; atomicExch(status, 13); break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
+                    const uint64_t desc_a = umma_desc(a_addr), desc_b = umma_desc(a_addr + BM * BK * 2);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)      // 16 bf16 = 32 bytes = 2 units of the address field
+                        umma_bf16(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(&empty[s]);                 // stage free once these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[buf]);        // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue: warps 2..5
+        const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int buf = local & 1;
+            if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) { ok = false; if (lane == 0) atomicExch(status, 14); break; }
+            tc_fence_after();
+            const int m = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+            TOut* orow = out + (size_t)m * ldo;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (c + 32 >= BN) {                          // accumulator is in registers: hand TMEM back
+                    tc_fence_before();
+                    mbar_arrive(&acc_empty[buf]);
+                }
+                const int n = n0 + c;
+                if (m < M && n < N) {
+                    const bool full_chunk = n + 32 <= N;
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(r[j]);
+                        if (bias && (full_chunk || n + j < N)) x += bias[n + j];
+                        v[j] = apply_act(x, act);
+                    }
+                    if constexpr (sizeof(TOut) == 2) {
+                        if (full_chunk && ((((uintptr_t)(orow + n)) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 pack;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                pack.x = *reinterpret_cast<uint32_t*>(&p0);
+                                pack.y = *reinterpret_cast<uint32_t*>(&p1);
+                                pack.z = *reinterpret_cast<uint32_t*>(&p2);
+                                pack.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(orow + n + j) = pack;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && n + j < N; ++j) orow[n + j] = from_float<TOut>(v[j]);
+                        }
+                    } else {
+                        if (full_chunk && ((((uintptr_t)(orow + n)) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4* dst = reinterpret_cast<float4*>(orow + n + j);
+                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                if (accumulate) {
+                                    float4 old = *dst;
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *dst = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && n + j < N; ++j) {
+                                float x = v[j];
+                                if (accumulate) x += to_float(orow[n + j]);
+                                orow[n + j] = from_float<TOut>(x);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// A row-major [rows, K] bf16 matrix with leading dimension ld; boxes of box_rows x 64 elements, 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int sm_count() {
+    static int count = 0;
+    if (!count) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+        if (count <= 0) count = 1;
+    }
+    return count;
+}
+
+template <int BN, typename TOut>
+int launch(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
+           int act, int accumulate, int* status, cudaStream_t stream) {
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_w, W, N, K, ldw, BN)) return PS_ERR_LAUNCH;
+    auto kernel = gemm_tc_kernel<BN, TOut>;
+    static bool raised = false;
+    if (!raised) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Config<BN>::SMEM) !=
+            cudaSuccess)
+            return PS_ERR_LAUNCH;
+        raised = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    return launch_pdl(kernel, dim3(grid), dim3(THREADS), Config<BN>::SMEM, stream, map_a, map_w, bias, (TOut*)out, ldo,
+                      M, N, K, act, accumulate, status);
+}
+
+template <typename TOut>
+int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
+         int act, int accumulate, int* status, int bn, cudaStream_t stream) {
+    if (bn == 0) {
+        const int tiles_m = (M + BM - 1) / BM;
+        // widest tile that still gives the SMs enough tiles (measured on B200: 128 wide wins until the
+        // grid falls below half the SMs; 256 wide needs two full waves)
+        if (tiles_m * ((N + 255) / 256) >= 2 * sm_count()) bn = 256;
+        else if (2 * tiles_m * ((N + 127) / 128) >= sm_count()) bn = 128;
+        else bn = 64;
+    }
+    if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    return PS_ERR_BAD_ARGUMENT;
+}
+
+}  // namespace tc
+}  // namespace ps
+
+// status: device int32 that a bounded wait sets when it runs out (must not be null).
+// bn: 0 = choose, else 64, 128 or 256 (the N extent of the MMA tile).
+PS_EXPORT int ps_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
+                         int N, int K, int out_dtype, int act, int accumulate, int* status, int bn, void* stream) {
+    if (M <= 0 || N <= 0) return PS_OK;
+    if (!status) return PS_ERR_BAD_ARGUMENT;
+    // TMA: 16-byte aligned base, row stride a multiple of 16 bytes
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K || ldo < N)
+        return PS_ERR_UNSUPPORTED;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return PS_ERR_UNSUPPORTED;
+    if (accumulate && out_dtype != PS_F32) return PS_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == PS_F32)
+        return ps::tc::pick<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, s);
+    if (out_dtype == PS_BF16)
+        return ps::tc::pick<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, s);
+    return PS_ERR_UNSUPPORTED;
+}

@@ -96,11 +96,16 @@ class StepContext:
     entry a token belongs to), ``item_slot[I]``, ``q_start[I+1]`` (first token of each entry),
     ``kv_len[I]`` (the request's length after this step), ``logit_rows[R]`` (flat token index of
     each wanted place), ``block_tables[g]`` (``[I, max pages]`` per cache group; -1 = no page).
+    Items are laid out short entries first (``num_short_items`` items, ``num_short_tokens`` tokens), then
+    the prompt portions of ``LONG_ENTRY`` or more tokens; ``logit_rows`` keeps the caller's order.
     ``status`` is a device int32 that kernels set non-zero on bad input (checked after the step).
     """
 
+    LONG_ENTRY = 16          # entries of at least this many tokens count as prompt portions
+
     def __init__(self, layout: BatchLayout, device_buffer: torch.Tensor, host: HostBatch, cache, status,
-                 max_q_len: int, max_kv_len: int):
+                 max_q_len: int, max_kv_len: int, num_short_items: int = None, num_short_tokens: int = None,
+                 num_long_blocks: int = 0):
         self.layout = layout
         self.host = host
         self.cache = cache
@@ -110,6 +115,10 @@ class StepContext:
         self.num_logit_rows = layout.num_rows
         self.max_q_len = max_q_len
         self.max_kv_len = max_kv_len
+        # short entries come first in the flat batch; long ones (prompt portions) after them
+        self.num_short_items = layout.num_items if num_short_items is None else num_short_items
+        self.num_short_tokens = layout.num_tokens if num_short_tokens is None else num_short_tokens
+        self.num_long_blocks = num_long_blocks      # 64-query blocks of the long entries
         T, I, R = layout.num_tokens, layout.num_items, layout.num_rows
         buf = device_buffer
         self.token_ids = buf[layout.token_ids:layout.token_ids + T]

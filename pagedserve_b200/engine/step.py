@@ -141,11 +141,20 @@ class ModelRunner:
         q_start = host[layout.q_start:layout.q_start + I + 1]
         kv_len = host[layout.kv_len:layout.kv_len + I]
         logit_rows = host[layout.logit_rows:layout.logit_rows + R]
+        # layout order: short entries (decode tokens, short portions) first, prompt portions after them
+        long_entry = StepContext.LONG_ENTRY
+        order = [i for i, e in enumerate(entries) if len(e.tokens) < long_entry] + \
+                [i for i, e in enumerate(entries) if len(e.tokens) >= long_entry]
+        num_short_items = sum(1 for e in entries if len(e.tokens) < long_entry)
         cursor = 0
-        row = 0
         max_q = 0
         max_kv = 0
-        for index, entry in enumerate(entries):
+        num_short_tokens = 0
+        num_long_blocks = 0
+        starts = [0] * I
+        laid_out = []
+        for index, source in enumerate(order):
+            entry = entries[source]
             count = len(entry.tokens)
             start = cache.length(entry.request)
             token_ids[cursor:cursor + count] = entry.tokens
@@ -154,22 +163,30 @@ class ModelRunner:
             item_slot[index] = cache.slot_of[entry.request]
             q_start[index] = cursor
             kv_len[index] = start + count
-            for place in entry.want:
-                logit_rows[row] = cursor + place
-                row += 1
+            starts[source] = cursor
+            laid_out.append(entry)
             max_q = max(max_q, count)
             max_kv = max(max_kv, start + count)
             cursor += count
+            if index < num_short_items:
+                num_short_tokens = cursor
+            else:
+                num_long_blocks += -(-count // 64)
         q_start[I] = cursor
+        row = 0
+        for source, entry in enumerate(entries):          # logits rows keep the caller's order
+            for place in entry.want:
+                logit_rows[row] = starts[source] + place
+                row += 1
         if sampling is not None:
             temperatures, seeds = sampling
             host[layout.temperature:layout.temperature + I].view(np.float32)[:] = np.asarray(
-                temperatures, dtype=np.float32)
+                [temperatures[source] for source in order], dtype=np.float32)
             host[layout.seed:layout.seed + 2 * I].view(np.uint64)[:] = np.asarray(
-                [int(seed) & 0xFFFFFFFFFFFFFFFF for seed in seeds], dtype=np.uint64)
+                [int(seeds[source]) & 0xFFFFFFFFFFFFFFFF for source in order], dtype=np.uint64)
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
             table = host[offset:offset + I * width].reshape(I, width)
-            for index, entry in enumerate(entries):
+            for index, entry in enumerate(laid_out):
                 cache.table_row(group_index, entry.request, table[index])
 
         self._device_buffer[:layout.total].copy_(staging[:layout.total], non_blocking=True)
@@ -178,9 +195,10 @@ class ModelRunner:
         self._staging_events[turn] = event
         host_batch = HostBatch(token_ids.copy(), positions.copy(), token_item.copy(), item_slot.copy(),
                                q_start.copy(), kv_len.copy(), logit_rows.copy(),
-                               [entry.request for entry in entries])
+                               [entry.request for entry in laid_out])
         self.h2d_bytes = layout.total * 4
-        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, max_q, max_kv)
+        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, max_q, max_kv,
+                           num_short_items, num_short_tokens, num_long_blocks)
 
     def _abandon(self, entries) -> None:
         for entry in entries:

@@ -33,7 +33,8 @@ NVCC_FLAGS = [
 # library name -> sources (relative to csrc/)
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["embed_norm.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu"],
-    "bf16": ["gemm_skinny.cu", "attention_decode.cu"],
+    "bf16": ["gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu"],
+    "tc": ["gemm_tc.cu"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

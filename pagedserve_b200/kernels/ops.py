@@ -67,6 +67,8 @@ class Ops:
         self.code = _DTYPE_CODE[dtype]
         self.core = _load_library("core")
         self.fast = _load_library("bf16") if dtype == torch.bfloat16 else None
+        self._tc = None              # tcgen05 library, loaded when a product first needs it
+        self._tc_status = None
         self._counters = None        # zeroed int32 scratch of the split attention kernel
         self.launches = 0            # count of kernel launches issued through this object
 
@@ -160,6 +162,38 @@ class Ops:
                                         _c_int(1 if accumulate else 0), _stream()), "gemm_skinny")
         return out
 
+    def linear_tc(self, a, w, bias, out, act=None, accumulate=False, status=None, bn=0):
+        """tcgen05 / TMA / TMEM product (bfloat16 operands, float32 accumulation); any M."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError("linear_tc: shapes do not match")
+        _require(a, "a", torch.bfloat16)
+        _require(w, "w", torch.bfloat16)
+        _require(out, "out")
+        if bias is not None:
+            _require(bias, "bias", torch.float32)
+        if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("linear_tc: innermost stride must be 1")
+        if self._tc is None:
+            self._tc = _load_library("tc")
+        if status is None:
+            if self._tc_status is None:
+                self._tc_status = torch.zeros(1, dtype=torch.int32, device=a.device)
+            status = self._tc_status
+        self.launches += 1
+        _check(self._tc.ps_gemm_tc(_ptr(a), _c_int(a.stride(0)), _ptr(w), _c_int(w.stride(0)), _ptr(bias), _ptr(out),
+                                   _c_int(out.stride(0)), _c_int(M), _c_int(N), _c_int(K),
+                                   _c_int(dtype_code(out.dtype)), _c_int(_ACT_CODE[act]),
+                                   _c_int(1 if accumulate else 0), _ptr(status), _c_int(bn), _stream()), "gemm_tc")
+        return out
+
+    @staticmethod
+    def tc_ok(a, w):
+        K = a.shape[1]
+        return (K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
     @staticmethod
     def skinny_ok(a, w):
         K = a.shape[1]
@@ -249,6 +283,24 @@ class Ops:
             _c_int(block_table.stride(0)), _c_int(T), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
             _c_int(page_size), _c_int(window or 0), _c_float(scale), _c_int(split_tiles), _c_int(n_splits),
             _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(status), _stream()), "paged_attention_decode")
+        return out
+
+    def prefill_attention(self, q, out, k_pool, v_pool, page_stride, q_start, kv_len, block_table, first_item,
+                          n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale):
+        """Tensor-core causal attention of prompt portions (bfloat16): items ``first_item ..`` of the step,
+        ``max_blocks`` >= the number of 64-query blocks they make up.  ``q`` / ``out`` are the step's flat
+        token arrays (row 0 = token 0)."""
+        _require(q, "q", torch.bfloat16)
+        _require(out, "out", torch.bfloat16)
+        if head_dim > 128:
+            raise KernelError("prefill_attention: head sizes above 128 are not supported")
+        self.launches += 1
+        _check(self.fast.ps_prefill_attention(
+            _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(k_pool), _ptr(v_pool),
+            _c_ll(page_stride), _ptr(q_start), _ptr(kv_len), _ptr(block_table), _c_int(block_table.stride(0)),
+            _c_int(first_item), _c_int(n_items), _c_int(max_blocks), _c_int(n_heads), _c_int(n_kv_heads),
+            _c_int(head_dim), _c_int(page_size), _c_int(window or 0), _c_float(scale), _stream()),
+            "prefill_attention")
         return out
 
     def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):

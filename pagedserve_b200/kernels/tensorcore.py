@@ -2,8 +2,8 @@
 
 ``linear``    out = act(a @ w.T + bias) with bfloat16 operands and float32 accumulation:
               at most 64 rows -> the weight-streaming kernel (csrc/gemm_skinny.cu);
-              more rows       -> the tcgen05 kernel (csrc/gemm_tc.cu) when it takes the shape,
-                                 else the CUDA-core kernel.
+              more rows       -> the tcgen05 / TMA / TMEM kernel (csrc/gemm_tc.cu);
+              shapes neither takes (K not a multiple of 8, unaligned rows) -> the CUDA-core kernel.
 ``attention`` causal attention over the paged cache for bfloat16 queries.
 """
 
@@ -12,13 +12,29 @@ from __future__ import annotations
 import torch
 
 
-def linear(ops, a, w, bias, out, act=None, accumulate=False):
+def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
     if ops.skinny_ok(a, w):
         return ops.linear_skinny(a, w, bias, out, act, accumulate)
+    if ops.tc_ok(a, w):
+        return ops.linear_tc(a, w, bias, out, act, accumulate, status=status)
     return ops.linear_simt(a, w, bias, out, act, accumulate)
 
 
 def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):
-    return ops.paged_attention_decode(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.token_item,
-                                      ctx.positions, layer.block_table, n_heads, n_kv_heads, head_dim,
-                                      layer.page_size, window, scale, ctx.max_kv_len, status=ctx.status)
+    """Short entries (fewer than ``ctx.LONG_ENTRY`` tokens: decode tokens, short portions) come first in the
+    step's flat batch and go token by token through the split-key kernel; long portions go through the
+    tensor-core prefill kernel in blocks of 64 queries."""
+    short_tokens = ctx.num_short_tokens
+    long_items = ctx.num_items - ctx.num_short_items
+    if long_items and head_dim > 128:
+        short_tokens, long_items = ctx.num_tokens, 0
+    if short_tokens:
+        ops.paged_attention_decode(q[:short_tokens], out[:short_tokens], layer.k_pool, layer.v_pool,
+                                   layer.page_stride, ctx.token_item[:short_tokens], ctx.positions[:short_tokens],
+                                   layer.block_table, n_heads, n_kv_heads, head_dim, layer.page_size, window, scale,
+                                   ctx.max_kv_len, status=ctx.status)
+    if long_items:
+        ops.prefill_attention(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.q_start, ctx.kv_len,
+                              layer.block_table, ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads,
+                              n_kv_heads, head_dim, layer.page_size, window, scale)
+    return out

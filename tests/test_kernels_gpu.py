@@ -129,6 +129,40 @@ def test_gemm_skinny(M, N, K):
     assert rel_err(fast, simt) < 1e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(65, 64, 64), (128, 256, 64), (130, 1003, 96), (300, 320, 328),
+                                   (1024, 2304, 768), (257, 770, 3072), (2048, 96, 1600)])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_gemm_tcgen05(M, N, K, bn):
+    """The tcgen05/TMA/TMEM product against the CUDA-core product on the same bfloat16 inputs (both
+    accumulate in float32) and against float64: tails in M, N and K, every tile width, all epilogues."""
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(M + N + K + bn)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for act, out_dtype, tol in ((None, torch.float32, 2e-5), ("gelu_tanh", torch.bfloat16, 6e-3),
+                                ("gelu_erf", torch.float32, 2e-5)):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        ops.linear_tc(a.to(DEV), w.to(DEV), bias.to(DEV), out, act=act, status=status, bn=bn)
+        assert rel_err(out, gemm_reference(a, w, bias, act, None)) < tol, (act, out_dtype)
+    base = torch.randn(M, N, generator=g)
+    stream = base.clone().to(DEV)
+    ops.linear_tc(a.to(DEV), w.to(DEV), None, stream, accumulate=True, status=status, bn=bn)
+    assert rel_err(stream, gemm_reference(a, w, None, None, base)) < 2e-5
+    simt = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    fast = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_simt(a.to(DEV), w.to(DEV), None, simt)
+    ops.linear_tc(a.to(DEV), w.to(DEV), None, fast, status=status, bn=bn)
+    assert rel_err(fast, simt) < 1e-5
+    # a row's result does not depend on the rows beside it
+    rows = min(70, M)
+    part = torch.empty(rows, N, dtype=torch.float32, device=DEV)
+    ops.linear_tc(a[M - rows:].to(DEV), w.to(DEV), None, part, status=status, bn=bn)
+    assert torch.equal(part, fast[M - rows:])
+    assert int(status.item()) == 0
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take():
     from pagedserve_b200.kernels.ops import KernelError
 
@@ -253,6 +287,42 @@ def test_attention_decode_bfloat16(heads, kv_heads, head_dim, page, window, targ
     assert int(ops._counters.abs().sum()) == 0 if ops._counters is not None else True
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (2, 2, 48, 8), (12, 12, 64, 16),
+                                                          (8, 2, 128, 32), (3, 1, 96, 64), (2, 2, 80, 4)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_prefill_attention_bfloat16(heads, kv_heads, head_dim, page, window):
+    """Whole prompts and portions that continue a cached prompt, lengths around the 64-row and 64-key
+    block edges, fragmented tables; items before ``first_item`` are left alone."""
+    ops = ops_for(torch.bfloat16)
+    lengths = [40, 16, 63, 64, 65, 127, 128, 129, 200, 1000]
+    case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=3 + head_dim)
+    reference = case.reference(window)
+    # how many of each sequence's last tokens form the portion of this step (the rest is "cached")
+    portions = [40, 16, 63, 17, 65, 64, 128, 100, 37, 1000]
+    rows, q_start, kv_len, flat_ref = [], [0], [], []
+    begin = 0
+    for length, portion in zip(lengths, portions):
+        index = torch.arange(begin + length - portion, begin + length)
+        rows.append(index)
+        q_start.append(q_start[-1] + portion)
+        kv_len.append(length)
+        begin += length
+    rows = torch.cat(rows)
+    q = case.q[rows].to(DEV)
+    out = torch.full((rows.numel(), heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    first_item = 1                                             # item 0 belongs to "another kernel"
+    blocks = sum(-(-p // 64) for p in portions[first_item:])
+    ops.prefill_attention(q, out, case.k_pool, case.v_pool, case.page_stride,
+                          torch.tensor(q_start, dtype=torch.int32, device=DEV),
+                          torch.tensor(kv_len, dtype=torch.int32, device=DEV), case.table, first_item,
+                          len(lengths) - first_item, blocks + 3, heads, kv_heads, head_dim, page, window,
+                          head_dim ** -0.5)
+    assert torch.isnan(out[:portions[0]].float()).all()        # untouched
+    got = out[portions[0]:]
+    assert torch.isfinite(got.float()).all()
+    assert rel_err(got, reference[rows[portions[0]:]]) < 8e-3
+
+
 @pytest.mark.parametrize("far", [0, 31, 32, 255, 256, 600])
 def test_attention_finds_a_far_key(far):
     """One key among a thousand carries almost all the weight: the output must be its value."""
@@ -268,6 +338,14 @@ def test_attention_finds_a_far_key(far):
                                        case.token_item, case.positions, case.table, 4, 2, 64, 16, None, 0.125,
                                        1000, target_ctas=10 ** 7)
         want = case.reference()
+        if dtype == torch.bfloat16:
+            tensor_core = torch.empty_like(out)
+            ops.prefill_attention(case.q.to(DEV), tensor_core, case.k_pool, case.v_pool, case.page_stride,
+                                  torch.tensor([0, 1000, 1040], dtype=torch.int32, device=DEV),
+                                  torch.tensor([1000, 40], dtype=torch.int32, device=DEV), case.table, 0, 2, 17,
+                                  4, 2, 64, 16, None, 0.125)
+            assert float((tensor_core[999, 192:256].double().cpu() - case.v[far, 64:128].double()).abs().max()) < 0.05
+            assert rel_err(tensor_core, want) < tol
         got_row = out[999, 3 * 64:4 * 64].double().cpu()
         value_row = case.v[far, 64:128].double()
         assert float((got_row - value_row).abs().max()) < 0.05          # the spike's value came through
