@@ -61,7 +61,7 @@ class ModelRunner:
                                min(max_step_tokens, 4 * cache.max_slots), self.table_widths).total)
         self.steps = 0
         self.tokens_run = 0
-        self.enable_cuda_graphs = enable_cuda_graphs
+        self.enable_cuda_graphs = enable_cuda_graphs and model.graph_safe
         self.ops = model.env.ops
         self._graphs = {}                 # (batch size, kind) -> _DecodeGraph
         self.graph_replays = 0

@@ -303,10 +303,12 @@ class Ops:
             "prefill_attention")
         return out
 
-    def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):
+    def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale,
+                  write_cache=True):
         """Write the step's keys and values into the pages, then attend from the pages."""
-        self.kv_append(k, v, ctx.token_item, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
-                       layer.page_stride, n_kv_heads, head_dim, layer.page_size)
+        if write_cache:
+            self.kv_append(k, v, ctx.token_item, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
+                           layer.page_stride, n_kv_heads, head_dim, layer.page_size)
         if self.dtype == torch.float32:
             return self.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride,
                                              ctx.token_item, ctx.positions, layer.block_table, n_heads,

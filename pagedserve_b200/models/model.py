@@ -52,6 +52,11 @@ class Model:
         yield self.final_norm
         yield self.head
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode-only step of this model may be captured as a CUDA graph."""
+        return all(part.graph_safe for part in self.parts())
+
     def param_plan(self) -> List[Tuple[ParamSpec, tuple]]:
         plan = []
         for part in self.parts():
@@ -81,11 +86,23 @@ class Model:
         return sum(seen.values())
 
     # ------------------------------------------------------------------ cache needs
+    def _needs(self, which: str) -> list:
+        """Per cache layer, what the mixer of the run(s) that use it asks for."""
+        needs = [None] * self.spec.num_cache_layers
+        seen = [False] * self.spec.num_cache_layers
+        for entry in self.spec.schedule:
+            need = getattr(self.blocks[entry.layer].mixer, which)()
+            if seen[entry.cache_layer] and needs[entry.cache_layer] != need:
+                raise ValueError(f"cache layer {entry.cache_layer} is shared by runs with different needs")
+            needs[entry.cache_layer] = need
+            seen[entry.cache_layer] = True
+        return needs
+
     def kv_needs(self) -> List[Optional[KVNeed]]:
-        return [block.mixer.cache_need() for block in self.blocks]
+        return self._needs("cache_need")
 
     def state_needs(self) -> List[Optional[StateNeed]]:
-        return [block.mixer.state_need() for block in self.blocks]
+        return self._needs("state_need")
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx) -> torch.Tensor:

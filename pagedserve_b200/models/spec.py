@@ -31,7 +31,9 @@ class LayerSpec:
 @dataclass
 class ScheduleEntry:
     layer: int                      # which layer's parameters run
-    cache_layer: int                # whose cache (pages / slot state) it reads and writes
+    cache_layer: int                # which cache layer (pages / slot state) this run reads and writes;
+                                    # cache layers are their own index space: a layer that runs twice
+                                    # takes two, two runs that name the same one share it
 
 
 @dataclass
@@ -55,5 +57,9 @@ class ModelSpec:
         if not self.schedule:
             self.schedule = [ScheduleEntry(i, i) for i in range(len(self.layers))]
         for entry in self.schedule:
-            if not (0 <= entry.layer < len(self.layers)) or not (0 <= entry.cache_layer < len(self.layers)):
+            if not (0 <= entry.layer < len(self.layers)) or entry.cache_layer < 0:
                 raise ValueError("schedule names a layer that does not exist")
+
+    @property
+    def num_cache_layers(self) -> int:
+        return max(entry.cache_layer for entry in self.schedule) + 1

@@ -25,8 +25,11 @@ class CausalSelfAttention(Mixer):
 
     params: hidden_size, n_heads, n_kv_heads, head_dim, scale, window (None = all keys),
     has_bias, stored_in_out (True: matrices stored [in, out]), qkv_name, out_name,
-    init_std, out_init_std.
+    init_std, out_init_std, write_cache (False: this run only reads a cache layer that another
+    run of the schedule has written in the same step).
     """
+
+    graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -79,5 +82,5 @@ class CausalSelfAttention(Mixer):
         layer.positions.rotate(q, k, ctx)
         context = torch.empty((tokens, self.q_width), dtype=self.env.dtype, device=x.device)
         ops.attention(q, k, v, context, ctx, layer, p["n_heads"], p["n_kv_heads"], p["head_dim"],
-                      p.get("window"), float(p["scale"]))
+                      p.get("window"), float(p["scale"]), write_cache=p.get("write_cache", True))
         ops.linear(context, self.w_out, self.b_out, residual, accumulate=True)

@@ -59,6 +59,11 @@ class LayerContext:
 
 class Part:
     category = ""
+    # True when ``forward`` only launches work whose shapes and addresses depend on the batch size alone
+    # and reads the batch from ``ctx``'s device arrays: such a step can be captured once as a CUDA graph
+    # and replayed. A part that branches on host data (``ctx.host``) leaves this False, and a model
+    # with such a part runs every step eagerly.
+    graph_safe = False
 
     def __init__(self, params: dict, prefix: str, env: PartEnv):
         self.params = dict(params)

@@ -12,6 +12,8 @@ class PreNormBlock(Block):
     is float32 and is updated in place; the adds happen in the epilogues of the
     mixer's and the feed-forward's last matrix products."""
 
+    graph_safe = True
+
     required_norms = ("pre_mixer", "pre_feed_forward")
 
     def forward(self, hidden, ctx, layer):

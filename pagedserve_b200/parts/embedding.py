@@ -15,6 +15,8 @@ class TokenEmbedding(Embedding):
     reference: src/model/paged_decoder.py:288, 306-314.  The result is float32:
     it starts the residual stream.  params: vocab_size, hidden_size, name, init_std."""
 
+    graph_safe = True
+
     def param_specs(self):
         p = self.params
         return [(ParamSpec(self._n(p["name"] + ".weight"), (p["vocab_size"], p["hidden_size"]), "table"),
@@ -38,6 +40,8 @@ class LMHead(Head):
     """logits = x table^T in float32, no bias; ``tied`` uses the token embedding's table
     (reference: src/model/paged_decoder.py:295-301; src/model/gpt2.py:42-43, 77-78).
     params: vocab_size, hidden_size, tied, name, init_std."""
+
+    graph_safe = True
 
     def param_specs(self):
         p = self.params

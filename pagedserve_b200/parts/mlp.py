@@ -17,6 +17,8 @@ class DenseMLP(FeedForward):
     params: hidden_size, inner_size, activation ('gelu_tanh' | 'gelu_erf'), has_bias,
     stored_in_out, up_name, down_name, init_std, out_init_std."""
 
+    graph_safe = True
+
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         if self.params["activation"] not in ACTIVATIONS:

@@ -17,6 +17,8 @@ class LayerNorm(Norm):
     params: width, eps, name, has_mean (False gives the RMS form), has_bias, init_std.
     """
 
+    graph_safe = True
+
     def param_specs(self):
         p = self.params
         specs = [(ParamSpec(self._n(p["name"] + ".weight"), (p["width"],), "vector"),

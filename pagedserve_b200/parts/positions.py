@@ -12,6 +12,8 @@ class LearnedAbsolutePositions(PositionEncoding):
     (reference: src/model/paged_decoder.py:289, 306-314, 521-522).
     params: max_positions, hidden_size, name, init_std."""
 
+    graph_safe = True
+
     def param_specs(self):
         p = self.params
         return [(ParamSpec(self._n(p["name"] + ".weight"), (p["max_positions"], p["hidden_size"]), "table"),
@@ -30,3 +32,5 @@ class LearnedAbsolutePositions(PositionEncoding):
 @register_part("positions", "none")
 class NoPositions(PositionEncoding):
     """No position information at all."""
+
+    graph_safe = True

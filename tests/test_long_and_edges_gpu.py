@@ -1,0 +1,81 @@
+"""Long decoding, the first tokens of a sequence, and inputs built so that a fault of the cache shows."""
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_gpt2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_long_decoding_token_by_token(which, dtype):
+    """Two requests decoded one token per step from their second token to the model's last position,
+    side by side (so every step is a replayed CUDA graph), against whole-sequence logits."""
+    values, _, block = helpers.TINY[which]
+    length = values["n_positions"]
+    seqs = {"p": helpers.random_tokens(values["vocab_size"], length, seed=21),
+            "q": helpers.random_tokens(values["vocab_size"], length - 37, seed=22)}
+    want = helpers.plain_logits(which, seqs)
+    steps = [{"step": 0, "entries": [{"id": n, "tokens": t[:1], "want": [0]} for n, t in seqs.items()], "end": []}]
+    for place in range(1, length):
+        entries = [{"id": n, "tokens": [t[place]], "want": [0]} for n, t in seqs.items() if place < len(t)]
+        ended = [n for n, t in seqs.items() if place == len(t) - 1]
+        steps.append({"step": place, "entries": entries, "end": ended})
+    got = helpers.replay(helpers.model_folder(which), dtype, steps, helpers.peak_tokens(steps), block_size=block)
+    for name in seqs:
+        helpers.assert_close(got[name], want[name], dtype, f"long decode {which}/{dtype}/{name}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(dtype):
+    """Positions 0..3 alone, as one-token prompts, two-token prompts, and decoded from position 0."""
+    vocab = helpers.TINY["a"][0]["vocab_size"]
+    seqs = {f"s{i}": helpers.random_tokens(vocab, n, seed=70 + i) for i, n in enumerate([1, 2, 3, 4])}
+    want = helpers.plain_logits("a", seqs)
+    whole = helpers.replay(helpers.model_folder("a"), dtype, helpers.trace_whole(seqs), 256)
+    single = helpers.replay(helpers.model_folder("a"), dtype, helpers.trace_tail(seqs, tail=32), 256)
+    together = [{"step": 0, "entries": [{"id": n, "tokens": t, "want": list(range(len(t)))} for n, t in seqs.items()],
+                 "end": list(seqs)}]
+    batch = helpers.replay(helpers.model_folder("a"), dtype, together, 256)
+    for name in seqs:
+        for got in (whole, single, batch):
+            helpers.assert_close(got[name], want[name], dtype, f"first tokens {name}")
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
+def test_a_reused_page_never_leaks_and_page_edges_hold(dtype, tol):
+    """A request fills pages with large keys and values and ends; the next requests get those very pages
+    (LIFO) and stop one token short of, at, and one past a page edge. Stale rows of the reused pages lie
+    right behind their last token: if a kernel read one slot too far the logits would move visibly."""
+    from pagedserve_b200.config.engine_config import EngineConfig
+    from pagedserve_b200.engine.batch import StepEntry
+    from pagedserve_b200.engine.engine import Engine
+
+    config, weights = helpers.plain_model("a")
+    engine = Engine.from_folder(helpers.model_folder("a"), EngineConfig(dtype=dtype, block_size=16, num_blocks=8,
+                                                                       max_num_seqs=4))
+    vocab = config["vocab_size"]
+    first = helpers.random_tokens(vocab, 128, seed=5)
+    engine.step([StepEntry("old", first, [127])])
+    pool = engine.cache.groups[0].pool
+    pool.mul_(50.0)                                   # what "old" leaves behind is loud
+    engine.finish("old")
+    assert engine.cache.free_pages() == 8
+    for length in (15, 16, 17, 31, 32, 33):
+        tokens = helpers.random_tokens(vocab, length, seed=100 + length)
+        want = plain_gpt2.forward_logits(config, weights, tokens).numpy()
+        head = max(1, length - 3)
+        rows = [engine.step([StepEntry("new", tokens[:head], list(range(head)))]).cpu().numpy()]
+        for place in range(head, length):
+            rows.append(engine.step([StepEntry("new", [tokens[place]], [0])]).cpu().numpy())
+        got = np.concatenate(rows)
+        scale = float(np.abs(want).max())
+        assert float(np.abs(got - want).max()) <= tol * scale, f"length {length}"
+        table = list(engine.cache.groups[0].tables["new"])
+        engine.finish("new")
+        pool[table].mul_(50.0) if dtype == "float32" else None
+    engine.cache.check_invariants()
