@@ -149,6 +149,211 @@ int pick_tiles(const void* A, int lda, const void* W, int ldw, const float* bias
     return pick_warps<8, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The same product with the norm of its input fused in front and the cache write fused behind:
+//   A[m, :] = norm(X[rows[m] or m, :]) computed on the fly from the float32 residual stream
+//             (statistics in two passes in float32, one warp per row, while the first weight
+//             loads are already in flight), rounded to bfloat16 as the separate norm kernel does;
+//   columns n >= q_width of the result are keys and values: they are written straight into the
+//             request's page (cache layout of attention_simt.cu) instead of the output buffer.
+// This removes the norm launch and the kv-append launch of a decode step.
+struct KvScatter {
+    __nv_bfloat16* k_pool;
+    __nv_bfloat16* v_pool;
+    long long page_stride;
+    const int* token_item;
+    const int* positions;
+    const int* block_table;
+    int bt_stride;
+    int q_width;       // columns [0, q_width) are queries and go to `out`
+    int kv_width;      // then kv_width key columns, then kv_width value columns
+    int head_dim;
+    int page_size;
+};
+
+struct NormInput {
+    const float* x;    // float32 rows
+    int ldx;
+    const int* rows;   // optional gather of rows
+    const float* gamma;
+    const float* beta; // optional
+    float eps;
+    int has_mean;
+};
+
+template <int MT, int WARPS, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int ldw,
+                         const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K,
+                         int act, int accumulate, KvScatter kv) {
+    extern __shared__ float red[];                 // [WARPS][16][8*MT], then stats [8*MT][2]
+    constexpr int UNROLL = 6;
+    constexpr int TOK = 8 * MT;
+    float* stats = red + (size_t)WARPS * 16 * TOK;
+    pdl_prologue();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
+    const __nv_bfloat16* w0 = W + (size_t)r0 * ldw + 8 * t;
+    const __nv_bfloat16* w1 = W + (size_t)r1 * ldw + 8 * t;
+    const int steps = (K + 31) >> 5;
+
+    // first batch of weight loads: in flight while the statistics are computed
+    uint4 wa[UNROLL], wb[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        int k = (warp + u * WARPS) << 5;
+        bool ok = (warp + u * WARPS) < steps && (k + 8 * t) < K;
+        wa[u] = ok ? ldg_stream(w0 + k) : make_uint4(0, 0, 0, 0);
+        wb[u] = ok ? ldg_stream(w1 + k) : make_uint4(0, 0, 0, 0);
+    }
+    // statistics: one warp per row
+    for (int m = warp; m < M; m += WARPS) {
+        const float* xr = in.x + (size_t)(in.rows ? in.rows[m] : m) * in.ldx;
+        float sum = 0.f;
+        for (int k = lane; k < K; k += 32) sum += xr[k];
+        float mean = in.has_mean ? warp_sum(sum) / (float)K : 0.f;
+        float sq = 0.f;
+        for (int k = lane; k < K; k += 32) { float d = xr[k] - mean; sq += d * d; }
+        float rstd = rsqrtf(warp_sum(sq) / (float)K + in.eps);
+        if (lane == 0) { stats[2 * m] = mean; stats[2 * m + 1] = rstd; }
+    }
+    __syncthreads();
+
+    const float* xrow[MT];
+    float mean[MT], rstd[MT];
+    bool aok[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        int m = 8 * mt + g;
+        aok[mt] = m < M;
+        int mm = aok[mt] ? m : 0;
+        xrow[mt] = in.x + (size_t)(in.rows ? in.rows[mm] : mm) * in.ldx + 8 * t;
+        mean[mt] = stats[2 * mm];
+        rstd[mt] = stats[2 * mm + 1];
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+
+    for (int s0 = warp; s0 < steps; s0 += WARPS * UNROLL) {
+        if (s0 != warp) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int k = (s0 + u * WARPS) << 5;
+                bool ok = (s0 + u * WARPS) < steps && (k + 8 * t) < K;
+                wa[u] = ok ? ldg_stream(w0 + k) : make_uint4(0, 0, 0, 0);
+                wb[u] = ok ? ldg_stream(w1 + k) : make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            int k = (s0 + u * WARPS) << 5;
+            bool ok = (s0 + u * WARPS) < steps && (k + 8 * t) < K;
+            if (!ok) continue;
+            uint32_t a1[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
+            uint32_t a2[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+            const float4 ga = *reinterpret_cast<const float4*>(in.gamma + k + 8 * t);
+            const float4 gb = *reinterpret_cast<const float4*>(in.gamma + k + 8 * t + 4);
+            float4 ba = make_float4(0, 0, 0, 0), bb = ba;
+            if (in.beta) {
+                ba = *reinterpret_cast<const float4*>(in.beta + k + 8 * t);
+                bb = *reinterpret_cast<const float4*>(in.beta + k + 8 * t + 4);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t b1[2] = {0, 0}, b2[2] = {0, 0};
+                if (aok[mt]) {
+                    const float4 xa = *reinterpret_cast<const float4*>(xrow[mt] + k);
+                    const float4 xb = *reinterpret_cast<const float4*>(xrow[mt] + k + 4);
+                    const float mu = mean[mt], rs = rstd[mt];
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn((xa.x - mu) * rs * ga.x + ba.x, (xa.y - mu) * rs * ga.y + ba.y);
+                    __nv_bfloat162 p1 = __floats2bfloat162_rn((xa.z - mu) * rs * ga.z + ba.z, (xa.w - mu) * rs * ga.w + ba.w);
+                    __nv_bfloat162 p2 = __floats2bfloat162_rn((xb.x - mu) * rs * gb.x + bb.x, (xb.y - mu) * rs * gb.y + bb.y);
+                    __nv_bfloat162 p3 = __floats2bfloat162_rn((xb.z - mu) * rs * gb.z + bb.z, (xb.w - mu) * rs * gb.w + bb.w);
+                    b1[0] = *reinterpret_cast<uint32_t*>(&p0); b1[1] = *reinterpret_cast<uint32_t*>(&p1);
+                    b2[0] = *reinterpret_cast<uint32_t*>(&p2); b2[1] = *reinterpret_cast<uint32_t*>(&p3);
+                }
+                mma_bf16_16816(acc[mt], a1, b1);
+                mma_bf16_16816(acc[mt], a2, b2);
+            }
+        }
+    }
+    float* mine = red + (size_t)warp * 16 * TOK;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        int c = 8 * mt + 2 * t;
+        mine[g * TOK + c] = acc[mt][0];
+        mine[g * TOK + c + 1] = acc[mt][1];
+        mine[(g + 8) * TOK + c] = acc[mt][2];
+        mine[(g + 8) * TOK + c + 1] = acc[mt][3];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * TOK; e += WARPS * 32) {
+        int r = e & 15, m = e >> 4;
+        int n = n0 + r;
+        if (m >= M || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * 16 * TOK + r * TOK + m];
+        if (bias) v += bias[n];
+        v = apply_act(v, act);
+        if (kv.k_pool && n >= kv.q_width) {
+            int c = n - kv.q_width;
+            __nv_bfloat16* pool = kv.k_pool;
+            if (c >= kv.kv_width) { c -= kv.kv_width; pool = kv.v_pool; }
+            int head = c / kv.head_dim, d = c - head * kv.head_dim;
+            int p = kv.positions[m];
+            int page = kv.block_table[(size_t)kv.token_item[m] * kv.bt_stride + p / kv.page_size];
+            if (page >= 0)
+                pool[(size_t)page * kv.page_stride + ((size_t)head * kv.page_size + (p % kv.page_size)) * kv.head_dim + d] =
+                    __float2bfloat16_rn(v);
+            continue;
+        }
+        size_t o = (size_t)m * ldo + n;
+        if (accumulate) v += to_float(out[o]);
+        out[o] = from_float<TOut>(v);
+    }
+}
+
+template <int MT, int WARPS, typename TOut>
+int launch_skinny_fused(const NormInput& in, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
+                        int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+    size_t smem = (size_t)(WARPS * 16 * 8 * MT + 16 * MT) * sizeof(float);
+    auto kernel = gemm_skinny_fused_kernel<MT, WARPS, TOut>;
+    if (smem > 48 * 1024) {
+        static bool raised = false;
+        if (!raised) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                return PS_ERR_LAUNCH;
+            raised = true;
+        }
+    }
+    return launch_pdl(kernel, dim3((N + 15) / 16), dim3(WARPS * 32), smem, s, in, (const __nv_bfloat16*)W, ldw, bias,
+                      (TOut*)out, ldo, M, N, K, act, accumulate, kv);
+}
+
+template <int MT, typename TOut>
+int pick_warps_fused(const NormInput& in, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N,
+                     int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+    int steps = (K + 31) / 32;
+    if (steps <= 24) return launch_skinny_fused<MT, 4, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    if (steps <= 48) return launch_skinny_fused<MT, 8, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    return launch_skinny_fused<MT, 16, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+}
+
+template <typename TOut>
+int pick_tiles_fused(const NormInput& in, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N,
+                     int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+    if (M <= 8) return pick_warps_fused<1, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    if (M <= 16) return pick_warps_fused<2, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    return pick_warps_fused<4, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+}
+
 }  // namespace ps
 
 PS_EXPORT int ps_gemm_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* out,
@@ -165,5 +370,32 @@ PS_EXPORT int ps_gemm_skinny(const void* A, int lda, const void* W, int ldw, con
         return ps::pick_tiles<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
     if (out_dtype == PS_BF16)
         return ps::pick_tiles<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
+    return PS_ERR_UNSUPPORTED;
+}
+
+// out = epilogue(norm(x[rows]) W^T + bias) for at most 32 rows, with an optional cache write of the key and
+// value columns (kv_* arguments; k_pool null = none). x float32 with ldx % 4 == 0, K % 8 == 0.
+PS_EXPORT int ps_gemm_skinny_fused(const float* x, int ldx, const int* rows, const float* gamma, const float* beta,
+                                   float eps, int has_mean, const void* W, int ldw, const float* bias, void* out,
+                                   int ldo, int M, int N, int K, int out_dtype, int act, int accumulate,
+                                   void* k_pool, void* v_pool, long long page_stride, const int* token_item,
+                                   const int* positions, const int* block_table, int bt_stride, int q_width,
+                                   int kv_width, int head_dim, int page_size, void* stream) {
+    if (M <= 0 || N <= 0) return PS_OK;
+    if (M > 32) return PS_ERR_UNSUPPORTED;
+    if (K <= 0 || K % 8 != 0 || ldx % 4 != 0 || ldw % 8 != 0 || ldx < K || ldw < K || ldo < N) return PS_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)W & 15) || ((uintptr_t)gamma & 15) || ((uintptr_t)beta & 15))
+        return PS_ERR_UNSUPPORTED;
+    if (accumulate && out_dtype != PS_F32) return PS_ERR_BAD_ARGUMENT;
+    if (k_pool && (q_width + 2 * kv_width != N || head_dim <= 0 || kv_width % head_dim != 0 || page_size <= 0))
+        return PS_ERR_BAD_ARGUMENT;
+    ps::NormInput in{x, ldx, rows, gamma, beta, eps, has_mean};
+    ps::KvScatter kv{(__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride, token_item, positions, block_table,
+                     bt_stride, q_width, kv_width, head_dim, page_size};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == PS_F32)
+        return ps::pick_tiles_fused<float>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    if (out_dtype == PS_BF16)
+        return ps::pick_tiles_fused<__nv_bfloat16>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
     return PS_ERR_UNSUPPORTED;
 }

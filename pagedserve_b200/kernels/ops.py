@@ -200,8 +200,61 @@ class Ops:
         return (a.shape[0] <= 64 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
+    FUSED_NORM_ROWS = 32          # most rows for which the norm is folded into the skinny product
+
+    def _fused_norm_ok(self, a, w):
+        norm = a.norm
+        return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS
+                and type(norm).__name__ == "LayerNorm" and a.x.dtype == torch.float32
+                and a.shape[1] % 8 == 0 and a.x.stride(0) % 4 == 0 and a.x.stride(1) == 1
+                and w.stride(0) % 8 == 0 and w.stride(1) == 1 and w.dtype == torch.bfloat16
+                and a.x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and norm.weight.data_ptr() % 16 == 0
+                and (norm.bias is None or norm.bias.data_ptr() % 16 == 0))
+
+    def linear_skinny_fused(self, a, w, bias, out, act=None, accumulate=False, kv=None):
+        """out = act(norm(x)[rows] @ w.T + bias) with the norm computed inside the product's kernel
+        (``a`` is a DeferredNorm); ``kv`` = (ctx, layer, q_width, kv_width, head_dim) also sends the key
+        and value columns of the result straight into the pages."""
+        norm = a.norm
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError("linear_skinny_fused: shapes do not match")
+        _require(out, "out")
+        if kv is not None:
+            ctx, layer, q_width, kv_width, head_dim = kv
+            kv_args = (_ptr(layer.k_pool), _ptr(layer.v_pool), _c_ll(layer.page_stride), _ptr(ctx.token_item),
+                       _ptr(ctx.positions), _ptr(layer.block_table), _c_int(layer.block_table.stride(0)),
+                       _c_int(q_width), _c_int(kv_width), _c_int(head_dim), _c_int(layer.page_size))
+        else:
+            kv_args = (_c_void_p(0), _c_void_p(0), _c_ll(0), _c_void_p(0), _c_void_p(0), _c_void_p(0), _c_int(0),
+                       _c_int(N), _c_int(0), _c_int(1), _c_int(1))
+        self.launches += 1
+        _check(self.fast.ps_gemm_skinny_fused(
+            _ptr(a.x), _c_int(a.x.stride(0)), _ptr(a.rows), _ptr(norm.weight), _ptr(norm.bias),
+            _c_float(float(norm.params["eps"])), _c_int(1 if norm.params.get("has_mean", True) else 0),
+            _ptr(w), _c_int(w.stride(0)), _ptr(bias), _ptr(out), _c_int(out.stride(0)), _c_int(M), _c_int(N),
+            _c_int(K), _c_int(dtype_code(out.dtype)), _c_int(_ACT_CODE[act]), _c_int(1 if accumulate else 0),
+            *kv_args, _stream()), "gemm_skinny_fused")
+        return out
+
+    def linear_qkv(self, a, w, bias, out, ctx, layer, q_width, kv_width, head_dim, scatter=True):
+        """The packed q|k|v projection.  Returns True when the key and value columns were written into
+        the pages by the product's own epilogue (then no separate cache write is needed)."""
+        if scatter and hasattr(a, "materialize") and self._fused_norm_ok(a, w) and layer.k_pool is not None:
+            self.linear_skinny_fused(a, w, bias, out, kv=(ctx, layer, q_width, kv_width, head_dim))
+            return True
+        self.linear(a, w, bias, out)
+        return False
+
     def linear(self, a, w, bias, out, act=None, accumulate=False):
-        """The matrix product of the model: float32 runs on FFMA, bfloat16 on tensor cores."""
+        """The matrix product of the model: float32 runs on FFMA, bfloat16 on tensor cores.
+        ``a`` may be a DeferredNorm: it is folded into the product where a kernel can, else evaluated."""
+        if hasattr(a, "materialize"):
+            if self._fused_norm_ok(a, w):
+                return self.linear_skinny_fused(a, w, bias, out, act, accumulate)
+            a = a.materialize()
         if self.dtype == torch.float32:
             return self.linear_simt(a, w, bias, out, act, accumulate)
         from pagedserve_b200.kernels import tensorcore

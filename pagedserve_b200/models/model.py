@@ -122,7 +122,10 @@ class Model:
             self.blocks[entry.layer].forward(hidden, ctx, layer)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=hidden.device)
-        normed = self.final_norm.forward(hidden, rows=ctx.logit_rows)
+        if hasattr(self.final_norm, "defer"):
+            normed = self.final_norm.defer(hidden, rows=ctx.logit_rows)     # the head's product may fold it in
+        else:
+            normed = self.final_norm.forward(hidden, rows=ctx.logit_rows)
         return self.head.forward(normed, self.embedding)
 
 

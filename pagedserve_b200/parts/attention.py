@@ -30,6 +30,7 @@ class CausalSelfAttention(Mixer):
     """
 
     graph_safe = True
+    accepts_deferred_norm = True       # x goes straight into ops.linear_qkv
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -74,13 +75,21 @@ class CausalSelfAttention(Mixer):
         p = self.params
         ops = self.env.ops
         tokens = x.shape[0]
+        from pagedserve_b200.parts.base import PositionEncoding
+
         qkv = torch.empty((tokens, self.q_width + 2 * self.kv_width), dtype=self.env.dtype, device=x.device)
-        ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        write_cache = p.get("write_cache", True)
+        # keys may go from the projection straight into the pages unless the position encoding
+        # still has to transform them
+        no_rotation = type(layer.positions).rotate is PositionEncoding.rotate
+        written = ops.linear_qkv(x, self.w_qkv, self.b_qkv, qkv, ctx, layer, self.q_width, self.kv_width,
+                                 p["head_dim"], scatter=write_cache and no_rotation)
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
-        layer.positions.rotate(q, k, ctx)
+        if not no_rotation:
+            layer.positions.rotate(q, k, ctx)
         context = torch.empty((tokens, self.q_width), dtype=self.env.dtype, device=x.device)
         ops.attention(q, k, v, context, ctx, layer, p["n_heads"], p["n_kv_heads"], p["head_dim"],
-                      p.get("window"), float(p["scale"]), write_cache=p.get("write_cache", True))
+                      p.get("window"), float(p["scale"]), write_cache=write_cache and not written)
         ops.linear(context, self.w_out, self.b_out, residual, accumulate=True)

@@ -16,8 +16,14 @@ class PreNormBlock(Block):
 
     required_norms = ("pre_mixer", "pre_feed_forward")
 
+    @staticmethod
+    def _normed(norm, consumer, hidden):
+        # a consumer whose first operation is a matrix product may take the norm unevaluated
+        if getattr(consumer, "accepts_deferred_norm", False) and hasattr(norm, "defer"):
+            return norm.defer(hidden)
+        return norm.forward(hidden)
+
     def forward(self, hidden, ctx, layer):
-        normed = self.norms["pre_mixer"].forward(hidden)
-        self.mixer.forward(normed, hidden, ctx, layer)
-        normed = self.norms["pre_feed_forward"].forward(hidden, out=normed)
-        self.feed_forward.forward(normed, hidden, ctx)
+        self.mixer.forward(self._normed(self.norms["pre_mixer"], self.mixer, hidden), hidden, ctx, layer)
+        self.feed_forward.forward(self._normed(self.norms["pre_feed_forward"], self.feed_forward, hidden),
+                                  hidden, ctx)

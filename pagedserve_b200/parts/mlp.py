@@ -18,6 +18,7 @@ class DenseMLP(FeedForward):
     stored_in_out, up_name, down_name, init_std, out_init_std."""
 
     graph_safe = True
+    accepts_deferred_norm = True       # x goes straight into ops.linear
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)

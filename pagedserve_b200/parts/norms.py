@@ -8,6 +8,22 @@ from pagedserve_b200.parts.base import Norm, register_part
 from pagedserve_b200.weights.loader import ParamSpec
 
 
+class DeferredNorm:
+    """A norm that has been asked for but not computed: the consumer (a matrix product) may fold it
+    into its own kernel, or call :meth:`materialize` to get the normed tensor."""
+
+    def __init__(self, norm, x, rows=None):
+        self.norm = norm
+        self.x = x
+        self.rows = rows
+        count = rows.numel() if rows is not None else x.shape[0]
+        self.shape = (count, x.shape[1])
+        self.device = x.device
+
+    def materialize(self, out=None):
+        return self.norm.forward(self.x, out=out, rows=self.rows)
+
+
 @register_part("norm", "layernorm")
 class LayerNorm(Norm):
     """y = (x - mean) / sqrt(var + eps) * weight + bias over the last axis, in float32.
@@ -32,6 +48,9 @@ class LayerNorm(Norm):
         p = self.params
         self.weight = tensors[self._n(p["name"] + ".weight")]
         self.bias = tensors[self._n(p["name"] + ".bias")] if p.get("has_bias", True) else None
+
+    def defer(self, x, rows=None):
+        return DeferredNorm(self, x, rows)
 
     def forward(self, x, out=None, rows=None, out_dtype=None):
         n_rows = rows.numel() if rows is not None else x.shape[0]

@@ -163,6 +163,90 @@ def test_gemm_tcgen05(M, N, K, bn):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("M", [1, 8, 9, 16, 25, 32])
+@pytest.mark.parametrize("N,K", [(288, 96), (2304, 768), (1000, 320), (768, 3072)])
+def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
+    """norm -> product in one kernel against norm kernel + product, with gathered rows, the RMS form, and
+    the key/value columns of a packed projection landing in the right page slots."""
+    from pagedserve_b200.parts.norms import DeferredNorm
+
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    x = (torch.randn(M + 5, K, generator=g) * 2 + 0.7).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    rows = torch.randperm(M + 5, generator=g)[:M].to(torch.int32).to(DEV)
+
+    class FakeNorm:
+        def __init__(self, has_mean, has_bias):
+            self.weight = (torch.randn(K, generator=g) * 0.1 + 1).to(DEV)
+            self.bias = torch.randn(K, generator=g).to(DEV) if has_bias else None
+            self.params = {"eps": 1e-5, "has_mean": has_mean}
+
+        def forward(self, x, out=None, rows=None):
+            count = rows.numel() if rows is not None else x.shape[0]
+            out = torch.empty(count, K, dtype=torch.bfloat16, device=DEV)
+            return ops.layernorm(x, self.weight, self.bias, 1e-5, out, rows=rows, has_mean=self.params["has_mean"])
+
+    FakeNorm.__name__ = "LayerNorm"
+    for has_mean, has_bias, use_rows in ((True, True, False), (False, False, True), (True, True, True)):
+        norm = FakeNorm(has_mean, has_bias)
+        deferred = DeferredNorm(norm, x if use_rows else x[:M], rows if use_rows else None)
+        assert ops._fused_norm_ok(deferred, w)
+        fused = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        ops.linear_skinny_fused(deferred, w, bias, fused, act="gelu_tanh")
+        separate = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        ops.linear_skinny(deferred.materialize(), w, bias, separate, act="gelu_tanh")
+        # same bfloat16 roundings of the normed input up to float32 reassociation in the statistics
+        assert rel_err(fused, separate) < 4e-3
+        picked = x[rows.long()] if use_rows else x[:M]
+        xd = picked.double().cpu()
+        if has_mean:
+            normed = plain_gpt2.layer_norm(xd, norm.weight.double().cpu(), norm.bias.double().cpu(), 1e-5)
+        else:
+            normed = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5) * norm.weight.double().cpu()
+        assert rel_err(fused, gemm_reference(normed, w.cpu(), bias.cpu(), "gelu_tanh", None)) < 8e-3
+    if N % 3 == 0 and (N // 3) % 16 == 0:
+        # packed projection: q to the buffer, k and v into pages
+        width = N // 3
+        head_dim = 16 if width % 48 else 48
+        kv_heads = width // head_dim
+        page = 8
+        lengths = [3 + 2 * i for i in range(M)]                 # every token is the last of its own request
+        pages = [-(-n // page) for n in lengths]
+        table = torch.full((M, max(pages)), -1, dtype=torch.int32)
+        order = torch.randperm(sum(pages), generator=g)
+        cursor = 0
+        for i, count in enumerate(pages):
+            table[i, :count] = order[cursor:cursor + count].to(torch.int32)
+            cursor += count
+        pool = torch.zeros(sum(pages), 1, 2, kv_heads, page, head_dim, dtype=torch.bfloat16, device=DEV)
+
+        class Ctx:
+            token_item = torch.arange(M, dtype=torch.int32, device=DEV)
+            positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+
+        class Layer:
+            k_pool, v_pool = pool[:, 0, 0], pool[:, 0, 1]
+            page_stride = 2 * kv_heads * page * head_dim
+            page_size = page
+            block_table = table.to(DEV)
+
+        norm = FakeNorm(True, True)
+        deferred = DeferredNorm(norm, x[:M])
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        assert ops.linear_qkv(deferred, w, bias, out, Ctx, Layer, width, width, head_dim, scatter=True)
+        want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ops.linear_skinny(deferred.materialize(), w, bias, want)
+        assert rel_err(out[:, :width], want[:, :width]) < 8e-3
+        assert float(out[:, width:].abs().max()) == 0.0           # keys and values did not go to the buffer
+        for i, n in enumerate(lengths):
+            slot = pool[int(table[i, (n - 1) // page]), 0, :, :, (n - 1) % page, :].reshape(2, width)
+            assert rel_err(slot[0], want[i, width:2 * width]) < 8e-3
+            assert rel_err(slot[1], want[i, 2 * width:]) < 8e-3
+        assert int((pool != 0).sum()) <= 2 * M * width             # nothing else was touched
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take():
     from pagedserve_b200.kernels.ops import KernelError
 
