@@ -67,7 +67,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     int block = blockIdx.x, item = -1, qb = 0;
     for (int i = first_item; i < first_item + n_items; ++i) {
         int blocks = (q_start[i + 1] - q_start[i] + BQ - 1) / BQ;
-        if (block < blocks) { item = i; qb = block; break; }
+        if (block < blocks) { item = i; qb = blocks - 1 - block; break; }   // late blocks see most keys: first
         block -= blocks;
     }
     if (item < 0) return;

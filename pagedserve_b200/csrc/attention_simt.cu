@@ -40,6 +40,52 @@ __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restric
     }
 }
 
+// The same copy in 16-byte pieces: thread = (token, k or v, piece).
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_append_vec_kernel(const T* __restrict__ k_src, const T* __restrict__ v_src, int src_stride,
+                     const int* __restrict__ token_item, const int* __restrict__ positions,
+                     const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
+                     T* __restrict__ v_pool, long long page_stride, int T_tokens, int n_kv_heads, int head_dim,
+                     int page_size) {
+    pdl_prologue();
+    constexpr int PER = 16 / sizeof(T);                       // elements per piece
+    const int pieces = n_kv_heads * head_dim / PER;           // per token and tensor
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)T_tokens * 2 * pieces) return;
+    const int piece = (int)(idx % pieces);
+    const int which = (int)((idx / pieces) & 1);
+    const int t = (int)(idx / (2 * pieces));
+    const int p = positions[t];
+    const int page = block_table[(size_t)token_item[t] * bt_stride + p / page_size];
+    if (page < 0) return;
+    const int c = piece * PER, g = c / head_dim, d = c - g * head_dim;
+    const size_t dst = (size_t)page * page_stride + ((size_t)g * page_size + (p % page_size)) * head_dim + d;
+    const T* src = (which ? v_src : k_src) + (size_t)t * src_stride + c;
+    T* pool = which ? v_pool : k_pool;
+    *reinterpret_cast<uint4*>(pool + dst) = *reinterpret_cast<const uint4*>(src);
+}
+
+template <typename T>
+int launch_kv_append(const void* k_src, const void* v_src, int src_stride, const int* token_item,
+                     const int* positions, const int* block_table, int bt_stride, void* k_pool, void* v_pool,
+                     long long page_stride, int T_tokens, int n_kv_heads, int head_dim, int page_size,
+                     cudaStream_t s) {
+    constexpr int PER = 16 / sizeof(T);
+    const bool aligned = (((uintptr_t)k_src | (uintptr_t)v_src | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0 &&
+                         src_stride % PER == 0 && page_stride % PER == 0 && head_dim % PER == 0;
+    if (aligned) {
+        long long total = (long long)T_tokens * 2 * (n_kv_heads * head_dim / PER);
+        return launch_pdl(kv_append_vec_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s,
+                          (const T*)k_src, (const T*)v_src, src_stride, token_item, positions, block_table, bt_stride,
+                          (T*)k_pool, (T*)v_pool, page_stride, T_tokens, n_kv_heads, head_dim, page_size);
+    }
+    int nt = n_kv_heads * head_dim >= 256 ? 256 : 128;
+    return launch_pdl(kv_append_kernel<T>, dim3(T_tokens), dim3(nt), 0, s, (const T*)k_src, (const T*)v_src, src_stride,
+                      token_item, positions, block_table, bt_stride, (T*)k_pool, (T*)v_pool, page_stride, n_kv_heads,
+                      head_dim, page_size);
+}
+
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_MAX_HD = 256;
 
@@ -150,16 +196,13 @@ PS_EXPORT int ps_kv_append(const void* k_src, const void* v_src, int src_stride,
     int rc = check_attention_sizes(n_kv_heads, n_kv_heads, head_dim, page_size);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    int nt = n_kv_heads * head_dim >= 256 ? 256 : 128;
     if (dtype == PS_F32)
-        return ps::launch_pdl(ps::kv_append_kernel<float>, dim3(T), dim3(nt), 0, s, (const float*)k_src,
-                              (const float*)v_src, src_stride, token_item, positions, block_table, bt_stride,
-                              (float*)k_pool, (float*)v_pool, page_stride, n_kv_heads, head_dim, page_size);
+        return ps::launch_kv_append<float>(k_src, v_src, src_stride, token_item, positions, block_table, bt_stride,
+                                           k_pool, v_pool, page_stride, T, n_kv_heads, head_dim, page_size, s);
     if (dtype == PS_BF16)
-        return ps::launch_pdl(ps::kv_append_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, s,
-                              (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, src_stride, token_item,
-                              positions, block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
-                              page_stride, n_kv_heads, head_dim, page_size);
+        return ps::launch_kv_append<__nv_bfloat16>(k_src, v_src, src_stride, token_item, positions, block_table,
+                                                   bt_stride, k_pool, v_pool, page_stride, T, n_kv_heads, head_dim,
+                                                   page_size, s);
     return PS_ERR_UNSUPPORTED;
 }
 

@@ -116,6 +116,75 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     }
 }
 
+// Many rows (prefill): one warp per row, the row held in registers (H <= 32 * 4 * WMAX), float4 loads,
+// no shared memory and no block-wide barrier. Same two-pass statistics as above.
+template <typename TOut, int WMAX>
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, float eps, TOut* __restrict__ out, int n_rows, int H,
+                      int has_mean) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
+    const int quads = H >> 2;
+    float4 v[WMAX];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < WMAX; ++i) {
+        int c = lane + 32 * i;
+        v[i] = c < quads ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = has_mean ? warp_sum(sum) / (float)H : 0.f;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < WMAX; ++i) {
+        if (lane + 32 * i < quads) {
+            float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+            sq += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / (float)H + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    TOut* o = out + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < WMAX; ++i) {
+        int c = lane + 32 * i;
+        if (c < quads) {
+            float4 g = g4[c];
+            float4 b = beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            float y0 = (v[i].x - mean) * rstd * g.x + b.x, y1 = (v[i].y - mean) * rstd * g.y + b.y;
+            float y2 = (v[i].z - mean) * rstd * g.z + b.z, y3 = (v[i].w - mean) * rstd * g.w + b.w;
+            if constexpr (sizeof(TOut) == 2) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+                uint2 pack = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                *reinterpret_cast<uint2*>(o + 4 * c) = pack;
+            } else {
+                *reinterpret_cast<float4*>(o + 4 * c) = make_float4(y0, y1, y2, y3);
+            }
+        }
+    }
+}
+
+template <typename TOut>
+int launch_layernorm(const float* x, const int* rows, int n_rows, int H, const float* gamma, const float* beta,
+                     float eps, int has_mean, TOut* out, cudaStream_t s) {
+    const bool aligned = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)beta | (uintptr_t)out) & 15) == 0;
+    if (n_rows >= 64 && aligned && H <= 32 * 4 * 16) {
+        dim3 grid((n_rows + 7) / 8);
+        if (H <= 32 * 4 * 8)
+            return launch_pdl(layernorm_warp_kernel<TOut, 8>, grid, dim3(256), 0, s, x, rows, gamma, beta, eps, out,
+                              n_rows, H, has_mean);
+        return launch_pdl(layernorm_warp_kernel<TOut, 16>, grid, dim3(256), 0, s, x, rows, gamma, beta, eps, out,
+                          n_rows, H, has_mean);
+    }
+    return launch_pdl(layernorm_kernel<TOut, 256>, dim3(n_rows), dim3(256), 0, s, x, rows, gamma, beta, eps, out, H,
+                      has_mean);
+}
+
 }  // namespace ps
 
 PS_EXPORT int ps_embed(const int* ids, const int* pos, const void* wte, const void* wpe, float* out,
@@ -140,12 +209,10 @@ PS_EXPORT int ps_layernorm(const float* x, const int* rows, int n_rows, int H, c
     if (n_rows <= 0) return PS_OK;
     if (H <= 0) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    constexpr int NT = 256;
     if (out_dtype == PS_F32)
-        return ps::launch_pdl(ps::layernorm_kernel<float, NT>, dim3(n_rows), dim3(NT), 0, s, x, rows, gamma, beta,
-                              eps, (float*)out, H, has_mean);
+        return ps::launch_layernorm<float>(x, rows, n_rows, H, gamma, beta, eps, has_mean, (float*)out, s);
     if (out_dtype == PS_BF16)
-        return ps::launch_pdl(ps::layernorm_kernel<__nv_bfloat16, NT>, dim3(n_rows), dim3(NT), 0, s, x, rows, gamma,
-                              beta, eps, (__nv_bfloat16*)out, H, has_mean);
+        return ps::launch_layernorm<__nv_bfloat16>(x, rows, n_rows, H, gamma, beta, eps, has_mean,
+                                                   (__nv_bfloat16*)out, s);
     return PS_ERR_UNSUPPORTED;
 }

@@ -204,7 +204,8 @@ class Ops:
 
     def _fused_norm_ok(self, a, w):
         norm = a.norm
-        return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS
+        # every CTA (16 output columns) recomputes the statistics: worth it only while the product is narrow
+        return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS and w.shape[0] <= 8192
                 and type(norm).__name__ == "LayerNorm" and a.x.dtype == torch.float32
                 and a.shape[1] % 8 == 0 and a.x.stride(0) % 4 == 0 and a.x.stride(1) == 1
                 and w.stride(0) % 8 == 0 and w.stride(1) == 1 and w.dtype == torch.bfloat16
