@@ -12,6 +12,8 @@ from __future__ import annotations
 
 from typing import Hashable, List, Sequence
 
+import os
+
 import numpy as np
 import torch
 
@@ -70,6 +72,12 @@ class ModelRunner:
                                     device=self.device)
         self._history_host = torch.empty(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32).pin_memory()
         self._step_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the persistent decode kernel, when the model's parts allow it
+        self.decode_stack = None
+        if enable_cuda_graphs and os.environ.get("PAGEDSERVE_B200_NO_DECODE_STACK") is None:
+            from pagedserve_b200.kernels.decode_stack import DecodeStack
+
+            self.decode_stack = DecodeStack.build_if_possible(model, cache, self.device)
 
     def _grow(self, needed: int) -> None:
         if needed <= self._capacity:
@@ -212,7 +220,9 @@ class ModelRunner:
         ctx = self.prepare(entries)
         decode_only = ctx.decode_only and all(entry.want == [0] for entry in entries)
         try:
-            if decode_only and self.enable_cuda_graphs:
+            if decode_only and self._stack_takes(ctx):
+                logits = self.decode_stack.run(ctx, 1, True, False, max_kv_len=ctx.max_kv_len)
+            elif decode_only and self.enable_cuda_graphs:
                 logits = self._run_decode_graph(ctx, "logits").logits.clone()
             else:
                 logits = self.model.forward(ctx)
@@ -250,7 +260,11 @@ class ModelRunner:
         B = ctx.num_items
         try:
             self._step_counter.zero_()
-            if self.enable_cuda_graphs:
+            if self._stack_takes(ctx):
+                self.decode_stack.run(ctx, steps, False, True, sampled=self._sampled, history=self._history,
+                                      step_counter=self._step_counter, max_steps=self.MAX_DEVICE_STEPS,
+                                      max_kv_len=ctx.max_kv_len + steps - 1)
+            elif self.enable_cuda_graphs:
                 graph = self._run_decode_graph(ctx, "sample")
                 for _ in range(steps - 1):
                     graph.replay()
@@ -268,6 +282,9 @@ class ModelRunner:
         self.steps += steps
         self.tokens_run += steps * B
         return self._history_host[:steps * B].numpy().reshape(steps, B).copy()
+
+    def _stack_takes(self, ctx: StepContext) -> bool:
+        return self.decode_stack is not None and ctx.decode_only and ctx.num_items <= self.decode_stack.MAX_BATCH
 
     def _forward_and_sample(self, ctx: StepContext) -> torch.Tensor:
         logits = self.model.forward(ctx)

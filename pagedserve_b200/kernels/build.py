@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "core": ["embed_norm.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu"],
     "bf16": ["gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu"],
     "tc": ["gemm_tc.cu"],
+    "stack": ["decode_stack.cu"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -132,8 +132,9 @@ def test_command_line_runs():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graph_replay_equals_eager_and_device_loop_equals_stepwise(dtype):
-    """The captured decode step gives the logits of the eager step, and a run of several decode
-    steps on the device gives the tokens of step-by-step generation."""
+    """The captured decode step (a CUDA graph, or the persistent decode kernel where the model qualifies)
+    gives the logits of the eager step, and a run of several decode steps on the device gives the tokens
+    of step-by-step generation."""
     from pagedserve_b200.engine.batch import StepEntry
 
     vocab = helpers.TINY["b"][0]["vocab_size"]
@@ -150,7 +151,9 @@ def test_graph_replay_equals_eager_and_device_loop_equals_stepwise(dtype):
             tokens = [int(t) for t in logits.argmax(-1).tolist()]
         # then 6 steps in one call, sampling on the device at temperature 0.7
         run = engine.decode([StepEntry(i, [tokens[i]]) for i in range(3)], [0.7, 0.0, 0.7], [5, 6, 7], steps=6)
-        results[graphs] = (torch.stack(rows), run, engine.runner.graph_replays)
+        stack = engine.runner.decode_stack
+        results[graphs] = (torch.stack(rows), run,
+                           engine.runner.graph_replays + (stack.launches if stack is not None else 0))
         assert [engine.cache.length(i) for i in range(3)] == [len(p) + 11 for p in prompts]
     eager, graph = results[False], results[True]
     assert graph[2] > 0 and eager[2] == 0
