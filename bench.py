@@ -124,6 +124,7 @@ def main():
     parser.add_argument("--skip-points", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--small", action="store_true", help="profiling aid: only the default decode measurement")
+    parser.add_argument("--prefill-only", action="store_true", help="profiling aid: only the prefill measurement")
     args = parser.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -248,6 +249,9 @@ def main():
         return {"value": T / (ms / 1e3), "tokens": T, "ms": ms, "frac": flops / (ms / 1e3) / peak,
                 "gflop": flops / 1e9}
 
+    if args.prefill_only:
+        print(json.dumps({"impl": "ours", "prefill": measure_prefill(repeats=3)}))
+        return 0
     main_run = measure_decode(args.batch, steps)
     e2e = measure_e2e(args.batch, steps)
     result = {

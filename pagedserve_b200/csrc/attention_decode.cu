@@ -229,16 +229,30 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if (!last_flag) return;
     __threadfence();
     const size_t base = ((size_t)t * n_heads + h) * n_splits;
+    // all (max, sum) pairs at once into shared memory (one trip to L2, not one per split)
+    float* ml_s = p_s;                                        // chunk_keys >= 32 floats: 16 splits fit
+    const bool staged = 2 * n_active <= chunk_keys;
+    if (staged) {
+        if (tid < 2 * n_active) ml_s[tid] = ldcg_f32(part_ml + (base + first_split) * 2 + tid);
+        __syncthreads();
+    }
     float M = -INFINITY;
-    for (int sidx = first_split; sidx <= last_split; ++sidx) M = fmaxf(M, ldcg_f32(part_ml + (base + sidx) * 2));
+    for (int i = 0; i < n_active; ++i)
+        M = fmaxf(M, staged ? ml_s[2 * i] : ldcg_f32(part_ml + (base + first_split + i) * 2));
     float L = 0.f;
-    for (int sidx = first_split; sidx <= last_split; ++sidx)
-        L += ldcg_f32(part_ml + (base + sidx) * 2 + 1) * exp2f(ldcg_f32(part_ml + (base + sidx) * 2) - M);
+    for (int i = 0; i < n_active; ++i) {
+        const float mi = staged ? ml_s[2 * i] : ldcg_f32(part_ml + (base + first_split + i) * 2);
+        const float li = staged ? ml_s[2 * i + 1] : ldcg_f32(part_ml + (base + first_split + i) * 2 + 1);
+        L += li * exp2f(mi - M);
+    }
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int d = tid; d < head_dim; d += DEC_THREADS) {
         float o = 0.f;
-        for (int sidx = first_split; sidx <= last_split; ++sidx)
-            o += ldcg_f32(part_acc + (base + sidx) * head_dim + d) * exp2f(ldcg_f32(part_ml + (base + sidx) * 2) - M);
+#pragma unroll 4
+        for (int i = 0; i < n_active; ++i) {
+            const float mi = staged ? ml_s[2 * i] : ldcg_f32(part_ml + (base + first_split + i) * 2);
+            o += ldcg_f32(part_acc + (base + first_split + i) * head_dim + d) * exp2f(mi - M);
+        }
         out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
     }
 }

@@ -56,6 +56,8 @@ struct Params {
     const float* temperature; const unsigned long long* seed;
     unsigned long long* best; int* sampled; int* history; int* step_counter; int max_steps;
     unsigned int* barrier; int* status;
+    int skip_mask;        // timing aid: phases whose bit is set do no work (1 norm, 2 qkv, 4 attention, 8 out, 16 up, 32 down, 64 head)
+    int ctas_per_sm;      // 0 = as many as fit, up to 3
 };
 
 __device__ __forceinline__ uint64_t timer_ns() {
@@ -106,15 +108,19 @@ struct GridSync {
 __device__ __forceinline__ void grid_barrier(GridSync& g) {
     __syncthreads();
     if (threadIdx.x == 0 && g.ok) {
-        __threadfence();
+        // arrivals count on counter[0]; the last arriver publishes the epoch in counter[32] (another
+        // 128-byte line), which is all the waiting CTAs read: polls do not queue behind the atomics
         const unsigned int target = (g.epoch + 1) * g.blocks;
-        atomicAdd(g.counter, 1u);
+        unsigned int old;
+        asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(g.counter) : "memory");
+        if (old + 1 == target)
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.counter + 32), "r"(g.epoch + 1) : "memory");
         const uint64_t start = timer_ns();
         unsigned int seen;
         int spins = 0;
         while (true) {
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.counter) : "memory");
-            if (seen >= target) break;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.counter + 32) : "memory");
+            if (seen >= g.epoch + 1) break;
             if ((++spins & 255) == 0) {
                 if (*(volatile int*)g.status != 0 || timer_ns() - start > WAIT_LIMIT_NS) {
                     atomicExch(g.status, 21);
@@ -123,7 +129,6 @@ __device__ __forceinline__ void grid_barrier(GridSync& g) {
                 }
             }
         }
-        __threadfence();
     }
     g.epoch += 1;
     // thread 0's verdict to the whole CTA
@@ -583,7 +588,7 @@ __global__ void __launch_bounds__(THREADS, 3) decode_stack_kernel(const Params p
             // P1: norm1 -> q|k|v
             Product g{};
             if (p.stage_in_smem) {
-                stage_norm(p, lw.ln1_g, lw.ln1_b, l == 0, a_s, lda_s);
+                if (!(p.skip_mask & 1)) stage_norm(p, lw.ln1_g, lw.ln1_b, l == 0, a_s, lda_s);
                 g.a = a_s; g.lda = lda_s;
             } else {
                 norm_to_global(p, lw.ln1_g, lw.ln1_b, l == 0);
@@ -592,23 +597,23 @@ __global__ void __launch_bounds__(THREADS, 3) decode_stack_kernel(const Params p
             }
             g.w = lw.w_qkv; g.bias = lw.b_qkv; g.N = q_width + 2 * kv_width; g.K = p.H; g.epilogue = EPI_QKV;
             g.out_bf16 = p.q; g.ldo = q_width; g.k_pool = lw.k_pool; g.v_pool = lw.v_pool;
-            run_product<MT>(p, g, red, cta_best);
+            if (!(p.skip_mask & 2)) run_product<MT>(p, g, red, cta_best);
             prefetch_tiles(lw.w_out, p.H, q_width);
             grid_barrier(sync);
             // P2: attention
-            run_attention(p, lw, smem, &bar, phase, attn_ok);
+            if (!(p.skip_mask & 4)) run_attention(p, lw, smem, &bar, phase, attn_ok);
             grid_barrier(sync);
             // P3: output projection into the stream
             g = Product{};
             g.a = p.attn; g.lda = q_width; g.w = lw.w_out; g.bias = lw.b_out; g.N = p.H; g.K = q_width;
             g.epilogue = EPI_ACCUMULATE; g.out_f32 = p.h; g.ldo = p.H;
-            run_product<MT>(p, g, red, cta_best);
+            if (!(p.skip_mask & 8)) run_product<MT>(p, g, red, cta_best);
             prefetch_tiles(lw.w_up, p.I, p.H);
             grid_barrier(sync);
             // P4: norm2 -> up projection + GELU
             g = Product{};
             if (p.stage_in_smem) {
-                stage_norm(p, lw.ln2_g, lw.ln2_b, false, a_s, lda_s);
+                if (!(p.skip_mask & 1)) stage_norm(p, lw.ln2_g, lw.ln2_b, false, a_s, lda_s);
                 g.a = a_s; g.lda = lda_s;
             } else {
                 norm_to_global(p, lw.ln2_g, lw.ln2_b, false);
@@ -616,14 +621,14 @@ __global__ void __launch_bounds__(THREADS, 3) decode_stack_kernel(const Params p
                 g.a = p.xn; g.lda = p.H;
             }
             g.w = lw.w_up; g.bias = lw.b_up; g.N = p.I; g.K = p.H; g.epilogue = EPI_ACT; g.out_bf16 = p.inner; g.ldo = p.I;
-            run_product<MT>(p, g, red, cta_best);
+            if (!(p.skip_mask & 16)) run_product<MT>(p, g, red, cta_best);
             prefetch_tiles(lw.w_down, p.H, p.I);
             grid_barrier(sync);
             // P5: down projection into the stream
             g = Product{};
             g.a = p.inner; g.lda = p.I; g.w = lw.w_down; g.bias = lw.b_down; g.N = p.H; g.K = p.I;
             g.epilogue = EPI_ACCUMULATE; g.out_f32 = p.h; g.ldo = p.H;
-            run_product<MT>(p, g, red, cta_best);
+            if (!(p.skip_mask & 32)) run_product<MT>(p, g, red, cta_best);
             if (l + 1 < p.n_layers) prefetch_tiles(p.layers[l + 1].w_qkv, q_width + 2 * kv_width, p.H);
             else prefetch_tiles(p.lm_head, p.V, p.H);
             grid_barrier(sync);
@@ -639,7 +644,7 @@ __global__ void __launch_bounds__(THREADS, 3) decode_stack_kernel(const Params p
             g.a = p.xn; g.lda = p.H;
         }
         g.w = p.lm_head; g.bias = nullptr; g.N = p.V; g.K = p.H; g.epilogue = EPI_LOGITS; g.out_f32 = p.logits; g.ldo = p.V;
-        run_product<MT>(p, g, red, cta_best);
+        if (!(p.skip_mask & 64)) run_product<MT>(p, g, red, cta_best);
         if (p.do_sample) {
             for (int m = threadIdx.x; m < p.B; m += THREADS) {
                 if (cta_best[m]) atomicMax(&p.best[m], cta_best[m]);
@@ -691,9 +696,10 @@ int launch(const Params& p, int sm_limit, cudaStream_t stream) {
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, smem) != cudaSuccess || per_sm < 1)
         return PS_ERR_LAUNCH;
     if (per_sm > 3) per_sm = 3;
+    if (p.ctas_per_sm > 0 && p.ctas_per_sm < per_sm) per_sm = p.ctas_per_sm;
     if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
     dim3 grid(sms * per_sm);
-    if (cudaMemsetAsync(p.barrier, 0, sizeof(unsigned int), stream) != cudaSuccess) return PS_ERR_LAUNCH;
+    if (cudaMemsetAsync(p.barrier, 0, 64 * sizeof(unsigned int), stream) != cudaSuccess) return PS_ERR_LAUNCH;
     void* args[] = {const_cast<Params*>(&p)};
     cudaError_t e = cudaLaunchCooperativeKernel((void*)kernel, grid, dim3(THREADS), args, smem, stream);
     return e == cudaSuccess ? PS_OK : PS_ERR_LAUNCH;

@@ -37,7 +37,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
                    const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K,
                    int act, int accumulate) {
     extern __shared__ float red[];                 // [WARPS][16][8*MT]
-    constexpr int UNROLL = 4;
+    constexpr int UNROLL = 6;                      // K = 3072 over 16 warps is one round of loads
     pdl_prologue();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -187,10 +187,12 @@ __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int ldw,
                          const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K,
                          int act, int accumulate, KvScatter kv) {
-    extern __shared__ float red[];                 // [WARPS][16][8*MT], then stats [8*MT][2]
+    // shared memory: cross-warp sums [WARPS][16][8*MT] floats, then the normed rows [8*MT][K+8] bf16
+    extern __shared__ __align__(16) float red[];
     constexpr int UNROLL = 6;
     constexpr int TOK = 8 * MT;
-    float* stats = red + (size_t)WARPS * 16 * TOK;
+    const int lda_s = K + 8;                       // padded: 16-byte reads of 8 rows hit 8 different bank groups
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(red + (size_t)WARPS * 16 * TOK);
     pdl_prologue();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -200,7 +202,7 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
     const __nv_bfloat16* w1 = W + (size_t)r1 * ldw + 8 * t;
     const int steps = (K + 31) >> 5;
 
-    // first batch of weight loads: in flight while the statistics are computed
+    // first batch of weight loads: in flight while the rows are normed
     uint4 wa[UNROLL], wb[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -209,30 +211,60 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         wa[u] = ok ? ldg_stream(w0 + k) : make_uint4(0, 0, 0, 0);
         wb[u] = ok ? ldg_stream(w1 + k) : make_uint4(0, 0, 0, 0);
     }
-    // statistics: one warp per row
+    // norm: one warp per row; the row sits in registers (float4 pieces, all loads issued at once) when
+    // K <= 1024, else it is read again from L1
+    const int quads = K >> 2;
     for (int m = warp; m < M; m += WARPS) {
-        const float* xr = in.x + (size_t)(in.rows ? in.rows[m] : m) * in.ldx;
+        const float4* xr = reinterpret_cast<const float4*>(in.x + (size_t)(in.rows ? in.rows[m] : m) * in.ldx);
+        constexpr int HOLD = 8;
+        float4 v[HOLD];
         float sum = 0.f;
-        for (int k = lane; k < K; k += 32) sum += xr[k];
-        float mean = in.has_mean ? warp_sum(sum) / (float)K : 0.f;
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            int c = lane + 32 * i;
+            v[i] = c < quads ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+        for (int c = lane + 32 * HOLD; c < quads; c += 32) { float4 y = xr[c]; sum += (y.x + y.y) + (y.z + y.w); }
+        const float mean = in.has_mean ? warp_sum(sum) / (float)K : 0.f;
         float sq = 0.f;
-        for (int k = lane; k < K; k += 32) { float d = xr[k] - mean; sq += d * d; }
-        float rstd = rsqrtf(warp_sum(sq) / (float)K + in.eps);
-        if (lane == 0) { stats[2 * m] = mean; stats[2 * m + 1] = rstd; }
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            if (lane + 32 * i < quads) {
+                float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+                sq += (a * a + b * b) + (c * c + d * d);
+            }
+        }
+        for (int c = lane + 32 * HOLD; c < quads; c += 32) {
+            float4 y = xr[c];
+            float a = y.x - mean, b = y.y - mean, cc = y.z - mean, d = y.w - mean;
+            sq += (a * a + b * b) + (cc * cc + d * d);
+        }
+        const float rstd = rsqrtf(warp_sum(sq) / (float)K + in.eps);
+        const float4* g4 = reinterpret_cast<const float4*>(in.gamma);
+        const float4* b4 = reinterpret_cast<const float4*>(in.beta);
+        for (int c = lane; c < quads; c += 32) {
+            const int i = c >> 5;
+            float4 y = (i < HOLD) ? make_float4(0.f, 0.f, 0.f, 0.f) : xr[c];
+#pragma unroll
+            for (int j = 0; j < HOLD; ++j) if (j == i) y = v[j];
+            const float4 gm = g4[c];
+            const float4 bt = in.beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            __nv_bfloat162 lo = __floats2bfloat162_rn((y.x - mean) * rstd * gm.x + bt.x, (y.y - mean) * rstd * gm.y + bt.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn((y.z - mean) * rstd * gm.z + bt.z, (y.w - mean) * rstd * gm.w + bt.w);
+            *reinterpret_cast<uint2*>(a_s + (size_t)m * lda_s + 4 * c) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
     }
     __syncthreads();
 
-    const float* xrow[MT];
-    float mean[MT], rstd[MT];
+    const __nv_bfloat16* arow[MT];
     bool aok[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         int m = 8 * mt + g;
         aok[mt] = m < M;
-        int mm = aok[mt] ? m : 0;
-        xrow[mt] = in.x + (size_t)(in.rows ? in.rows[mm] : mm) * in.ldx + 8 * t;
-        mean[mt] = stats[2 * mm];
-        rstd[mt] = stats[2 * mm + 1];
+        arow[mt] = a_s + (size_t)(aok[mt] ? m : 0) * lda_s + 8 * t;
     }
     float acc[MT][4];
 #pragma unroll
@@ -257,27 +289,10 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
             if (!ok) continue;
             uint32_t a1[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
             uint32_t a2[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
-            const float4 ga = *reinterpret_cast<const float4*>(in.gamma + k + 8 * t);
-            const float4 gb = *reinterpret_cast<const float4*>(in.gamma + k + 8 * t + 4);
-            float4 ba = make_float4(0, 0, 0, 0), bb = ba;
-            if (in.beta) {
-                ba = *reinterpret_cast<const float4*>(in.beta + k + 8 * t);
-                bb = *reinterpret_cast<const float4*>(in.beta + k + 8 * t + 4);
-            }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                uint32_t b1[2] = {0, 0}, b2[2] = {0, 0};
-                if (aok[mt]) {
-                    const float4 xa = *reinterpret_cast<const float4*>(xrow[mt] + k);
-                    const float4 xb = *reinterpret_cast<const float4*>(xrow[mt] + k + 4);
-                    const float mu = mean[mt], rs = rstd[mt];
-                    __nv_bfloat162 p0 = __floats2bfloat162_rn((xa.x - mu) * rs * ga.x + ba.x, (xa.y - mu) * rs * ga.y + ba.y);
-                    __nv_bfloat162 p1 = __floats2bfloat162_rn((xa.z - mu) * rs * ga.z + ba.z, (xa.w - mu) * rs * ga.w + ba.w);
-                    __nv_bfloat162 p2 = __floats2bfloat162_rn((xb.x - mu) * rs * gb.x + bb.x, (xb.y - mu) * rs * gb.y + bb.y);
-                    __nv_bfloat162 p3 = __floats2bfloat162_rn((xb.z - mu) * rs * gb.z + bb.z, (xb.w - mu) * rs * gb.w + bb.w);
-                    b1[0] = *reinterpret_cast<uint32_t*>(&p0); b1[1] = *reinterpret_cast<uint32_t*>(&p1);
-                    b2[0] = *reinterpret_cast<uint32_t*>(&p2); b2[1] = *reinterpret_cast<uint32_t*>(&p3);
-                }
+                uint4 x = aok[mt] ? *reinterpret_cast<const uint4*>(arow[mt] + k) : make_uint4(0, 0, 0, 0);
+                uint32_t b1[2] = {x.x, x.y}, b2[2] = {x.z, x.w};
                 mma_bf16_16816(acc[mt], a1, b1);
                 mma_bf16_16816(acc[mt], a2, b2);
             }
@@ -323,15 +338,14 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
 template <int MT, int WARPS, typename TOut>
 int launch_skinny_fused(const NormInput& in, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
                         int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
-    size_t smem = (size_t)(WARPS * 16 * 8 * MT + 16 * MT) * sizeof(float);
+    size_t smem = (size_t)WARPS * 16 * 8 * MT * sizeof(float) + (size_t)8 * MT * (K + 8) * 2;
     auto kernel = gemm_skinny_fused_kernel<MT, WARPS, TOut>;
-    if (smem > 48 * 1024) {
-        static bool raised = false;
-        if (!raised) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                return PS_ERR_LAUNCH;
-            raised = true;
-        }
+    if (smem > 200 * 1024) return PS_ERR_UNSUPPORTED;
+    static size_t raised = 48 * 1024;
+    if (smem > raised) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return PS_ERR_LAUNCH;
+        raised = smem;
     }
     return launch_pdl(kernel, dim3((N + 15) / 16), dim3(WARPS * 32), smem, s, in, (const __nv_bfloat16*)W, ldw, bias,
                       (TOut*)out, ldo, M, N, K, act, accumulate, kv);

@@ -221,10 +221,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const bool full_chunk = n + 32 <= N;
                     float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(r[j]);
-                        if (bias && (full_chunk || n + j < N)) x += bias[n + j];
-                        v[j] = apply_act(x, act);
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (bias) {
+                        if (full_chunk && ((((uintptr_t)(bias + n)) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 b4 = *reinterpret_cast<const float4*>(bias + n + j);
+                                v[j] += b4.x; v[j + 1] += b4.y; v[j + 2] += b4.z; v[j + 3] += b4.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < N) v[j] += bias[n + j];
+                        }
+                    }
+                    if (act != PS_ACT_NONE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
                     }
                     if constexpr (sizeof(TOut) == 2) {
                         if (full_chunk && ((((uintptr_t)(orow + n)) & 15) == 0)) {
@@ -242,7 +255,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 *reinterpret_cast<uint4*>(orow + n + j) = pack;
                             }
                         } else {
-                            for (int j = 0; j < 32 && n + j < N; ++j) orow[n + j] = from_float<TOut>(v[j]);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < N) orow[n + j] = from_float<TOut>(v[j]);
                         }
                     } else {
                         if (full_chunk && ((((uintptr_t)(orow + n)) & 15) == 0)) {
@@ -257,10 +272,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 *dst = o;
                             }
                         } else {
-                            for (int j = 0; j < 32 && n + j < N; ++j) {
-                                float x = v[j];
-                                if (accumulate) x += to_float(orow[n + j]);
-                                orow[n + j] = from_float<TOut>(x);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (n + j < N) {
+                                    float x = v[j];
+                                    if (accumulate) x += to_float(orow[n + j]);
+                                    orow[n + j] = from_float<TOut>(x);
+                                }
                             }
                         }
                     }

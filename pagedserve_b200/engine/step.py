@@ -74,7 +74,9 @@ class ModelRunner:
         self._step_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the persistent decode kernel, when the model's parts allow it
         self.decode_stack = None
-        if enable_cuda_graphs and os.environ.get("PAGEDSERVE_B200_NO_DECODE_STACK") is None:
+        # (opt-in: measured on B200 its ~62 grid barriers per step cost as much as the launch gaps they
+        # replace, and the graph of separate kernels is currently faster)
+        if enable_cuda_graphs and os.environ.get("PAGEDSERVE_B200_DECODE_STACK") is not None:
             from pagedserve_b200.kernels.decode_stack import DecodeStack
 
             self.decode_stack = DecodeStack.build_if_possible(model, cache, self.device)

@@ -10,6 +10,7 @@ general path (one kernel per operation, captured as a CUDA graph).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -40,7 +41,7 @@ class _Params(ctypes.Structure):
         + [("chunk_keys", _i), ("split_chunks", _i), ("n_splits", _i)]
         + [(name, _p) for name in ("logits", "temperature", "seed", "best", "sampled", "history", "step_counter")]
         + [("max_steps", _i)]
-        + [("barrier", _p), ("status", _p)]
+        + [("barrier", _p), ("status", _p), ("skip_mask", _i), ("ctas_per_sm", _i)]
     )
 
 
@@ -101,7 +102,9 @@ class DecodeStack:
         self.inner = torch.empty(B, self.I, dtype=bf16, device=device)
         self.counters = torch.zeros(B * self.n_heads, dtype=torch.int32, device=device)
         self.best = torch.zeros(B, dtype=torch.int64, device=device)
-        self.barrier = torch.zeros(1, dtype=torch.int32, device=device)
+        self.barrier = torch.zeros(64, dtype=torch.int32, device=device)
+        self.skip_mask = 0          # timing aid (see csrc/decode_stack.cu); results are wrong when non-zero
+        self.ctas_per_sm = int(os.environ.get("PAGEDSERVE_B200_STACK_CTAS", "0"))
         self.logits = None
         self.part_acc = self.part_ml = None
         self.sms = torch.cuda.get_device_properties(device).multi_processor_count
@@ -151,7 +154,7 @@ class DecodeStack:
             raise KernelError("decode_stack takes decode-only batches of at most 64 requests")
         group = self.group
         chunk = Ops.attention_chunk_keys(self.head_dim, group.page_size)
-        grid = self.sms * 3
+        grid = self.sms * (self.ctas_per_sm or 3)
         chunks = max(1, -(-int(max_kv_len) // chunk))
         wanted = max(1, -(-grid // (B * self.n_heads)))
         split_chunks = max(1, -(-chunks // wanted))
@@ -178,7 +181,7 @@ class DecodeStack:
             _ptr(self.part_ml), _ptr(self.counters), chunk, split_chunks, n_splits,
             _ptr(logits), _ptr(ctx.temperature if do_sample else None), _ptr(ctx.seed if do_sample else None),
             _ptr(self.best), _ptr(sampled), _ptr(history), _ptr(step_counter), max_steps,
-            _ptr(self.barrier), _ptr(ctx.status))
+            _ptr(self.barrier), _ptr(ctx.status), self.skip_mask, self.ctas_per_sm)
         status = self.lib.ps_decode_stack(ctypes.byref(params), _i(0),
                                           _p(torch.cuda.current_stream().cuda_stream))
         if status != 0:

@@ -17,11 +17,26 @@ import sys
 import torch
 
 
-def _time(fn, iters, warmup=3):
-    for _ in range(warmup):
-        fn(0)
+def _time(fn, iters, warmup=3, graph=False):
+    """Seconds per call.  ``graph``: the calls are captured into one CUDA graph and replayed, which takes
+    the host's launch cost out of the figure (needed for kernels of a few microseconds)."""
+    for i in range(warmup):
+        fn(i)
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            for i in range(iters):
+                fn(i)
+        captured.replay()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(5):
+            captured.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / (5 * iters) * 1e-3
     start.record()
     for i in range(iters):
         fn(i)
@@ -53,7 +68,7 @@ def bench_gemm(args):
         else:
             ops.linear_simt(a[j], w[j], bias, out, act=args.act)
 
-    seconds = _time(run, args.iters)
+    seconds = _time(run, args.iters, graph=args.graph)
     flops = 2.0 * M * N * K
     print(f"gemm {args.impl} M={M} N={N} K={K} bn={args.bn} out={args.out}: {seconds * 1e6:.2f} us, "
           f"{flops / seconds / 1e12:.1f} TFLOP/s, weight stream {N * K * 2 / seconds / 1e9:.0f} GB/s, "
@@ -81,7 +96,7 @@ def bench_attention(args):
         ops.paged_attention_decode(q, out, pool[:, layer, 0], pool[:, layer, 1], stride, token_item, positions, table,
                                    H, H, D, page, None, D ** -0.5, args.max_context or ctx, status=status)
 
-    seconds = _time(run, args.iters)
+    seconds = _time(run, args.iters, graph=args.graph)
     nbytes = B * ctx * H * D * 2 * 2
     print(f"decode attention B={B} ctx={ctx} heads={H} hd={D} page={page}: {seconds * 1e6:.2f} us, "
           f"{nbytes / seconds / 1e9:.0f} GB/s of K+V, status {int(status.item())}")
@@ -99,6 +114,7 @@ def main(argv=None):
     g.add_argument("--act", default=None)
     g.add_argument("--out", default="bfloat16", choices=("bfloat16", "float32"))
     g.add_argument("--iters", type=int, default=50)
+    g.add_argument("--graph", action="store_true", help="replay the calls as one CUDA graph")
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, default=64)
     a.add_argument("--context", type=int, default=640)
@@ -107,6 +123,7 @@ def main(argv=None):
     a.add_argument("--head-dim", type=int, default=64)
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--iters", type=int, default=50)
+    a.add_argument("--graph", action="store_true", help="replay the calls as one CUDA graph")
     args = parser.parse_args(argv)
     if args.kind == "gemm":
         bench_gemm(args)

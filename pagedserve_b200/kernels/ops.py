@@ -32,11 +32,52 @@ class KernelError(RuntimeError):
 
 
 def _ptr(tensor: Optional[torch.Tensor]):
-    return _c_void_p(tensor.data_ptr()) if tensor is not None else _c_void_p(0)
+    return tensor.data_ptr() if tensor is not None else None
+
+
+# Argument types of the entry points, declared once: ctypes then converts plain Python ints, floats and
+# None itself, which is several times cheaper per call than building c_int / c_void_p objects.
+_P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+_SIGNATURES = {
+    "core": {
+        "ps_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "ps_layernorm": [_P, _P, _I, _I, _P, _P, _F, _I, _P, _I, _P],
+        "ps_gemm_simt": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ps_kv_append": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+        "ps_paged_attention_simt": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
+        "ps_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+    },
+    "bf16": {
+        "ps_gemm_skinny": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ps_gemm_skinny_fused": [_P, _I, _P, _P, _P, _F, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                 _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ps_paged_attention_decode_checked": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                              _F, _I, _I, _P, _P, _P, _P, _P],
+        "ps_prefill_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+    },
+    "tc": {
+        "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+    },
+}
+
+
+def _declare(lib, name: str):
+    for function, argtypes in _SIGNATURES[name].items():
+        handle = getattr(lib, function)
+        handle.argtypes = argtypes
+        handle.restype = ctypes.c_int
+    return lib
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def _stream():
-    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current CUDA stream's handle (the fast private lookup when torch has it)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _require(tensor: torch.Tensor, name: str, dtype=None):
@@ -65,8 +106,8 @@ class Ops:
             raise KernelError(f"unsupported compute dtype {dtype}")
         self.dtype = dtype
         self.code = _DTYPE_CODE[dtype]
-        self.core = _load_library("core")
-        self.fast = _load_library("bf16") if dtype == torch.bfloat16 else None
+        self.core = _declare(_load_library("core"), "core")
+        self.fast = _declare(_load_library("bf16"), "bf16") if dtype == torch.bfloat16 else None
         self._tc = None              # tcgen05 library, loaded when a product first needs it
         self._tc_status = None
         self._counters = None        # zeroed int32 scratch of the split attention kernel
@@ -88,8 +129,8 @@ class Ops:
             raise KernelError("embed: shapes do not match")
         self.launches += 1
         _check(self.core.ps_embed(_ptr(ids), _ptr(positions if wpe is not None else None), _ptr(wte), _ptr(wpe),
-                                  _ptr(out), _c_int(T), _c_int(H), _c_int(wte.shape[0]),
-                                  _c_int(wpe.shape[0] if wpe is not None else 0), _c_int(self.code),
+                                  _ptr(out), T, H, wte.shape[0],
+                                  wpe.shape[0] if wpe is not None else 0, self.code,
                                   _ptr(status), _stream()), "embed")
         return out
 
@@ -111,9 +152,9 @@ class Ops:
         if not x.is_contiguous() or not out.is_contiguous():
             raise KernelError("layernorm: tensors must be contiguous")
         self.launches += 1
-        _check(self.core.ps_layernorm(_ptr(x), _ptr(rows), _c_int(n_rows), _c_int(H), _ptr(gamma), _ptr(beta),
-                                      _c_float(eps), _c_int(1 if has_mean else 0), _ptr(out),
-                                      _c_int(dtype_code(out.dtype)), _stream()), "layernorm")
+        _check(self.core.ps_layernorm(_ptr(x), _ptr(rows), n_rows, H, _ptr(gamma), _ptr(beta),
+                                      eps, 1 if has_mean else 0, _ptr(out),
+                                      dtype_code(out.dtype), _stream()), "layernorm")
         return out
 
     # ------------------------------------------------------------------ matrix product
@@ -135,10 +176,10 @@ class Ops:
         if accumulate and out.dtype != torch.float32:
             raise KernelError("linear: accumulate needs a float32 output")
         self.launches += 1
-        _check(self.core.ps_gemm_simt(_ptr(a), _c_int(a.stride(0)), _ptr(w), _c_int(w.stride(0)), _ptr(bias),
-                                      _ptr(out), _c_int(out.stride(0)), _c_int(M), _c_int(N), _c_int(K),
-                                      _c_int(dtype_code(a.dtype)), _c_int(dtype_code(out.dtype)),
-                                      _c_int(_ACT_CODE[act]), _c_int(1 if accumulate else 0), _stream()),
+        _check(self.core.ps_gemm_simt(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias),
+                                      _ptr(out), out.stride(0), M, N, K,
+                                      dtype_code(a.dtype), dtype_code(out.dtype),
+                                      _ACT_CODE[act], 1 if accumulate else 0, _stream()),
                "gemm_simt")
         return out
 
@@ -156,10 +197,10 @@ class Ops:
         if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
             raise KernelError("linear_skinny: innermost stride must be 1")
         self.launches += 1
-        _check(self.fast.ps_gemm_skinny(_ptr(a), _c_int(a.stride(0)), _ptr(w), _c_int(w.stride(0)), _ptr(bias),
-                                        _ptr(out), _c_int(out.stride(0)), _c_int(M), _c_int(N), _c_int(K),
-                                        _c_int(dtype_code(out.dtype)), _c_int(_ACT_CODE[act]),
-                                        _c_int(1 if accumulate else 0), _stream()), "gemm_skinny")
+        _check(self.fast.ps_gemm_skinny(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias),
+                                        _ptr(out), out.stride(0), M, N, K,
+                                        dtype_code(out.dtype), _ACT_CODE[act],
+                                        1 if accumulate else 0, _stream()), "gemm_skinny")
         return out
 
     def linear_tc(self, a, w, bias, out, act=None, accumulate=False, status=None, bn=0):
@@ -176,16 +217,16 @@ class Ops:
         if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
             raise KernelError("linear_tc: innermost stride must be 1")
         if self._tc is None:
-            self._tc = _load_library("tc")
+            self._tc = _declare(_load_library("tc"), "tc")
         if status is None:
             if self._tc_status is None:
                 self._tc_status = torch.zeros(1, dtype=torch.int32, device=a.device)
             status = self._tc_status
         self.launches += 1
-        _check(self._tc.ps_gemm_tc(_ptr(a), _c_int(a.stride(0)), _ptr(w), _c_int(w.stride(0)), _ptr(bias), _ptr(out),
-                                   _c_int(out.stride(0)), _c_int(M), _c_int(N), _c_int(K),
-                                   _c_int(dtype_code(out.dtype)), _c_int(_ACT_CODE[act]),
-                                   _c_int(1 if accumulate else 0), _ptr(status), _c_int(bn), _stream()), "gemm_tc")
+        _check(self._tc.ps_gemm_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
+                                   out.stride(0), M, N, K,
+                                   dtype_code(out.dtype), _ACT_CODE[act],
+                                   1 if accumulate else 0, _ptr(status), bn, _stream()), "gemm_tc")
         return out
 
     @staticmethod
@@ -205,6 +246,9 @@ class Ops:
     def _fused_norm_ok(self, a, w):
         norm = a.norm
         # every CTA (16 output columns) recomputes the statistics: worth it only while the product is narrow
+        rows = 8 if a.shape[0] <= 8 else 16 if a.shape[0] <= 16 else 32
+        if rows * (a.shape[1] + 8) * 2 > 96 * 1024:          # the normed rows are staged in shared memory
+            return False
         return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS and w.shape[0] <= 8192
                 and type(norm).__name__ == "LayerNorm" and a.x.dtype == torch.float32
                 and a.shape[1] % 8 == 0 and a.x.stride(0) % 4 == 0 and a.x.stride(1) == 1
@@ -225,18 +269,18 @@ class Ops:
         _require(out, "out")
         if kv is not None:
             ctx, layer, q_width, kv_width, head_dim = kv
-            kv_args = (_ptr(layer.k_pool), _ptr(layer.v_pool), _c_ll(layer.page_stride), _ptr(ctx.token_item),
-                       _ptr(ctx.positions), _ptr(layer.block_table), _c_int(layer.block_table.stride(0)),
-                       _c_int(q_width), _c_int(kv_width), _c_int(head_dim), _c_int(layer.page_size))
+            kv_args = (_ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride, _ptr(ctx.token_item),
+                       _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
+                       q_width, kv_width, head_dim, layer.page_size)
         else:
-            kv_args = (_c_void_p(0), _c_void_p(0), _c_ll(0), _c_void_p(0), _c_void_p(0), _c_void_p(0), _c_int(0),
-                       _c_int(N), _c_int(0), _c_int(1), _c_int(1))
+            kv_args = (None, None, 0, None, None, None, 0,
+                       N, 0, 1, 1)
         self.launches += 1
         _check(self.fast.ps_gemm_skinny_fused(
-            _ptr(a.x), _c_int(a.x.stride(0)), _ptr(a.rows), _ptr(norm.weight), _ptr(norm.bias),
-            _c_float(float(norm.params["eps"])), _c_int(1 if norm.params.get("has_mean", True) else 0),
-            _ptr(w), _c_int(w.stride(0)), _ptr(bias), _ptr(out), _c_int(out.stride(0)), _c_int(M), _c_int(N),
-            _c_int(K), _c_int(dtype_code(out.dtype)), _c_int(_ACT_CODE[act]), _c_int(1 if accumulate else 0),
+            _ptr(a.x), a.x.stride(0), _ptr(a.rows), _ptr(norm.weight), _ptr(norm.bias),
+            float(norm.params["eps"]), 1 if norm.params.get("has_mean", True) else 0,
+            _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N,
+            K, dtype_code(out.dtype), _ACT_CODE[act], 1 if accumulate else 0,
             *kv_args, _stream()), "gemm_skinny_fused")
         return out
 
@@ -273,11 +317,11 @@ class Ops:
         if k_src.stride(1) != 1 or v_src.stride(1) != 1 or k_src.stride(0) != v_src.stride(0):
             raise KernelError("kv_append: k and v must be row views with equal row stride")
         self.launches += 1
-        _check(self.core.ps_kv_append(_ptr(k_src), _ptr(v_src), _c_int(k_src.stride(0)), _ptr(token_item),
-                                      _ptr(positions), _ptr(block_table), _c_int(block_table.stride(0)),
-                                      _ptr(k_pool), _ptr(v_pool), _c_ll(page_stride), _c_int(T),
-                                      _c_int(n_kv_heads), _c_int(head_dim), _c_int(page_size),
-                                      _c_int(self.code), _stream()), "kv_append")
+        _check(self.core.ps_kv_append(_ptr(k_src), _ptr(v_src), k_src.stride(0), _ptr(token_item),
+                                      _ptr(positions), _ptr(block_table), block_table.stride(0),
+                                      _ptr(k_pool), _ptr(v_pool), page_stride, T,
+                                      n_kv_heads, head_dim, page_size,
+                                      self.code, _stream()), "kv_append")
 
     def paged_attention_simt(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
                              n_heads, n_kv_heads, head_dim, page_size, window, scale):
@@ -289,10 +333,10 @@ class Ops:
             raise KernelError("attention: innermost stride must be 1")
         self.launches += 1
         _check(self.core.ps_paged_attention_simt(
-            _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(k_pool), _ptr(v_pool),
-            _c_ll(page_stride), _ptr(token_item), _ptr(positions), _ptr(block_table),
-            _c_int(block_table.stride(0)), _c_int(T), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
-            _c_int(page_size), _c_int(window or 0), _c_float(scale), _c_int(self.code), _stream()),
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
+            page_stride, _ptr(token_item), _ptr(positions), _ptr(block_table),
+            block_table.stride(0), T, n_heads, n_kv_heads, head_dim,
+            page_size, window or 0, scale, self.code, _stream()),
             "paged_attention_simt")
         return out
 
@@ -332,10 +376,10 @@ class Ops:
             part_ml = torch.empty((T * n_heads * n_splits, 2), dtype=torch.float32, device=q.device)
         self.launches += 1
         _check(self.fast.ps_paged_attention_decode_checked(
-            _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(k_pool), _ptr(v_pool),
-            _c_ll(page_stride), _ptr(token_item), _ptr(positions), _ptr(block_table),
-            _c_int(block_table.stride(0)), _c_int(T), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
-            _c_int(page_size), _c_int(window or 0), _c_float(scale), _c_int(split_tiles), _c_int(n_splits),
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
+            page_stride, _ptr(token_item), _ptr(positions), _ptr(block_table),
+            block_table.stride(0), T, n_heads, n_kv_heads, head_dim,
+            page_size, window or 0, scale, split_tiles, n_splits,
             _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(status), _stream()), "paged_attention_decode")
         return out
 
@@ -350,10 +394,10 @@ class Ops:
             raise KernelError("prefill_attention: head sizes above 128 are not supported")
         self.launches += 1
         _check(self.fast.ps_prefill_attention(
-            _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(k_pool), _ptr(v_pool),
-            _c_ll(page_stride), _ptr(q_start), _ptr(kv_len), _ptr(block_table), _c_int(block_table.stride(0)),
-            _c_int(first_item), _c_int(n_items), _c_int(max_blocks), _c_int(n_heads), _c_int(n_kv_heads),
-            _c_int(head_dim), _c_int(page_size), _c_int(window or 0), _c_float(scale), _stream()),
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
+            page_stride, _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0),
+            first_item, n_items, max_blocks, n_heads, n_kv_heads,
+            head_dim, page_size, window or 0, scale, _stream()),
             "prefill_attention")
         return out
 
@@ -383,8 +427,8 @@ class Ops:
             _require(seed, "seed", torch.int64)
             _require(position, "position", torch.int32)
         self.launches += 1
-        _check(self.core.ps_sample(_ptr(logits), _c_int(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
-                                   _ptr(seed), _ptr(position), _c_int(pos_offset), _ptr(out), _stream()),
+        _check(self.core.ps_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature),
+                                   _ptr(seed), _ptr(position), pos_offset, _ptr(out), _stream()),
                "sample")
         return out
 
@@ -393,5 +437,5 @@ class Ops:
         B = sampled.numel()
         self.launches += 1
         _check(self.core.ps_advance(_ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(kv_len), _ptr(history),
-                                    _ptr(step_counter), _c_int(B), _c_int(max_steps), _stream()),
+                                    _ptr(step_counter), B, max_steps, _stream()),
                "advance")
