@@ -25,11 +25,15 @@ namespace ps {
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
 
+// elements between units in shared memory: the unit's bytes padded so that the stride is 16 (mod 128)
+__host__ __device__ inline int attention_unit_stride(int unit, int head_dim) {
+    const int bytes = unit * head_dim * 2;
+    return (bytes + ((16 - bytes % 128) + 128) % 128) / 2;
+}
+
 __host__ __device__ inline int attention_chunk_keys(int head_dim, int page_size) {
-    int keys = (8192 / head_dim) & ~31;
-    if (keys > DEC_THREADS) keys = DEC_THREADS;
+    int keys = head_dim <= 64 ? 128 : (head_dim <= 128 ? 64 : 32);     // a power of two, K + V of a chunk <= 32 KB
     if (keys < page_size) keys = page_size;
-    if (keys < 32) keys = 32;
     return keys;
 }
 
@@ -66,7 +70,33 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32
         ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
 }
 
-__global__ void __launch_bounds__(DEC_THREADS)
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Scores and p.V on tensor cores although there is one query: keys (then head dims) sit on the 16-row
+// side of mma.sync.m16n8k16 and the query (then the probabilities) is column 0 of the 8-column side.
+//   S^T[key]  = sum_d K[key][d] q[d]        A = K rows from shared memory (ldmatrix),   B = q in lanes g == 0
+//   O^T[d]    = sum_key V[key][d] p[key]    A = V^T (ldmatrix.trans),                   B = p in lanes g == 0
+// A chunk is copied in units of U consecutive keys of one page (one bulk copy for K, one for V; U = 16 at
+// head size 64). In shared memory the units lie `unit_stride` bytes apart with unit_stride = 16 (mod 128),
+// and MMA row m of the chunk is key (m mod NU) * U + m / NU (NU units per chunk): the 8 rows of every
+// ldmatrix then come from 8 different units and fall on 8 different bank groups, although each unit is a
+// plain contiguous copy. Keys outside [lo, p] have their V rows zeroed and their scores masked.
+// KS: head-dim steps of 16 the kernel is compiled for (head_dim <= 16 * KS); fewer steps, fewer registers.
+template <int KS>
+__global__ void __launch_bounds__(DEC_THREADS, KS == 4 ? 6 : (KS == 8 ? 4 : 2))
 paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               __nv_bfloat16* __restrict__ out, int out_stride,
                               const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
@@ -77,11 +107,15 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               float* __restrict__ part_acc, float* __restrict__ part_ml,
                               int* __restrict__ counters, int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [chunk_keys][head_dim]
-    __nv_bfloat16* v_s = k_s + (size_t)chunk_keys * head_dim;                        // [chunk_keys][head_dim]
-    float* q_s = reinterpret_cast<float*>(v_s + (size_t)chunk_keys * head_dim);      // [head_dim]
-    float* p_s = q_s + head_dim;                                                     // [chunk_keys]
-    float* acc_s = p_s + chunk_keys;                                                 // [DEC_WARPS][head_dim]
+    const int unit = min(page_size, chunk_keys >> 3);                                // keys per copy
+    const int n_units = chunk_keys / unit;                                           // >= 8
+    const int unit_elems = attention_unit_stride(unit, head_dim);                    // padded unit, elements
+    // One stage of chunk buffers: measured on B200, a second stage (copying the next chunk during the
+    // compute of this one) halves the CTAs per SM and was slower at every batch size (batch 64: 44 vs 36 us).
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [n_units][unit_elems]
+    __nv_bfloat16* v_s = k_s + (size_t)n_units * unit_elems;
+    __nv_bfloat16* p_s = v_s + (size_t)n_units * unit_elems;                         // [chunk_keys] probabilities
+    float* o_s = reinterpret_cast<float*>(p_s + chunk_keys);                         // [head_dim] merged output
     __shared__ float red_a[DEC_WARPS], red_b[DEC_WARPS];
     __shared__ __align__(8) uint64_t bar;
     __shared__ int last_flag;
@@ -89,6 +123,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     pdl_prologue();
     const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, tq = lane & 3;
     const int p = positions[t];
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
@@ -104,119 +139,157 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         mbar_init(&bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int d = tid; d < head_dim; d += DEC_THREADS)
-        q_s[d] = __bfloat162float(q[(size_t)t * q_stride + h * head_dim + d]) * scale_log2;
+    // the query as B fragments: lanes with g == 0 hold q[16 ks + 2 t .. +1] and q[16 ks + 2 t + 8 .. +9]
+    const int ksteps = head_dim >> 4;                              // <= KS
+    uint32_t qb[KS][2];
+    {
+        const __nv_bfloat16* qrow = q + (size_t)t * q_stride + h * head_dim;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qb[ks][0] = qb[ks][1] = 0u;
+            if (ks < ksteps && gq == 0) {
+                qb[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * tq);
+                qb[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * tq + 8);
+            }
+        }
+    }
     __syncthreads();
 
-    float acc[4][2];
+    // this warp owns the output rows (head dims) of m-tiles warp, warp + 4, ...
+    constexpr int OT = (KS + DEC_WARPS - 1) / DEC_WARPS;          // output tiles per warp
+    float o_acc[OT][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = 0.f;
+    for (int i = 0; i < OT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
-    const int row_chunks = head_dim >> 3;                      // 16-byte pieces of a key row
-    const int pages_per_chunk = chunk_keys / page_size;
-    const uint32_t block_bytes = (uint32_t)page_size * head_dim * 2;
+    const uint32_t unit_bytes = (uint32_t)unit * head_dim * 2;
+    const int key_tiles = chunk_keys >> 4;
     uint32_t phase = 0;
     bool ok = true;
 
     for (int chunk = chunk_lo; chunk <= chunk_hi; ++chunk) {
         const int key0 = chunk * chunk_keys;
-        // pages of this chunk that hold keys in [lo, p]
-        const int pg_first = max(lo, key0) / page_size - key0 / page_size;
-        const int pg_last = min(p, key0 + chunk_keys - 1) / page_size - key0 / page_size;
-        if (tid == 0) mbar_expect_tx(&bar, 2u * block_bytes * (uint32_t)(pg_last - pg_first + 1));
-        if (tid >= pg_first && tid <= pg_last && tid < pages_per_chunk) {
-            const int page = bt[key0 / page_size + tid];
-            const long long base = (long long)page * page_stride + (long long)g * page_size * head_dim;
-            bulk_copy_g2s(k_s + (size_t)tid * page_size * head_dim, k_pool + base, block_bytes, &bar);
-            bulk_copy_g2s(v_s + (size_t)tid * page_size * head_dim, v_pool + base, block_bytes, &bar);
+        const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;   // valid keys of the chunk
+        const int u_lo = j_lo / unit, u_hi = j_hi / unit;
+        if (tid == 0) mbar_expect_tx(&bar, 2u * unit_bytes * (uint32_t)(u_hi - u_lo + 1));
+        if (tid >= u_lo && tid <= u_hi) {
+            const int key = key0 + tid * unit;
+            const int page = bt[key / page_size];
+            const long long src = (long long)page * page_stride +
+                                  ((long long)g * page_size + (key % page_size)) * head_dim;
+            bulk_copy_g2s(k_s + (size_t)tid * unit_elems, k_pool + src, unit_bytes, &bar);
+            bulk_copy_g2s(v_s + (size_t)tid * unit_elems, v_pool + src, unit_bytes, &bar);
         }
         if (ok && !mbar_wait_bounded(&bar, phase)) {
             ok = false;
             if (status) atomicExch(status, 2);
         }
         phase ^= 1;
-        // scores: thread j owns key j of the chunk
-        const int kpos = key0 + tid;
-        const bool valid = ok && tid < chunk_keys && kpos >= lo && kpos <= p;
-        float s = -INFINITY;
-        if (valid) {
-            const __nv_bfloat16* kr = k_s + (size_t)tid * head_dim;
-            float dot = 0.f;
-            const int rot = tid % row_chunks;
-            for (int c = 0; c < row_chunks; ++c) {
-                int cc = c + rot;                               // (c + j) mod row_chunks
-                if (cc >= row_chunks) cc -= row_chunks;
-                const uint4 kv = *reinterpret_cast<const uint4*>(kr + 8 * cc);
-                const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
-                const float4 qa = *reinterpret_cast<const float4*>(q_s + 8 * cc);
-                const float4 qb = *reinterpret_cast<const float4*>(q_s + 8 * cc + 4);
-                float2 f0 = __bfloat1622float2(k2[0]), f1 = __bfloat1622float2(k2[1]);
-                float2 f2 = __bfloat1622float2(k2[2]), f3 = __bfloat1622float2(k2[3]);
-                dot = fmaf(qa.x, f0.x, dot); dot = fmaf(qa.y, f0.y, dot);
-                dot = fmaf(qa.z, f1.x, dot); dot = fmaf(qa.w, f1.y, dot);
-                dot = fmaf(qb.x, f2.x, dot); dot = fmaf(qb.y, f2.y, dot);
-                dot = fmaf(qb.z, f3.x, dot); dot = fmaf(qb.w, f3.y, dot);
+        if (tid < chunk_keys) {
+            // MMA row tid is key (tid % n_units) * unit + tid / n_units; rows of keys outside [j_lo, j_hi]
+            // hold stale or no data: 0 * garbage must stay 0
+            const int key = (tid % n_units) * unit + tid / n_units;
+            if (key < j_lo || key > j_hi) {
+                const size_t off = (size_t)(tid % n_units) * unit_elems + (size_t)(tid / n_units) * head_dim;
+                uint4* vz = reinterpret_cast<uint4*>(v_s + off);
+                uint4* kz = reinterpret_cast<uint4*>(k_s + off);
+                for (int c = 0; c < (head_dim >> 3); ++c) { vz[c] = make_uint4(0, 0, 0, 0); kz[c] = make_uint4(0, 0, 0, 0); }
             }
-            s = dot;                                           // already in log2 units
         }
-        float wmax = warp_max(s);
+        __syncthreads();
+        // ---- scores: key tiles warp, warp + 4, ... ; lanes with t == 0 end up with keys g and g + 8
+        float sc[2][2];                                           // [tile of this warp][row g / g+8]
+        float wmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int mt = warp + DEC_WARPS * i;
+            sc[i][0] = sc[i][1] = -INFINITY;
+            if (mt < key_tiles) {
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    if (ks < ksteps) {
+                        uint32_t a[4];
+                        const int m = 16 * mt + (lane & 15);
+                        ldsm_x4(a, k_s + (size_t)(m % n_units) * unit_elems + (size_t)(m / n_units) * head_dim +
+                                       (2 * ks + (lane >> 4)) * 8);
+                        mma_16816(c, a, qb[ks][0], qb[ks][1]);
+                    }
+                }
+                const int ma = 16 * mt + gq, mb = ma + 8;                 // MMA rows -> keys of the chunk
+                const int ka = (ma % n_units) * unit + ma / n_units, kb = (mb % n_units) * unit + mb / n_units;
+                if (tq == 0 && ok) {
+                    if (ka >= j_lo && ka <= j_hi) sc[i][0] = c[0] * scale_log2;
+                    if (kb >= j_lo && kb <= j_hi) sc[i][1] = c[2] * scale_log2;
+                }
+                wmax = fmaxf(wmax, fmaxf(sc[i][0], sc[i][1]));
+            }
+        }
+        wmax = warp_max(wmax);
         if (lane == 0) red_a[warp] = wmax;
         __syncthreads();
-        float cmax = fmaxf(fmaxf(red_a[0], red_a[1]), fmaxf(red_a[2], red_a[3]));
+        const float cmax = fmaxf(fmaxf(red_a[0], red_a[1]), fmaxf(red_a[2], red_a[3]));
         const float m_new = fmaxf(m_run, cmax);
-        const float pr = valid ? exp2f(s - m_new) : 0.f;
-        if (tid < chunk_keys) p_s[tid] = pr;
-        float wsum = warp_sum(pr);
+        float wsum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int mt = warp + DEC_WARPS * i;
+            if (mt < key_tiles && tq == 0) {
+                const float pa = (sc[i][0] == -INFINITY) ? 0.f : exp2f(sc[i][0] - m_new);
+                const float pb = (sc[i][1] == -INFINITY) ? 0.f : exp2f(sc[i][1] - m_new);
+                p_s[16 * mt + gq] = __float2bfloat16_rn(pa);
+                p_s[16 * mt + gq + 8] = __float2bfloat16_rn(pb);
+                wsum += pa + pb;
+            }
+        }
+        wsum = warp_sum(wsum);
         if (lane == 0) red_b[warp] = wsum;
         __syncthreads();
         const float csum = (red_b[0] + red_b[1]) + (red_b[2] + red_b[3]);
         const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
         l_run = l_run * corr + csum;
         m_run = m_new;
+        // ---- O^T += V^T p : this warp's head-dim tiles, all key steps of the chunk
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { acc[i][0] *= corr; acc[i][1] *= corr; }
-        // p.V: warp w takes keys j = w (mod 4); lanes own pairs of head dims
-        const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;
-        int j = j_lo + ((warp - j_lo) & (DEC_WARPS - 1));
-        if (ok)
-            for (; j <= j_hi; j += DEC_WARPS) {
-                const float pj = p_s[j];
-                const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(v_s + (size_t)j * head_dim);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    int d2 = lane + 32 * i;
-                    if (2 * d2 < head_dim) {
-                        float2 v = __bfloat1622float2(vr[d2]);
-                        acc[i][0] = fmaf(pj, v.x, acc[i][0]);
-                        acc[i][1] = fmaf(pj, v.y, acc[i][1]);
+        for (int i = 0; i < OT; ++i) {
+            const int dt = warp + DEC_WARPS * i;
+            if (dt < ksteps) {
+                o_acc[i][0] *= corr; o_acc[i][1] *= corr; o_acc[i][2] *= corr; o_acc[i][3] *= corr;
+                for (int kk = 0; kk < key_tiles; ++kk) {
+                    uint32_t a[4];
+                    const int m = 16 * kk + (lane & 7) + ((lane >> 4) & 1) * 8;
+                    ldsm_x4_trans(a, v_s + (size_t)(m % n_units) * unit_elems + (size_t)(m / n_units) * head_dim +
+                                         (2 * dt + ((lane >> 3) & 1)) * 8);
+                    uint32_t b0 = 0u, b1 = 0u;
+                    if (gq == 0) {
+                        b0 = *reinterpret_cast<const uint32_t*>(p_s + 16 * kk + 2 * tq);
+                        b1 = *reinterpret_cast<const uint32_t*>(p_s + 16 * kk + 2 * tq + 8);
                     }
+                    mma_16816(o_acc[i], a, b0, b1);
                 }
             }
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();                                      // the buffers may be overwritten now
     }
+    // column 0 of the accumulators is the output: lanes with t == 0 hold head dims 16 dt + g and + 8
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        int d = 2 * (lane + 32 * i);
-        if (d < head_dim) {
-            acc_s[warp * head_dim + d] = acc[i][0];
-            acc_s[warp * head_dim + d + 1] = acc[i][1];
+    for (int i = 0; i < OT; ++i) {
+        const int dt = warp + DEC_WARPS * i;
+        if (dt < ksteps && tq == 0) {
+            o_s[16 * dt + gq] = o_acc[i][0];
+            o_s[16 * dt + gq + 8] = o_acc[i][2];
         }
     }
     __syncthreads();
     if (n_splits == 1 || n_active == 1) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        for (int d = tid; d < head_dim; d += DEC_THREADS) {
-            float o = (acc_s[d] + acc_s[head_dim + d]) + (acc_s[2 * head_dim + d] + acc_s[3 * head_dim + d]);
-            out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
-        }
+        for (int d = tid; d < head_dim; d += DEC_THREADS)
+            out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o_s[d] * inv);
         return;
     }
     // several splits hold keys of this token: publish the partial state
     const size_t slot = ((size_t)t * n_heads + h) * n_splits + split;
-    for (int d = tid; d < head_dim; d += DEC_THREADS)
-        part_acc[slot * head_dim + d] =
-            (acc_s[d] + acc_s[head_dim + d]) + (acc_s[2 * head_dim + d] + acc_s[3 * head_dim + d]);
+    for (int d = tid; d < head_dim; d += DEC_THREADS) part_acc[slot * head_dim + d] = o_s[d];
     if (tid == 0) { part_ml[slot * 2] = m_run; part_ml[slot * 2 + 1] = l_run; }
     __threadfence();
     __syncthreads();
@@ -230,7 +303,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __threadfence();
     const size_t base = ((size_t)t * n_heads + h) * n_splits;
     // all (max, sum) pairs at once into shared memory (one trip to L2, not one per split)
-    float* ml_s = p_s;                                        // chunk_keys >= 32 floats: 16 splits fit
+    float* ml_s = reinterpret_cast<float*>(k_s);              // the K buffer is free now
     const bool staged = 2 * n_active <= chunk_keys;
     if (staged) {
         if (tid < 2 * n_active) ml_s[tid] = ldcg_f32(part_ml + (base + first_split) * 2 + tid);
@@ -287,22 +360,30 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
     if ((split_tiles * 32) % chunk_keys != 0) return PS_ERR_BAD_ARGUMENT;
     const int split_chunks = split_tiles * 32 / chunk_keys;
     dim3 grid(T, n_heads, n_splits);
-    size_t smem = (size_t)chunk_keys * head_dim * 2 * 2 + (size_t)(head_dim + chunk_keys + ps::DEC_WARPS * head_dim) * 4;
-    if (smem > 48 * 1024) {
-        static bool raised = false;
-        if (!raised) {
-            if (cudaFuncSetAttribute(ps::paged_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     96 * 1024) != cudaSuccess)
-                return PS_ERR_LAUNCH;
-            raised = true;
-        }
+    const int unit = page_size < (chunk_keys >> 3) ? page_size : (chunk_keys >> 3);
+    size_t smem = (size_t)(chunk_keys / unit) * ps::attention_unit_stride(unit, head_dim) * 2 * 2 +
+                  (size_t)chunk_keys * 2 + (size_t)head_dim * 4;
+    cudaStream_t s = (cudaStream_t)stream;
+#define PS_DECODE_LAUNCH(KS)                                                                                          \
+    {                                                                                                                \
+        auto kernel = ps::paged_attention_decode_kernel<KS>;                                                         \
+        static size_t raised = 48 * 1024;                                                                            \
+        if (smem > raised) {                                                                                         \
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+                return PS_ERR_LAUNCH;                                                                                \
+            raised = smem;                                                                                           \
+        }                                                                                                            \
+        return ps::launch_pdl(kernel, grid, dim3(ps::DEC_THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,       \
+                              (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,                          \
+                              (const __nv_bfloat16*)v_pool, page_stride, token_item, positions, block_table,          \
+                              bt_stride, n_heads, n_kv_heads, head_dim, page_size, window,                            \
+                              scale * 1.4426950408889634f, chunk_keys, split_chunks, n_splits, part_acc, part_ml,     \
+                              counters, status);                                                                      \
     }
-    return ps::launch_pdl(ps::paged_attention_decode_kernel, grid, dim3(ps::DEC_THREADS), smem, (cudaStream_t)stream,
-                          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
-                          (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride, token_item,
-                          positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim, page_size, window,
-                          scale * 1.4426950408889634f, chunk_keys, split_chunks, n_splits, part_acc, part_ml,
-                          counters, status);
+    if (head_dim <= 64) PS_DECODE_LAUNCH(4)
+    if (head_dim <= 128) PS_DECODE_LAUNCH(8)
+    PS_DECODE_LAUNCH(16)
+#undef PS_DECODE_LAUNCH
 }
 
 PS_EXPORT int ps_paged_attention_decode(const void* q, int q_stride, void* out, int out_stride,

@@ -343,8 +343,8 @@ class Ops:
     @staticmethod
     def attention_chunk_keys(head_dim, page_size):
         """Keys per shared-memory chunk of the split attention kernel (mirrors the CUDA side)."""
-        keys = min(128, (8192 // head_dim) & ~31)
-        return max(keys, page_size, 32)
+        keys = 128 if head_dim <= 64 else 64 if head_dim <= 128 else 32
+        return max(keys, page_size)
 
     def attention_split_plan(self, T, n_heads, head_dim, page_size, max_kv_len, target_ctas=1184):
         """(split_tiles, n_splits): how the keys of a token are cut over CTAs.

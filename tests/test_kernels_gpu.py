@@ -192,7 +192,10 @@ def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
     for has_mean, has_bias, use_rows in ((True, True, False), (False, False, True), (True, True, True)):
         norm = FakeNorm(has_mean, has_bias)
         deferred = DeferredNorm(norm, x if use_rows else x[:M], rows if use_rows else None)
-        assert ops._fused_norm_ok(deferred, w) == ((8 if M <= 8 else 16 if M <= 16 else 32) * (K + 8) * 2 <= 96 * 1024)
+        staged = (8 if M <= 8 else 16 if M <= 16 else 32) * (K + 8) * 2       # bytes of normed rows in shared memory
+        assert ops._fused_norm_ok(deferred, w) == (staged <= 96 * 1024)
+        if staged > 160 * 1024:
+            continue                                                            # beyond what the kernel takes
         fused = torch.empty(M, N, dtype=torch.float32, device=DEV)
         ops.linear_skinny_fused(deferred, w, bias, fused, act="gelu_tanh")
         separate = torch.empty(M, N, dtype=torch.float32, device=DEV)
