@@ -1,6 +1,9 @@
 // Causal attention of prompt portions over the paged cache on tensor cores (bfloat16).
 //
-// One CTA (4 warps) per (block of 64 query tokens of one request, head). The step's keys and values are
+// One CTA (8 warps = two groups of 4) per (block of 64 query tokens of one request, head). Both groups hold the
+// same 64 queries (16 rows per warp); group 0 walks the even key tiles, group 1 the odd ones, each with its own
+// double-buffered K/V tiles and its own named barrier; at the end group 0 merges the two (max, sum, O) states.
+// This halves the chain of dependent MMAs of the longest CTA (the last query block of a long prompt). The step's keys and values are
 // already in the pages, so the kernel reads every key, old or new, through the block table: a portion
 // that continues a cached prompt needs no gather (the reference concatenates gathered past K/V and
 // materialises the scores: src/model/paged_attention.py:262-295, 396-420), and fresh prompts need no
@@ -16,7 +19,7 @@
 namespace ps {
 namespace pf {
 
-constexpr int BQ = 64, BKEY = 64, THREADS = 128;   // 4 warps of 16 query rows
+constexpr int BQ = 64, BKEY = 64, GROUP = 128, THREADS = 256;   // 2 groups x 4 warps x 16 query rows
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -41,6 +44,9 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void group_sync(int group) {           // barrier of one 128-thread group
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(GROUP) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -59,8 +65,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     constexpr int KS = HD / 16;                        // k steps over the head dim
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BQ][RS]
-    __nv_bfloat16* k_s = q_s + BQ * RS;                                        // [2][BKEY][RS]
-    __nv_bfloat16* v_s = k_s + 2 * BKEY * RS;                                  // [2][BKEY][RS]
+    const int wg = threadIdx.x >> 7;                                           // warp group 0 / 1
+    __nv_bfloat16* k_s = q_s + BQ * RS + wg * (4 * BKEY * RS);                 // this group's [2][BKEY][RS]
+    __nv_bfloat16* v_s = k_s + 2 * BKEY * RS;                                  // this group's [2][BKEY][RS]
 
     pdl_prologue();
     // which (item, query block) is this CTA?
@@ -72,7 +79,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     }
     if (item < 0) return;
     const int h = blockIdx.y, g = h / (n_heads / n_kv_heads);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x & (GROUP - 1), lane = tid & 31, warp = tid >> 5;   // within the group
     const int qs = q_start[item], q_len = q_start[item + 1] - qs;
     const int pos0 = kv_len[item] - q_len + qb * BQ;              // position of the block's first query
     const int rows = min(BQ, q_len - qb * BQ);                    // valid query rows of the block
@@ -83,7 +90,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int* bt = block_table + (size_t)item * bt_stride;
 
     // ---- Q tile
-    for (int c = tid; c < BQ * CH; c += THREADS) {
+    for (int c = threadIdx.x; c < BQ * CH; c += THREADS) {
         int r = c / CH, piece = c % CH;
         bool ok = r < rows;
         const __nv_bfloat16* src = q + (size_t)(tok0 + (ok ? r : 0)) * q_stride + h * HD + piece * 8;
@@ -91,7 +98,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     }
     auto load_kv = [&](int kb, int buf) {
         const int key0 = kb * BKEY;
-        for (int c = tid; c < BKEY * CH; c += THREADS) {
+        for (int c = tid; c < BKEY * CH; c += GROUP) {
             int r = c / CH, piece = c % CH;
             int key = key0 + r;
             bool ok = key <= hi && key >= lo;
@@ -104,8 +111,10 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             cp_async16(v_s + (buf * BKEY + r) * RS + piece * 8, v_pool + off, ok);
         }
     };
-    load_kv(kb_first, 0);
+    if (kb_first + wg <= kb_last) load_kv(kb_first + wg, 0);
     cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();                                   // the Q tile (loaded by all 256 threads) is in place
 
     uint32_t qf[KS][4];
     float o[HD / 8][4];
@@ -116,17 +125,15 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int row0 = warp * 16 + gq, row1 = row0 + 8;            // the two query rows of this thread
     const int pos_r0 = pos0 + row0, pos_r1 = pos0 + row1;
 
-    for (int kb = kb_first; kb <= kb_last; ++kb) {
-        const int buf = (kb - kb_first) & 1;
-        if (kb < kb_last) load_kv(kb + 1, buf ^ 1);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+        ldmatrix_x4(qf[ks], q_s + (warp * 16 + (lane & 15)) * RS + (ks * 2 + (lane >> 4)) * 8);
+    for (int kb = kb_first + wg; kb <= kb_last; kb += 2) {
+        const int buf = ((kb - kb_first) >> 1) & 1;
+        if (kb + 2 <= kb_last) load_kv(kb + 2, buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
-        __syncthreads();
-        if (kb == kb_first) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks)
-                ldmatrix_x4(qf[ks], q_s + (warp * 16 + (lane & 15)) * RS + (ks * 2 + (lane >> 4)) * 8);
-        }
+        group_sync(wg);
         // ---- S = Q K^T for 16 rows x 64 keys
         float s[BKEY / 8][4];
 #pragma unroll
@@ -203,14 +210,48 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                 mma16816(o[dn + 1], a, b[2], b[3]);
             }
         }
-        __syncthreads();                               // this buffer is refilled two iterations on
+        group_sync(wg);                                // this buffer is refilled two iterations on
     }
     cp_async_wait<0>();
-    // ---- normalise and store
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+    // ---- merge the two groups: group 1 hands its state over through its (now free) K/V buffers
+    __syncthreads();
+    float* o1 = reinterpret_cast<float*>(q_s + BQ * RS + 4 * BKEY * RS);       // [BQ][HD] of group 1
+    float* ml1 = o1 + BQ * HD;                                                  // [BQ][2]
+    if (wg == 1) {
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; ++dn) {
+            const int d = dn * 8 + tq * 2;
+            *reinterpret_cast<float2*>(o1 + row0 * HD + d) = make_float2(o[dn][0], o[dn][1]);
+            *reinterpret_cast<float2*>(o1 + row1 * HD + d) = make_float2(o[dn][2], o[dn][3]);
+        }
+        if (tq == 0) {
+            ml1[2 * row0] = m_run[0]; ml1[2 * row0 + 1] = l_run[0];
+            ml1[2 * row1] = m_run[1]; ml1[2 * row1 + 1] = l_run[1];
+        }
+    }
+    __syncthreads();
+    if (wg == 1) return;
+    {
+        const float ma = ml1[2 * row0], la = ml1[2 * row0 + 1], mb = ml1[2 * row1], lb = ml1[2 * row1 + 1];
+        const float n0 = fmaxf(m_run[0], ma), n1 = fmaxf(m_run[1], mb);
+        const float b0 = (n0 == -INFINITY) ? 0.f : n0, b1 = (n1 == -INFINITY) ? 0.f : n1;
+        const float s0 = exp2f(m_run[0] - b0), t0 = exp2f(ma - b0), s1 = exp2f(m_run[1] - b1), t1 = exp2f(mb - b1);
+        l_run[0] = l_run[0] * s0 + la * t0;
+        l_run[1] = l_run[1] * s1 + lb * t1;
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; ++dn) {
+            const int d = dn * 8 + tq * 2;
+            const float2 pa = *reinterpret_cast<const float2*>(o1 + row0 * HD + d);
+            const float2 pb = *reinterpret_cast<const float2*>(o1 + row1 * HD + d);
+            o[dn][0] = o[dn][0] * s0 + pa.x * t0; o[dn][1] = o[dn][1] * s0 + pa.y * t0;
+            o[dn][2] = o[dn][2] * s1 + pb.x * t1; o[dn][3] = o[dn][3] * s1 + pb.y * t1;
+        }
+    }
+    // ---- normalise and store
     const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
 #pragma unroll
     for (int dn = 0; dn < HD / 8; ++dn) {
@@ -230,7 +271,7 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
            int first_item, int n_items, int max_blocks, int n_heads, int n_kv_heads, int page_size, int window,
            float scale, cudaStream_t stream) {
     constexpr int RS = HD + 8;
-    size_t smem = (size_t)(BQ + 4 * BKEY) * RS * 2;
+    size_t smem = (size_t)(BQ + 8 * BKEY) * RS * 2;
     auto kernel = prefill_attention_kernel<HD>;
     if (smem > 48 * 1024) {
         static bool raised = false;

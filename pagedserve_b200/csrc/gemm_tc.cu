@@ -8,9 +8,15 @@
 // the same rows of A in L2). TMEM holds two accumulators of BN columns; while the four epilogue warps
 // drain one, the MMA warp fills the other.
 //   warp 0: TMA producer (one lane)          warp 1: TMEM allocation + MMA issue (one lane)
-//   warps 2..5: epilogue, warp w owns TMEM lanes 32*(w%4) .. +31 (= rows of the tile)
+//   warps 2..9: epilogue in two teams of four; warp w owns TMEM lanes 32*(w%4) .. +31 (= rows of the tile),
+//               team (w-2)/4 takes every other 128-byte column group of the accumulator
 // A k-block is 64 bf16 = one 128-byte swizzle row; the K loop of an output element runs in one fixed
 // order whatever M is, so a row's result does not depend on the rows beside it.
+// Output: the epilogue warps stage 128 rows x 128 bytes of results in shared memory (swizzled, so that a
+// warp's 16-byte writes fall on different banks) and one thread hands them to TMA: a plain tensor store for
+// bfloat16 / float32 results, or a reducing store (cp.reduce.async.bulk.tensor ... .add) when the product is
+// accumulated into the float32 residual stream - the add happens in L2 and the SM never reads the stream.
+// Outputs whose row pitch is not a multiple of 16 bytes (a vocabulary of 50257) are stored from registers.
 // Every mbarrier wait is bounded: when one runs out the CTA sets *status, stops, frees its TMEM and returns.
 //
 // Replaces the cuBLAS nn.Linear calls of the reference (src/model/paged_decoder.py:49-50, 178-179, 295-299)
@@ -24,7 +30,7 @@ namespace tc {
 
 constexpr int BM = 128;
 constexpr int BK = 64;                 // bf16 elements per k-block = 128 bytes
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;           // TMA warp, MMA warp, two teams of four epilogue warps
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -101,26 +107,44 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void team_sync(int team) {             // the 128 threads of one epilogue team
+    asm volatile("bar.sync %0, 128;" ::"r"(team + 1) : "memory");
+}
+__device__ __forceinline__ float gelu_tanh_fast(float x) {       // tanh.approx: exact enough before a bf16 rounding
+    float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x), th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(inner));
+    return 0.5f * x * (1.0f + th);
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 template <int BN> struct Config {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int STAGES = BN == 256 ? 3 : (BN == 128 ? 5 : 6);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int STAGING_BYTES = 2 * BM * 128;           // two buffers of 128 rows x 128 bytes
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
-template <int BN, typename TOut>
+template <int BN, typename TOut, bool TMA_OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K, int act,
-               int accumulate, int* __restrict__ status) {
+               const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias, TOut* __restrict__ out,
+               int ldo, int M, int N, int K, int act, int accumulate, int* __restrict__ status) {
     using Cfg = Config<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * Cfg::STAGE_BYTES);
+    unsigned char* staging = tiles + (size_t)STAGES * Cfg::STAGE_BYTES;              // [2][128 rows][128 bytes]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::STAGING_BYTES);
     uint64_t* full = bars;                     // [STAGES]  TMA -> MMA
     uint64_t* empty = bars + STAGES;           // [STAGES]  MMA -> TMA
     uint64_t* acc_full = bars + 2 * STAGES;    // [2]       MMA -> epilogue
@@ -137,7 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -195,8 +219,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else {
-        // ------------------------------------------------ epilogue: warps 2..5
+        // ------------------------------------------------ epilogue: warps 2..9
         const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31
+        const int team = (warp - 2) >> 2;                   // which column groups this warp takes
         uint32_t local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
@@ -206,13 +231,89 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int m = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+            if constexpr (TMA_OUT) {
+                // columns per staged buffer: 128 bytes of output per row
+                constexpr int COLS = 128 / (int)sizeof(TOut);
+                const int r = quarter * 32 + lane;                        // row of the tile = row of the buffer
+                const bool leader = (quarter == 2 && lane == 0);          // first warp of the team (warps 2 and 6)
+                unsigned char* stage_buf = staging + (size_t)team * (BM * 128);
+                bool released = false;
+#pragma unroll 1
+                for (int c = team * COLS; c < BN; c += 2 * COLS) {
+                    if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the buffer is free
+                    team_sync(team);
+#pragma unroll
+                    for (int half = 0; half < COLS / 32; ++half) {
+                        uint32_t rr[32];
+                        tmem_ld32(taddr + c + 32 * half, rr);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (c + 2 * COLS >= BN && half == COLS / 32 - 1) {   // this team's last read of the accumulator
+                            tc_fence_before();
+                            mbar_arrive(&acc_empty[buf]);
+                            released = true;
+                        }
+                        const int n = n0 + c + 32 * half;
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
+                        if (bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < N) v[j] += bias[n + j];
+                        }
+                        if (act == PS_ACT_GELU_TANH) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = sizeof(TOut) == 2 ? gelu_tanh_fast(v[j]) : gelu_tanh(v[j]);
+                        } else if (act == PS_ACT_GELU_ERF) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                        }
+                        // 16-byte pieces of the row, XOR-swizzled by the row as the tensor map expects
+                        if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+                            for (int piece = 0; piece < 4; ++piece) {
+                                uint4 pack;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * piece], v[8 * piece + 1]);
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * piece + 2], v[8 * piece + 3]);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * piece + 4], v[8 * piece + 5]);
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * piece + 6], v[8 * piece + 7]);
+                                pack.x = *reinterpret_cast<uint32_t*>(&p0); pack.y = *reinterpret_cast<uint32_t*>(&p1);
+                                pack.z = *reinterpret_cast<uint32_t*>(&p2); pack.w = *reinterpret_cast<uint32_t*>(&p3);
+                                const int slot = (4 * half + piece) ^ (r & 7);
+                                *reinterpret_cast<uint4*>(stage_buf + r * 128 + slot * 16) = pack;
+                            }
+                        } else {
+#pragma unroll
+                            for (int piece = 0; piece < 8; ++piece) {
+                                const int slot = piece ^ (r & 7);
+                                *reinterpret_cast<float4*>(stage_buf + r * 128 + slot * 16) =
+                                    make_float4(v[4 * piece], v[4 * piece + 1], v[4 * piece + 2], v[4 * piece + 3]);
+                            }
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    team_sync(team);
+                    if (leader) {
+                        if (n0 + c < N) {
+                            if (accumulate) tma_reduce_add_2d(&map_out, stage_buf, n0 + c, m0);
+                            else tma_store_2d(&map_out, stage_buf, n0 + c, m0);
+                        }
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+                if (!released) {                                          // a team without a column group (BN < 2 groups)
+                    tc_fence_before();
+                    mbar_arrive(&acc_empty[buf]);
+                }
+                continue;
+            }
             TOut* orow = out + (size_t)m * ldo;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int c = 32 * team; c < BN; c += 64) {      // the two teams take alternate 32-column chunks
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c + 32 >= BN) {                          // accumulator is in registers: hand TMEM back
+                if (c + 64 >= BN) {                          // this team's last read: hand TMEM back
                     tc_fence_before();
                     mbar_arrive(&acc_empty[buf]);
                 }
@@ -286,6 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     }
+    if (TMA_OUT && (warp == 2 || warp == 6) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -327,6 +429,19 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The output [M, N] (row pitch ldo elements) in boxes of 128 rows x 128 bytes, 128-byte swizzle.
+static bool make_out_map(CUtensorMap* map, void* base, int M, int N, int ldo, int elem_bytes) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)ldo * elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)BM};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims,
+              strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static int sm_count() {
     static int count = 0;
     if (!count) {
@@ -338,12 +453,10 @@ static int sm_count() {
     return count;
 }
 
-template <int BN, typename TOut>
-int launch(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
-           int act, int accumulate, int* status, cudaStream_t stream) {
-    CUtensorMap map_a, map_w;
-    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_w, W, N, K, ldw, BN)) return PS_ERR_LAUNCH;
-    auto kernel = gemm_tc_kernel<BN, TOut>;
+template <int BN, typename TOut, bool TMA_OUT>
+int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_out, const float* bias,
+                  void* out, int ldo, int M, int N, int K, int act, int accumulate, int* status, cudaStream_t stream) {
+    auto kernel = gemm_tc_kernel<BN, TOut, TMA_OUT>;
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Config<BN>::SMEM) !=
@@ -353,8 +466,22 @@ int launch(const void* A, int lda, const void* W, int ldw, const float* bias, vo
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    return launch_pdl(kernel, dim3(grid), dim3(THREADS), Config<BN>::SMEM, stream, map_a, map_w, bias, (TOut*)out, ldo,
-                      M, N, K, act, accumulate, status);
+    return launch_pdl(kernel, dim3(grid), dim3(THREADS), Config<BN>::SMEM, stream, map_a, map_w, map_out, bias,
+                      (TOut*)out, ldo, M, N, K, act, accumulate, status);
+}
+
+template <int BN, typename TOut>
+int launch(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
+           int act, int accumulate, int* status, cudaStream_t stream) {
+    CUtensorMap map_a, map_w, map_out;
+    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_w, W, N, K, ldw, BN)) return PS_ERR_LAUNCH;
+    // TMA can write the output when its rows start on 16-byte boundaries
+    const bool tma_out = (((uintptr_t)out & 15) == 0) && (((size_t)ldo * sizeof(TOut)) % 16 == 0) &&
+                         make_out_map(&map_out, out, M, N, ldo, (int)sizeof(TOut));
+    if (tma_out)
+        return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    map_out = map_a;    // unused
+    return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, stream);
 }
 
 template <typename TOut>
