@@ -58,6 +58,8 @@ _SIGNATURES = {
     },
     "tc": {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+        "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
+                                    _I, _F, _P, _P],
     },
 }
 
@@ -399,6 +401,37 @@ class Ops:
             first_item, n_items, max_blocks, n_heads, n_kv_heads,
             head_dim, page_size, window or 0, scale, _stream()),
             "prefill_attention")
+        return out
+
+    @staticmethod
+    def prefill_tc_ok(head_dim, page_size, q, out, pool):
+        return (head_dim in (64, 128) and 8 <= page_size <= 64 and pool is not None and q.stride(0) % 8 == 0
+                and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+    def prefill_attention_tc(self, q, out, pool, cache_layer_local, q_start, kv_len, block_table, first_item,
+                             n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale,
+                             status=None):
+        """tcgen05 causal attention of prompt portions (bfloat16, head size 64 or 128).  ``pool`` is the cache
+        group's whole pool ``[pages, layers, 2, kv heads, page size, head dim]``; ``cache_layer_local`` the
+        layer's index inside it; ``max_blocks`` >= the number of 128-query blocks of the items."""
+        _require(q, "q", torch.bfloat16)
+        _require(out, "out", torch.bfloat16)
+        if self._tc is None:
+            self._tc = _declare(_load_library("tc"), "tc")
+        if status is None:
+            if self._tc_status is None:
+                self._tc_status = torch.zeros(1, dtype=torch.int32, device=q.device)
+            status = self._tc_status
+        pages, layers, two, kv_heads, ps, hd = pool.shape
+        rows_per_tensor = kv_heads * ps                      # rows of one (layer, k or v) inside a page
+        page_rows = layers * 2 * rows_per_tensor
+        self.launches += 1
+        _check(self._tc.ps_prefill_attention_tc(
+            _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(pool), pages * page_rows,
+            (cache_layer_local * 2) * rows_per_tensor, (cache_layer_local * 2 + 1) * rows_per_tensor, page_rows,
+            _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), first_item, n_items, max_blocks,
+            n_heads, n_kv_heads, head_dim, page_size, window or 0, scale, _ptr(status), _stream()),
+            "prefill_attention_tc")
         return out
 
     def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale,

@@ -34,7 +34,13 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
                                    layer.block_table, n_heads, n_kv_heads, head_dim, layer.page_size, window, scale,
                                    ctx.max_kv_len, status=ctx.status)
     if long_items:
-        ops.prefill_attention(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.q_start, ctx.kv_len,
-                              layer.block_table, ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads,
-                              n_kv_heads, head_dim, layer.page_size, window, scale)
+        if ops.prefill_tc_ok(head_dim, layer.page_size, q, out, getattr(layer, "pool", None)):
+            # blocks of 128 queries: never more than the count of 64-query blocks
+            ops.prefill_attention_tc(q, out, layer.pool, layer.pool_layer, ctx.q_start, ctx.kv_len, layer.block_table,
+                                     ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads, n_kv_heads,
+                                     head_dim, layer.page_size, window, scale, status=ctx.status)
+        else:
+            ops.prefill_attention(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.q_start, ctx.kv_len,
+                                  layer.block_table, ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads,
+                                  n_kv_heads, head_dim, layer.page_size, window, scale)
     return out

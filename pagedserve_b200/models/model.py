@@ -117,6 +117,8 @@ class Model:
                 layer.k_pool, layer.v_pool = group.layer_views(entry.cache_layer)
                 layer.page_stride = group.page_stride
                 layer.page_size = group.page_size
+                layer.pool = group.pool
+                layer.pool_layer = group.cache_layers.index(entry.cache_layer)
                 layer.block_table = ctx.block_tables[group_index]
             layer.state = cache.state.get(entry.cache_layer)
             self.blocks[entry.layer].forward(hidden, ctx, layer)

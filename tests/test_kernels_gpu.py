@@ -411,6 +411,42 @@ def test_prefill_attention_bfloat16(heads, kv_heads, head_dim, page, window):
     assert rel_err(got, reference[rows[portions[0]:]]) < 8e-3
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(12, 12, 64, 16), (8, 2, 128, 32), (3, 1, 64, 8),
+                                                          (2, 2, 128, 64)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_prefill_attention_tcgen05(heads, kv_heads, head_dim, page, window):
+    """The tcgen05 kernel (S, P and O_j in TMEM) on whole prompts and on portions that continue a cached
+    prompt, lengths around the 128-row and 128-key block edges, fragmented tables, a poisoned pool (NaN in
+    every slot that was never written), items before ``first_item`` left alone."""
+    ops = ops_for(torch.bfloat16)
+    lengths = [40, 16, 127, 128, 129, 255, 256, 257, 300, 1000]
+    case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=5 + head_dim)
+    reference = case.reference(window)
+    portions = [40, 16, 127, 17, 129, 128, 256, 100, 37, 1000]
+    rows, q_start, kv_len = [], [0], []
+    begin = 0
+    for length, portion in zip(lengths, portions):
+        rows.append(torch.arange(begin + length - portion, begin + length))
+        q_start.append(q_start[-1] + portion)
+        kv_len.append(length)
+        begin += length
+    rows = torch.cat(rows)
+    q = case.q[rows].to(DEV)
+    out = torch.full((rows.numel(), heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    first_item = 1
+    blocks = sum(-(-p // 128) for p in portions[first_item:])
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.prefill_attention_tc(q, out, case.pool, 0, torch.tensor(q_start, dtype=torch.int32, device=DEV),
+                             torch.tensor(kv_len, dtype=torch.int32, device=DEV), case.table, first_item,
+                             len(lengths) - first_item, blocks + 2, heads, kv_heads, head_dim, page, window,
+                             head_dim ** -0.5, status=status)
+    assert int(status.item()) == 0
+    assert torch.isnan(out[:portions[0]].float()).all()        # untouched
+    got = out[portions[0]:]
+    assert torch.isfinite(got.float()).all()
+    assert rel_err(got, reference[rows[portions[0]:]]) < 8e-3
+
+
 @pytest.mark.parametrize("far", [0, 31, 32, 255, 256, 600])
 def test_attention_finds_a_far_key(far):
     """One key among a thousand carries almost all the weight: the output must be its value."""
@@ -434,6 +470,13 @@ def test_attention_finds_a_far_key(far):
                                   4, 2, 64, 16, None, 0.125)
             assert float((tensor_core[999, 192:256].double().cpu() - case.v[far, 64:128].double()).abs().max()) < 0.05
             assert rel_err(tensor_core, want) < tol
+            fifth_gen = torch.empty_like(out)
+            ops.prefill_attention_tc(case.q.to(DEV), fifth_gen, case.pool, 0,
+                                     torch.tensor([0, 1000, 1040], dtype=torch.int32, device=DEV),
+                                     torch.tensor([1000, 40], dtype=torch.int32, device=DEV), case.table, 0, 2, 9,
+                                     4, 2, 64, 16, None, 0.125)
+            assert float((fifth_gen[999, 192:256].double().cpu() - case.v[far, 64:128].double()).abs().max()) < 0.05
+            assert rel_err(fifth_gen, want) < tol
         got_row = out[999, 3 * 64:4 * 64].double().cpu()
         value_row = case.v[far, 64:128].double()
         assert float((got_row - value_row).abs().max()) < 0.05          # the spike's value came through
