@@ -7,9 +7,10 @@
 //   S = Q K^T   tcgen05.mma, A = Q tile and B = K tile in shared memory (K-major, 128-byte swizzle), S in TMEM
 //   softmax     128 threads, one per query row: tcgen05.ld of its S row, scale, mask, running max and sum in
 //               float32 with exp2, P rounded to bfloat16 and written back to TMEM (tcgen05.st)
-//   O_j = P V   tcgen05.mma with A = P from TMEM and B = the V tile in shared memory (MN-major descriptor:
-//               V rows are keys, the head dim is contiguous); the row's thread adds O_j into its float32
-//               accumulator with the running rescale
+//   O += P V    tcgen05.mma with A = P from TMEM and B = the V tile in shared memory (MN-major descriptor:
+//               V rows are keys, the head dim is contiguous), accumulating in TMEM; when a tile raises a
+//               row's running maximum the row's thread first rescales its O row in TMEM (skipped by a whole
+//               warp when none of its 32 rows changed, which is the common case after the first tiles)
 // TMA brings the Q tile from the step's q|k|v buffer and, page by page, the K and V tiles from the pool
 // (one box of page_size x 64 per page; no multicast); two K/V stages.
 //   warp 0: TMA producer      warp 1: TMEM allocation + MMA issue      warps 2..5: softmax rows / output
@@ -143,7 +144,7 @@ struct Layout {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, HD == 64 ? 2 : 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ q_start,
                             const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride,
@@ -268,7 +269,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int k = 0; k < BKEY / 16; ++k)
                     umma_ts(tmem_base + L::O_COL, tmem_base + L::P_COL + 8 * k,
-                            desc_sw128(v_addr, BKEY * 128) + (uint64_t)((2048 * k) >> 4), idesc_pv, k ? 1u : 0u);
+                            desc_sw128(v_addr, BKEY * 128) + (uint64_t)((2048 * k) >> 4), idesc_pv, (it | k) ? 1u : 0u);
                 umma_commit(&kv_empty[s]);
                 umma_commit(o_full);
             }
@@ -279,9 +280,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int r = quarter * 32 + lane;                        // query row of the tile = TMEM lane
         const int pos = pos0 + r;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        float o_acc[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o_acc[d] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         uint32_t it = 0;
@@ -335,8 +333,20 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tmem_st32(lane_base + L::P_COL + (c >> 1), pr);
             }
             const float sum = (sum0 + sum1) + (sum2 + sum3);
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             l_run = l_run * corr + sum;
+            // O of the earlier tiles (complete: o_full of the last tile was waited below) follows the new maximum
+            if (it > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t orr[32];
+                    tmem_ld32(lane_base + L::O_COL + c, orr);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * corr);
+                    tmem_st32(lane_base + L::O_COL + c, orr);
+                }
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             // V rows of keys outside [lo, hi] hold stale shared memory or stale cache contents: 0 * garbage
             // must stay 0, so the row's thread clears them before the product reads the tile
             {
@@ -354,32 +364,32 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             tc_fence_before();
             mbar_arrive(p_ready);
-            // O += corr-rescaled running sum + O_j
+            // the product of this tile must be complete before O is touched again (or read at the end)
             if (!mbar_wait(o_full, it & 1, abort_flag)) { ok = false; if (lane == 0) atomicExch(status, 37); break; }
             tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD; c += 64) {
-                uint32_t orr[64];
-                tmem_ld32(lane_base + L::O_COL + c, *reinterpret_cast<uint32_t(*)[32]>(&orr[0]));
-                tmem_ld32(lane_base + L::O_COL + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[32]));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 64; ++j) o_acc[c + j] = fmaf(o_acc[c + j], corr, __uint_as_float(orr[j]));
-            }
         }
-        if (ok && r < rows) {
+        if (ok) {
+            // the whole warp reads its O rows from TMEM (the load is warp-wide); rows of the portion store
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* orow = out + (size_t)(tok0 + r) * out_stride + h * HD;
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
-                uint4 pack;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(o_acc[d] * inv, o_acc[d + 1] * inv);
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(o_acc[d + 2] * inv, o_acc[d + 3] * inv);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(o_acc[d + 4] * inv, o_acc[d + 5] * inv);
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(o_acc[d + 6] * inv, o_acc[d + 7] * inv);
-                pack.x = *reinterpret_cast<uint32_t*>(&p0); pack.y = *reinterpret_cast<uint32_t*>(&p1);
-                pack.z = *reinterpret_cast<uint32_t*>(&p2); pack.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(orow + d) = pack;
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t orr[32];
+                tmem_ld32(lane_base + L::O_COL + c, orr);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < rows) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 pack;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(orr[d]) * inv, __uint_as_float(orr[d + 1]) * inv);
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(orr[d + 2]) * inv, __uint_as_float(orr[d + 3]) * inv);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(orr[d + 4]) * inv, __uint_as_float(orr[d + 5]) * inv);
+                        __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(orr[d + 6]) * inv, __uint_as_float(orr[d + 7]) * inv);
+                        pack.x = *reinterpret_cast<uint32_t*>(&p0); pack.y = *reinterpret_cast<uint32_t*>(&p1);
+                        pack.z = *reinterpret_cast<uint32_t*>(&p2); pack.w = *reinterpret_cast<uint32_t*>(&p3);
+                        *reinterpret_cast<uint4*>(orow + c + d) = pack;
+                    }
+                }
             }
         }
     }
