@@ -163,7 +163,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* s_full = kv_empty + KV_STAGES;  // MMA -> softmax: S is complete
     uint64_t* p_ready = s_full + 1;           // softmax (128 arrivals) -> MMA: P is in TMEM, S and O_j are consumed
     uint64_t* o_full = p_ready + 1;           // MMA -> softmax: O_j is complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    uint64_t* s_free = o_full + 1;            // softmax (128 arrivals) -> MMA: S is in registers, the next S may land
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     pdl_prologue();
@@ -193,6 +194,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(s_full, 1);
         mbar_init(p_ready, 128);
         mbar_init(o_full, 1);
+        mbar_init(s_free, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -247,15 +249,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
             bool ok = mbar_wait(q_full, 0, abort_flag);
             if (!ok) atomicExch(status, 32);
-            uint32_t it = 0;
-            for (int kb = kb_first; kb <= kb_last && ok; ++kb, ++it) {
-                const int s = it % KV_STAGES;
-                if (!mbar_wait(&kv_full[s], (it / KV_STAGES) & 1, abort_flag)) { atomicExch(status, 33); break; }
-                // S of the last tile was consumed before its rows arrived on p_ready (waited below, last
-                // iteration); its O_j is read before the rows arrive for this tile
+            // S = Q K^T of tile `t` (its K tile must have landed); completion is signalled on s_full
+            auto issue_qk = [&](uint32_t t) -> bool {
+                const int st = t % KV_STAGES;
+                if (!mbar_wait(&kv_full[st], (t / KV_STAGES) & 1, abort_flag)) { atomicExch(status, 33); return false; }
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(kv_s + (size_t)s * L::STAGE_BYTES);
-                const uint32_t v_addr = k_addr + L::KV_BYTES;
+                const uint32_t k_addr = smem_u32(kv_s + (size_t)st * L::STAGE_BYTES);
 #pragma unroll
                 for (int c = 0; c < L::KCH; ++c)
 #pragma unroll
@@ -263,9 +262,22 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         umma_ss(tmem_base + L::S_COL, desc_sw128(smem_u32(q_s) + c * (BQ * 128), 16) + 2 * k,
                                 desc_sw128(k_addr + c * (BKEY * 128), 16) + 2 * k, idesc_qk, (c | k) ? 1u : 0u);
                 umma_commit(s_full);
-                // wait for P of this tile, then O_j = P V over the 128 keys (8 steps of 16 keys = 2048 bytes of V)
+                return true;
+            };
+            const uint32_t n_tiles = (uint32_t)(kb_last - kb_first + 1);
+            if (ok) ok = issue_qk(0);
+            for (uint32_t it = 0; it < n_tiles && ok; ++it) {
+                const int s = it % KV_STAGES;
+                // the scores of the next tile are computed while the rows work on this one: S is free as
+                // soon as every row has it in registers
+                if (it + 1 < n_tiles) {
+                    if (!mbar_wait(s_free, it & 1, abort_flag)) { atomicExch(status, 34); break; }
+                    if (!issue_qk(it + 1)) break;
+                }
+                // P of this tile is in TMEM (and O rescaled): O += P V over the 128 keys, 16 keys = 2048 bytes of V
                 if (!mbar_wait(p_ready, it & 1, abort_flag)) { atomicExch(status, 35); break; }
                 tc_fence_after();
+                const uint32_t v_addr = smem_u32(kv_s + (size_t)s * L::STAGE_BYTES) + L::KV_BYTES;
 #pragma unroll
                 for (int k = 0; k < BKEY / 16; ++k)
                     umma_ts(tmem_base + L::O_COL, tmem_base + L::P_COL + 8 * k,
@@ -290,6 +302,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // the row's 128 raw scores in registers (one TMEM round trip)
             uint32_t sr[BKEY];
             tmem_ld128(lane_base + L::S_COL, sr);
+            tc_fence_before();
+            mbar_arrive(s_free);                                  // the next tile's scores may overwrite S
             const bool need_mask = (key0 + BKEY - 1 > pos0) || (window > 0 && key0 < pos0 + rows - window) || rows < BQ;
             if (need_mask) {
                 // keys this row may see: [max(lo_row, lo), pos]; everything else becomes -inf

@@ -25,9 +25,12 @@ class StepEntry:
     want: Sequence[int] = ()          # places among ``tokens`` whose logits are returned
 
     def __post_init__(self):
-        self.tokens = [int(t) for t in self.tokens]
+        tokens = np.asarray(self.tokens)
+        if tokens.size and not np.issubdtype(tokens.dtype, np.integer):
+            raise ValueError("token ids must be integers")
+        self.tokens = tokens.astype(np.int64, copy=False).reshape(-1)      # kept as an array: prompts are long
         self.want = [int(w) for w in self.want]
-        if not self.tokens:
+        if self.tokens.size == 0:
             # reference: src/model/iteration.py:23-24
             raise ValueError("a step entry must contain at least one token")
         for place in self.want:

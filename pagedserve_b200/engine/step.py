@@ -65,7 +65,8 @@ class ModelRunner:
         self.tokens_run = 0
         self.enable_cuda_graphs = enable_cuda_graphs and model.graph_safe
         self.ops = model.env.ops
-        self._graphs = {}                 # (batch size, kind) -> _DecodeGraph
+        self._graphs = {}                 # (batch size, kind) or step shape -> _DecodeGraph
+        self._shape_seen = {}             # step shape -> times seen (a shape is captured when it comes back)
         self.graph_replays = 0
         self._sampled = torch.zeros(cache.max_slots, dtype=torch.int32, device=self.device)
         self._history = torch.zeros(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32,
@@ -106,9 +107,10 @@ class ModelRunner:
             if entry.request in seen:
                 raise StepError("a request can appear only once in a step")   # reference: iteration.py:62-63
             seen.add(entry.request)
-            bad = [t for t in entry.tokens if not (0 <= t < self.vocab_size)]
-            if bad:
-                raise StepError(f"token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
+            low, high = int(entry.tokens.min()), int(entry.tokens.max())
+            if low < 0 or high >= self.vocab_size:
+                raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
+                                f"{self.vocab_size}")
 
         admitted: List[Hashable] = []
         extended: List[Hashable] = []
@@ -226,6 +228,8 @@ class ModelRunner:
                 logits = self.decode_stack.run(ctx, 1, True, False, max_kv_len=ctx.max_kv_len)
             elif decode_only and self.enable_cuda_graphs:
                 logits = self._run_decode_graph(ctx, "logits").logits.clone()
+            elif self.enable_cuda_graphs:
+                logits = self._run_mixed_step(ctx)
             else:
                 logits = self.model.forward(ctx)
         except Exception:
@@ -296,6 +300,37 @@ class ModelRunner:
         self.ops.sample(logits, ctx.temperature, ctx.seed, ctx.positions, sampled, pos_offset=1)
         self.ops.advance(sampled, ctx.token_ids, ctx.positions, ctx.kv_len, self._history, self._step_counter,
                          self.MAX_DEVICE_STEPS)
+        return logits
+
+    def _run_mixed_step(self, ctx: StepContext) -> torch.Tensor:
+        """A step with prompt portions.  Its ~100 launches cost the host about as much time as the device
+        needs to run them, so a step shape that comes back (same counts of tokens, entries, wanted rows,
+        short entries and query blocks: a steady chunked-prefill budget, a benchmark) is captured as a CUDA
+        graph the second time it is seen and replayed from then on."""
+        bucket = -(-ctx.max_kv_len // 256) * 256
+        ctx.max_kv_len = min(bucket, self.max_model_len)
+        key = (ctx.num_tokens, ctx.num_items, ctx.num_logit_rows, ctx.num_short_items, ctx.num_short_tokens,
+               ctx.num_long_blocks, ctx.max_kv_len, "mixed")
+        graph = self._graphs.get(key)
+        if graph is not None:
+            graph.replay()
+            self.graph_replays += 1
+            return graph.logits.clone()
+        seen = self._shape_seen.get(key, 0) + 1
+        self._shape_seen[key] = seen
+        logits = self.model.forward(ctx)
+        if seen < 2:
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            return logits
+        if len(self._graphs) >= self.MAX_GRAPHS:
+            self._graphs.pop(next(iter(self._graphs)))
+        torch.cuda.current_stream().synchronize()
+        launches_before = self.ops.launches
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            static_logits = self.model.forward(ctx)
+        self._graphs[key] = _DecodeGraph(captured, static_logits, self.ops.launches - launches_before)
         return logits
 
     def _run_decode_graph(self, ctx: StepContext, kind: str):
