@@ -128,7 +128,7 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 
 template <int BN> struct Config {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int STAGES = BN == 256 ? 3 : (BN == 128 ? 5 : 6);
+    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 5 : 6);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     static constexpr int STAGING_BYTES = 2 * BM * 128;           // two buffers of 128 rows x 128 bytes
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
