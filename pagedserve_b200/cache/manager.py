@@ -121,6 +121,7 @@ class CacheGroup:
         self.max_pages_per_request = max_pages_per_request
         self.allocator = PageAllocator(num_pages)
         self.tables: Dict[Hashable, List[int]] = {}
+        self.rows = None                            # [slots, max pages] int32 mirror of the tables, -1 = no page
         self.pool = None
         if device is not None:
             shape = (num_pages, len(self.cache_layers), 2, need.n_kv_heads, page_size, need.head_dim)
@@ -177,6 +178,9 @@ class CacheManager:
             CacheGroup(need, layers, page_size, num_pages, self.max_pages_per_request, dtype, device)
             for need, layers in by_need.items()
         ]
+        for group in self.groups:
+            # the tables once more as one array by slot, so that a step gathers its rows in one operation
+            group.rows = np.full((max_slots, self.max_pages_per_request), -1, dtype=np.int32)
         self.group_of_layer: Dict[int, int] = {
             layer: index for index, group in enumerate(self.groups) for layer in group.cache_layers
         }
@@ -244,6 +248,7 @@ class CacheManager:
             tensor[slot].zero_()
         for group in self.groups:
             group.tables[request] = []
+            group.rows[slot] = -1
         return slot
 
     def extend(self, request: Hashable, new_tokens: int) -> None:
@@ -271,10 +276,12 @@ class CacheManager:
                 while len(table) < needed:
                     page = group.allocator.allocate()
                     fresh.append(page)
+                    group.rows[slot, len(table)] = page
                     table.append(page)
         except CacheFull:
             for group, fresh, old_len in taken:
                 del group.tables[request][old_len:]
+                group.rows[slot, old_len:] = -1
                 for page in reversed(fresh):
                     group.allocator.release(page)
             raise
@@ -292,6 +299,7 @@ class CacheManager:
                 if page >= 0:
                     group.allocator.release(page)
             del table[keep:]
+            group.rows[slot, keep:] = -1
         self.pending[slot] = 0
 
     def commit(self, request: Hashable) -> int:
@@ -312,6 +320,7 @@ class CacheManager:
                 if table[index] >= 0:
                     group.allocator.release(table[index])
                     table[index] = -1
+                    group.rows[slot, index] = -1
         return length
 
     def free(self, request: Hashable) -> None:
@@ -326,6 +335,7 @@ class CacheManager:
                 raise CacheError("request holds a page twice")
             for page in live:
                 group.allocator.release(page)
+            group.rows[slot] = -1
         del self.slot_of[request]
         self.lengths[slot] = 0
         self._free_slots.append(slot)
@@ -333,10 +343,11 @@ class CacheManager:
     # ------------------------------------------------------------------ tables for a step
     def table_row(self, group_index: int, request: Hashable, out: np.ndarray) -> None:
         """Write the request's block table (padded with -1) into ``out`` (int32 [max_pages])."""
-        table = self.groups[group_index].tables[request]
-        count = len(table)
-        out[:count] = table
-        out[count:] = -1
+        out[:] = self.groups[group_index].rows[self._slot(request)]
+
+    def table_rows(self, group_index: int, slots: np.ndarray, out: np.ndarray) -> None:
+        """The block tables of several slots at once into ``out`` (int32 [len(slots), max_pages])."""
+        np.take(self.groups[group_index].rows, slots, axis=0, out=out)
 
     # ------------------------------------------------------------------ checks and figures
     def check_invariants(self) -> None:
@@ -352,6 +363,10 @@ class CacheManager:
                 raise CacheError("a page is both free and held")
             if len(free) + len(held) != group.num_pages:
                 raise CacheError(f"pages lost: {group.num_pages - len(free) - len(held)}")
+            for request, table in group.tables.items():
+                row = group.rows[self.slot_of[request]]
+                if row[:len(table)].tolist() != table or (row[len(table):] != -1).any():
+                    raise CacheError(f"the table array of request {request!r} differs from its table")
         slots = list(self.slot_of.values())
         if len(slots) != len(set(slots)) or len(slots) + len(self._free_slots) != self.max_slots:
             raise CacheError("slot bookkeeping is inconsistent")

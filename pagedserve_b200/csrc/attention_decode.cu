@@ -121,6 +121,9 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __shared__ int last_flag;
 
     pdl_prologue();
+    q = pdl_fresh(q);
+    k_pool = pdl_fresh(k_pool);
+    v_pool = pdl_fresh(v_pool);
     const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, tq = lane & 3;

@@ -70,6 +70,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     __nv_bfloat16* v_s = k_s + 2 * BKEY * RS;                                  // this group's [2][BKEY][RS]
 
     pdl_prologue();
+    q = pdl_fresh(q);
+    k_pool = pdl_fresh(k_pool);
+    v_pool = pdl_fresh(v_pool);
     // which (item, query block) is this CTA?
     int block = blockIdx.x, item = -1, qb = 0;
     for (int i = first_item; i < first_item + n_items; ++i) {

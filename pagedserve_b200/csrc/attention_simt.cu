@@ -25,6 +25,8 @@ __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restric
                                  T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride,
                                  int n_kv_heads, int head_dim, int page_size) {
     pdl_prologue();
+    k_src = pdl_fresh(k_src);
+    v_src = pdl_fresh(v_src);
     int t = blockIdx.x;
     int item = token_item[t];
     int p = positions[t];
@@ -49,6 +51,8 @@ kv_append_vec_kernel(const T* __restrict__ k_src, const T* __restrict__ v_src, i
                      T* __restrict__ v_pool, long long page_stride, int T_tokens, int n_kv_heads, int head_dim,
                      int page_size) {
     pdl_prologue();
+    k_src = pdl_fresh(k_src);
+    v_src = pdl_fresh(v_src);
     constexpr int PER = 16 / sizeof(T);                       // elements per piece
     const int pieces = n_kv_heads * head_dim / PER;           // per token and tensor
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -102,6 +106,9 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
 
     pdl_prologue();
+    q = pdl_fresh(q);
+    k_pool = pdl_fresh(k_pool);
+    v_pool = pdl_fresh(v_pool);
     int t = blockIdx.x, h = blockIdx.y;
     int g = h / (n_heads / n_kv_heads);
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

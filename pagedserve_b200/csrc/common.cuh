@@ -3,6 +3,8 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstring>
+#include <cstdlib>
 #include <stdint.h>
 #include <stdlib.h>
 
@@ -60,14 +62,51 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// Programmatic dependent launch (off unless PAGEDSERVE_B200_PDL is set): every kernel of the step calls pdl_prologue() before it touches
-// memory that an earlier kernel wrote. It first lets the next kernel in the stream begin to launch
-// (its CTAs are scheduled as SM resources free up and run up to their own wait), then waits until
-// all earlier kernels have completed and their writes are visible. Without the launch attribute
-// both instructions do nothing.
+// Programmatic dependent launch (on unless PAGEDSERVE_B200_PDL=0). A kernel calls pdl_wait() before it
+// touches memory that an earlier kernel wrote: it returns when all earlier kernels have completed and their
+// writes are visible. What a kernel does before pdl_wait() (reading weights, which no kernel writes) overlaps
+// the end of the kernel before it. pdl_launch() lets the next kernel in the stream begin to launch: its CTAs
+// are scheduled as SM resources free up and run up to their own pdl_wait(). Because every kernel calls
+// pdl_launch() after its pdl_wait(), at most two kernels are resident at a time. Without the launch
+// attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_prologue() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pdl_wait();
+    pdl_launch();
+}
+// A pointer to data that an earlier kernel of the step wrote goes through pdl_fresh() after pdl_wait():
+// loads through a `const __restrict__` pointer count as loads of memory that never changes, which the
+// compiler may move above the wait; the value returned here does not exist before the wait.
+template <typename T>
+__device__ __forceinline__ T* pdl_fresh(T* p) {
+    asm volatile("" : "+l"(p) : : "memory");
+    return p;
+}
+
+// PAGEDSERVE_B200_PDL: unset or 1 = programmatic dependent launch for every kernel, 0 = for none; any other
+// value is a comma-separated list of pieces of kernel names that get it (for finding out which kernel gains
+// or misbehaves).
+inline bool pdl_enabled_for(const void* kernel) {
+    const char* env = getenv("PAGEDSERVE_B200_PDL");
+    if (!env || !*env || !strcmp(env, "1")) return true;
+    if (!strcmp(env, "0")) return false;
+    const char* name = nullptr;
+    if (cudaFuncGetName(&name, kernel) != cudaSuccess || !name) return false;
+    const char* piece = env;
+    while (*piece) {
+        const char* end = strchr(piece, ',');
+        size_t n = end ? (size_t)(end - piece) : strlen(piece);
+        if (n > 0 && n < 128) {
+            char buffer[128];
+            memcpy(buffer, piece, n);
+            buffer[n] = 0;
+            if (strstr(name, buffer)) return true;
+        }
+        if (!end) break;
+        piece = end + 1;
+    }
+    return false;
 }
 
 // Launch with the programmatic-stream-serialization attribute (kept when a stream is captured into a
@@ -80,9 +119,10 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     config.blockDim = block;
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    // Measured on B200 with the 101-kernel decode graph of GPT-2 124M: early launch of the next kernel made
-    // the step slower (553 vs 497 us at batch 1, 737 vs 590 us at batch 8), so it is opt-in.
-    static const bool enabled = getenv("PAGEDSERVE_B200_PDL") != nullptr;
+    // Measured on B200 with the 64-kernel decode graph of GPT-2 124M at batch 8: 362 us per step with it,
+    // 414 us without. (A first form, in which every kernel let its successor launch before its own wait, so
+    // that many kernels sat resident at once, was slower than no early launch at all.)
+    static const bool enabled = pdl_enabled_for((const void*)kernel);
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;

@@ -14,6 +14,8 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
                              const T* __restrict__ wte, const T* __restrict__ wpe,
                              float* __restrict__ out, int H, int V, int P, int* __restrict__ status) {
     pdl_prologue();
+    ids = pdl_fresh(ids);
+    pos = pdl_fresh(pos);
     int t = blockIdx.x;
     int id = ids[t];
     int p = pos ? pos[t] : 0;
@@ -40,6 +42,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     __shared__ float red[NT / 32];
     __shared__ float bcast;
     pdl_prologue();
+    x = pdl_fresh(x);
     int r = blockIdx.x;
     int src = rows ? rows[r] : r;
     const float* xr = x + (size_t)src * H;
@@ -124,6 +127,7 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                       const float* __restrict__ beta, float eps, TOut* __restrict__ out, int n_rows, int H,
                       int has_mean) {
     pdl_prologue();
+    x = pdl_fresh(x);
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= n_rows) return;

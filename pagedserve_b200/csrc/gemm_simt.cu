@@ -22,6 +22,7 @@ gemm_simt_kernel(const TIn* __restrict__ A, int lda, const TIn* __restrict__ W, 
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     pdl_prologue();
+    A = pdl_fresh(A);
     int tid = threadIdx.x;
     int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, 4x4 outputs each

@@ -38,7 +38,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
                    int act, int accumulate) {
     extern __shared__ float red[];                 // [WARPS][16][8*MT]
     constexpr int UNROLL = 6;                      // K = 3072 over 16 warps is one round of loads
-    pdl_prologue();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -59,7 +58,23 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
 
+    // what the output holds (to be added to) is fetched right after the wait, long before the epilogue needs it
+    constexpr int TOK = 8 * MT;
+    constexpr int EPT = (16 * TOK + WARPS * 32 - 1) / (WARPS * 32);      // epilogue elements per thread
+    float prev[EPT];
+    auto after_wait = [&]() {
+        pdl_prologue();
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) arow[mt] = pdl_fresh(arow[mt]);
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int e = threadIdx.x + j * WARPS * 32;
+            const int n = n0 + (e & 15), m = e >> 4;
+            prev[j] = (accumulate && e < 16 * TOK && m < M && n < N) ? to_float(out[(size_t)m * ldo + n]) : 0.f;
+        }
+    };
     const int steps = (K + 31) >> 5;
+    bool waited = false;
     for (int s0 = warp; s0 < steps; s0 += WARPS * UNROLL) {
         uint4 wa[UNROLL], wb[UNROLL];
 #pragma unroll
@@ -68,6 +83,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
             bool ok = (s0 + u * WARPS) < steps && (k + 8 * t) < K;
             wa[u] = ok ? ldg_stream(w0 + k) : make_uint4(0, 0, 0, 0);
             wb[u] = ok ? ldg_stream(w1 + k) : make_uint4(0, 0, 0, 0);
+        }
+        if (!waited) {               // the first weights are on their way: now wait for the kernel that writes A
+            after_wait();
+            waited = true;
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -85,8 +104,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
             }
         }
     }
+    if (!waited) after_wait();
     // acc[mt][0]: (row g, token 8mt+2t), [1]: (g, +1), [2]: (g+8, 2t), [3]: (g+8, 2t+1)
-    constexpr int TOK = 8 * MT;
     float* mine = red + (size_t)warp * 16 * TOK;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -97,7 +116,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         mine[(g + 8) * TOK + c + 1] = acc[mt][3];
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < 16 * TOK; e += WARPS * 32) {
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int e = threadIdx.x + j * WARPS * 32;
+        if (e >= 16 * TOK) break;
         int r = e & 15, m = e >> 4;           // weight row fastest: consecutive threads store consecutive n
         int n = n0 + r;
         if (m >= M || n >= N) continue;
@@ -106,9 +128,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * 16 * TOK + r * TOK + m];
         if (bias) v += bias[n];
         v = apply_act(v, act);
-        size_t o = (size_t)m * ldo + n;
-        if (accumulate) v += to_float(out[o]);
-        out[o] = from_float<TOut>(v);
+        v += prev[j];
+        out[(size_t)m * ldo + n] = from_float<TOut>(v);
     }
 }
 
@@ -182,18 +203,20 @@ struct NormInput {
     int has_mean;
 };
 
-template <int MT, int WARPS, typename TOut>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int MT, int WARPS, int UNROLL, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32, WARPS <= 8 ? 2 : 1)
 gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int ldw,
                          const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K,
                          int act, int accumulate, KvScatter kv) {
-    // shared memory: cross-warp sums [WARPS][16][8*MT] floats, then the normed rows [8*MT][K+8] bf16
+    // shared memory: cross-warp sums [WARPS][16][8*MT] floats, the norm's scale and shift [2][K] floats,
+    // the cache address of each row [8*MT] (64-bit), then the normed rows [8*MT][K+8] bf16
     extern __shared__ __align__(16) float red[];
-    constexpr int UNROLL = 6;
     constexpr int TOK = 8 * MT;
     const int lda_s = K + 8;                       // padded: 16-byte reads of 8 rows hit 8 different bank groups
-    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(red + (size_t)WARPS * 16 * TOK);
-    pdl_prologue();
+    float* gamma_s = red + (size_t)WARPS * 16 * TOK;
+    float* beta_s = gamma_s + K;
+    long long* dst_s = reinterpret_cast<long long*>(beta_s + K);
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(dst_s + TOK);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -201,8 +224,10 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
     const __nv_bfloat16* w0 = W + (size_t)r0 * ldw + 8 * t;
     const __nv_bfloat16* w1 = W + (size_t)r1 * ldw + 8 * t;
     const int steps = (K + 31) >> 5;
+    const int quads = K >> 2;
 
-    // first batch of weight loads: in flight while the rows are normed
+    // Before the wait, what no kernel writes: the first batch of weights (to registers) and the norm's
+    // scale and shift (to shared memory). They are in flight while the kernel before this one ends.
     uint4 wa[UNROLL], wb[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -211,49 +236,100 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         wa[u] = ok ? ldg_stream(w0 + k) : make_uint4(0, 0, 0, 0);
         wb[u] = ok ? ldg_stream(w1 + k) : make_uint4(0, 0, 0, 0);
     }
-    // norm: one warp per row; the row sits in registers (float4 pieces, all loads issued at once) when
-    // K <= 1024, else it is read again from L1
-    const int quads = K >> 2;
-    for (int m = warp; m < M; m += WARPS) {
-        const float4* xr = reinterpret_cast<const float4*>(in.x + (size_t)(in.rows ? in.rows[m] : m) * in.ldx);
+    {
+        const float4* g4 = reinterpret_cast<const float4*>(in.gamma);
+        const float4* b4 = reinterpret_cast<const float4*>(in.beta);
+        for (int c = threadIdx.x; c < quads; c += WARPS * 32) {
+            reinterpret_cast<float4*>(gamma_s)[c] = g4[c];
+            reinterpret_cast<float4*>(beta_s)[c] = in.beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    pdl_prologue();            // the rows come from the kernel before this one
+    if (kv.k_pool && threadIdx.x < M) {
+        // where this row's keys and values go: offset of (page, head 0, position in page, 0), or -1
+        const int m = threadIdx.x;
+        const int p = kv.positions[m];
+        const int page = kv.block_table[(size_t)kv.token_item[m] * kv.bt_stride + p / kv.page_size];
+        dst_s[m] = page >= 0 ? (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim : -1;
+    }
+    __syncthreads();
+    // norm: one warp per row, two rows at a time so that their loads and reductions overlap; a row sits in
+    // registers (float4 pieces, all loads issued at once) when K <= 1024, else its tail is read again from L1.
+    // Statistics in two passes in float32, as the separate norm kernel does.
+    // two rows per warp where a warp has more than one row; 16 warps have too few registers for that
+    constexpr bool PAIR = WARPS <= 8 && TOK > WARPS;
+    for (int m0 = warp; m0 < M; m0 += (PAIR ? 2 : 1) * WARPS) {
         constexpr int HOLD = 8;
-        float4 v[HOLD];
-        float sum = 0.f;
+        const int m1 = m0 + WARPS;
+        const bool two = PAIR && m1 < M;
+        const float4* xa = reinterpret_cast<const float4*>(in.x + (size_t)(in.rows ? in.rows[m0] : m0) * in.ldx);
+        const float4* xb = two ? reinterpret_cast<const float4*>(in.x + (size_t)(in.rows ? in.rows[m1] : m1) * in.ldx) : xa;
+        float4 va[HOLD], vb[HOLD];
 #pragma unroll
         for (int i = 0; i < HOLD; ++i) {
             int c = lane + 32 * i;
-            v[i] = c < quads ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-            sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            va[i] = c < quads ? xa[c] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        for (int c = lane + 32 * HOLD; c < quads; c += 32) { float4 y = xr[c]; sum += (y.x + y.y) + (y.z + y.w); }
-        const float mean = in.has_mean ? warp_sum(sum) / (float)K : 0.f;
-        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            int c = lane + 32 * i;
+            vb[i] = (two && c < quads) ? xb[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            sum_a += (va[i].x + va[i].y) + (va[i].z + va[i].w);
+            sum_b += (vb[i].x + vb[i].y) + (vb[i].z + vb[i].w);
+        }
+        for (int c = lane + 32 * HOLD; c < quads; c += 32) {
+            float4 y = xa[c]; sum_a += (y.x + y.y) + (y.z + y.w);
+            float4 z = xb[c]; sum_b += (z.x + z.y) + (z.z + z.w);
+        }
+        sum_a = warp_sum(sum_a);
+        sum_b = warp_sum(sum_b);
+        const float mean_a = in.has_mean ? sum_a / (float)K : 0.f;
+        const float mean_b = in.has_mean ? sum_b / (float)K : 0.f;
+        float sq_a = 0.f, sq_b = 0.f;
 #pragma unroll
         for (int i = 0; i < HOLD; ++i) {
             if (lane + 32 * i < quads) {
-                float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
-                sq += (a * a + b * b) + (c * c + d * d);
+                float a = va[i].x - mean_a, b = va[i].y - mean_a, c = va[i].z - mean_a, d = va[i].w - mean_a;
+                sq_a += (a * a + b * b) + (c * c + d * d);
+                a = vb[i].x - mean_b, b = vb[i].y - mean_b, c = vb[i].z - mean_b, d = vb[i].w - mean_b;
+                sq_b += (a * a + b * b) + (c * c + d * d);
             }
         }
         for (int c = lane + 32 * HOLD; c < quads; c += 32) {
-            float4 y = xr[c];
-            float a = y.x - mean, b = y.y - mean, cc = y.z - mean, d = y.w - mean;
-            sq += (a * a + b * b) + (cc * cc + d * d);
+            float4 y = xa[c];
+            float a = y.x - mean_a, b = y.y - mean_a, cc = y.z - mean_a, d = y.w - mean_a;
+            sq_a += (a * a + b * b) + (cc * cc + d * d);
+            y = xb[c];
+            a = y.x - mean_b, b = y.y - mean_b, cc = y.z - mean_b, d = y.w - mean_b;
+            sq_b += (a * a + b * b) + (cc * cc + d * d);
         }
-        const float rstd = rsqrtf(warp_sum(sq) / (float)K + in.eps);
-        const float4* g4 = reinterpret_cast<const float4*>(in.gamma);
-        const float4* b4 = reinterpret_cast<const float4*>(in.beta);
-        for (int c = lane; c < quads; c += 32) {
-            const int i = c >> 5;
-            float4 y = (i < HOLD) ? make_float4(0.f, 0.f, 0.f, 0.f) : xr[c];
-#pragma unroll
-            for (int j = 0; j < HOLD; ++j) if (j == i) y = v[j];
-            const float4 gm = g4[c];
-            const float4 bt = in.beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sq_a = warp_sum(sq_a);
+        sq_b = warp_sum(sq_b);
+        const float rstd_a = rsqrtf(sq_a / (float)K + in.eps);
+        const float rstd_b = rsqrtf(sq_b / (float)K + in.eps);
+        auto put = [&](int m, int c, const float4& y, float mean, float rstd) {
+            const float4 gm = reinterpret_cast<const float4*>(gamma_s)[c];
+            const float4 bt = reinterpret_cast<const float4*>(beta_s)[c];
             __nv_bfloat162 lo = __floats2bfloat162_rn((y.x - mean) * rstd * gm.x + bt.x, (y.y - mean) * rstd * gm.y + bt.y);
             __nv_bfloat162 hi = __floats2bfloat162_rn((y.z - mean) * rstd * gm.z + bt.z, (y.w - mean) * rstd * gm.w + bt.w);
             *reinterpret_cast<uint2*>(a_s + (size_t)m * lda_s + 4 * c) =
                 make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        };
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            const int c = lane + 32 * i;
+            if (c < quads) {
+                put(m0, c, va[i], mean_a, rstd_a);
+                if (two) put(m1, c, vb[i], mean_b, rstd_b);
+            }
+        }
+        for (int c = lane + 32 * HOLD; c < quads; c += 32) {
+            put(m0, c, xa[c], mean_a, rstd_a);
+            if (two) put(m1, c, xb[c], mean_b, rstd_b);
         }
     }
     __syncthreads();
@@ -322,11 +398,8 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
             __nv_bfloat16* pool = kv.k_pool;
             if (c >= kv.kv_width) { c -= kv.kv_width; pool = kv.v_pool; }
             int head = c / kv.head_dim, d = c - head * kv.head_dim;
-            int p = kv.positions[m];
-            int page = kv.block_table[(size_t)kv.token_item[m] * kv.bt_stride + p / kv.page_size];
-            if (page >= 0)
-                pool[(size_t)page * kv.page_stride + ((size_t)head * kv.page_size + (p % kv.page_size)) * kv.head_dim + d] =
-                    __float2bfloat16_rn(v);
+            const long long base = dst_s[m];
+            if (base >= 0) pool[base + (long long)head * kv.page_size * kv.head_dim + d] = __float2bfloat16_rn(v);
             continue;
         }
         size_t o = (size_t)m * ldo + n;
@@ -335,11 +408,17 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
     }
 }
 
-template <int MT, int WARPS, typename TOut>
+// Shared memory of the fused kernel for MT token tiles, WARPS warps and width K.
+inline size_t skinny_fused_smem(int MT, int WARPS, int K) {
+    return (size_t)WARPS * 16 * 8 * MT * sizeof(float) + (size_t)2 * K * sizeof(float) + (size_t)8 * MT * 8 +
+           (size_t)8 * MT * (K + 8) * 2;
+}
+
+template <int MT, int WARPS, int UNROLL, typename TOut>
 int launch_skinny_fused(const NormInput& in, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
                         int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
-    size_t smem = (size_t)WARPS * 16 * 8 * MT * sizeof(float) + (size_t)8 * MT * (K + 8) * 2;
-    auto kernel = gemm_skinny_fused_kernel<MT, WARPS, TOut>;
+    size_t smem = skinny_fused_smem(MT, WARPS, K);
+    auto kernel = gemm_skinny_fused_kernel<MT, WARPS, UNROLL, TOut>;
     if (smem > 200 * 1024) return PS_ERR_UNSUPPORTED;
     static size_t raised = 48 * 1024;
     if (smem > raised) {
@@ -354,10 +433,12 @@ int launch_skinny_fused(const NormInput& in, const void* W, int ldw, const float
 template <int MT, typename TOut>
 int pick_warps_fused(const NormInput& in, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N,
                      int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+    // at least 8 warps: they also share the rows of the norm between them
+    // UNROLL: the k steps of a warp whose weights are fetched before anything else
     int steps = (K + 31) / 32;
-    if (steps <= 24) return launch_skinny_fused<MT, 4, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
-    if (steps <= 48) return launch_skinny_fused<MT, 8, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
-    return launch_skinny_fused<MT, 16, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    if (steps <= 24) return launch_skinny_fused<MT, 8, 3, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    if (steps <= 48) return launch_skinny_fused<MT, 8, 6, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    return launch_skinny_fused<MT, 16, 6, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
 }
 
 template <typename TOut>

@@ -32,6 +32,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int V,
     __shared__ float best_v[NT / 32];
     __shared__ int best_i[NT / 32];
     pdl_prologue();
+    logits = pdl_fresh(logits);
     int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     float temp = temperature ? temperature[r] : 0.f;
@@ -70,6 +71,7 @@ __global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict_
                                int* __restrict__ positions, int* __restrict__ kv_len,
                                int* __restrict__ history, int* __restrict__ step_counter, int B, int max_steps) {
     pdl_prologue();
+    sampled = pdl_fresh(sampled);
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     int step = *step_counter;
     if (i < B) {

@@ -59,6 +59,7 @@ class BatchLayout:
     logit_rows: int = 0
     temperature: int = 0          # float32 bits, one per item
     seed: int = 0                 # 64-bit, two words per item
+    counter: int = 0              # one word, uploaded as 0: decode steps the device has run since the upload
     tables: List[int] = field(default_factory=list)
     total: int = 0
 
@@ -68,7 +69,7 @@ class BatchLayout:
                             ("token_item", self.num_tokens), ("item_slot", self.num_items),
                             ("q_start", self.num_items + 1), ("kv_len", self.num_items),
                             ("logit_rows", max(self.num_rows, 1)), ("temperature", self.num_items),
-                            ("seed", 2 * self.num_items)):
+                            ("seed", 2 * self.num_items), ("counter", 1)):
             setattr(self, name, cursor)
             cursor += _pad4(count)
         self.tables = []
@@ -79,7 +80,10 @@ class BatchLayout:
 
 
 class HostBatch:
-    """Host-side (numpy) view of a step, for parts that need host logic and for tests."""
+    """Host-side (numpy) view of a step, for parts that need host logic and for tests.
+
+    The arrays are views of the step's pinned staging buffer: they hold while the step runs and are
+    overwritten a few steps later."""
 
     def __init__(self, token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows, requests):
         self.token_ids = token_ids
@@ -108,7 +112,7 @@ class StepContext:
 
     def __init__(self, layout: BatchLayout, device_buffer: torch.Tensor, host: HostBatch, cache, status,
                  max_q_len: int, max_kv_len: int, num_short_items: int = None, num_short_tokens: int = None,
-                 num_long_blocks: int = 0):
+                 num_long_blocks: int = 0, views: "DeviceViews" = None):
         self.layout = layout
         self.host = host
         self.cache = cache
@@ -122,6 +126,26 @@ class StepContext:
         self.num_short_items = layout.num_items if num_short_items is None else num_short_items
         self.num_short_tokens = layout.num_tokens if num_short_tokens is None else num_short_tokens
         self.num_long_blocks = num_long_blocks      # 64-query blocks of the long entries
+        views = views if views is not None else DeviceViews(layout, device_buffer)
+        self.token_ids = views.token_ids
+        self.positions = views.positions
+        self.token_item = views.token_item
+        self.item_slot = views.item_slot
+        self.q_start = views.q_start
+        self.kv_len = views.kv_len
+        self.logit_rows = views.logit_rows
+        self.temperature = views.temperature
+        self.seed = views.seed
+        self.step_counter = views.step_counter
+        self.block_tables = views.block_tables
+        self.decode_only = (layout.num_tokens == layout.num_items)
+
+
+class DeviceViews:
+    """The sections of the packed device buffer as tensors; depends on the layout only, so the runner
+    keeps one per step shape."""
+
+    def __init__(self, layout: BatchLayout, device_buffer: torch.Tensor):
         T, I, R = layout.num_tokens, layout.num_items, layout.num_rows
         buf = device_buffer
         self.token_ids = buf[layout.token_ids:layout.token_ids + T]
@@ -133,8 +157,8 @@ class StepContext:
         self.logit_rows = buf[layout.logit_rows:layout.logit_rows + R]
         self.temperature = buf[layout.temperature:layout.temperature + I].view(torch.float32)
         self.seed = buf[layout.seed:layout.seed + 2 * I].view(torch.int64)
+        self.step_counter = buf[layout.counter:layout.counter + 1]
         self.block_tables = [
             buf[offset:offset + I * width].view(I, width)
             for offset, width in zip(layout.tables, layout.table_widths)
         ]
-        self.decode_only = (T == I)

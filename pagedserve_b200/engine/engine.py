@@ -116,6 +116,11 @@ class Engine:
         returns the sampled tokens as an int32 array ``[steps, batch]``."""
         return self.runner.decode(entries, temperatures, seeds, steps)
 
+    def decode_tokens(self, requests: Sequence[Hashable], tokens: Sequence[int], temperatures, seeds,
+                      steps: int = 1):
+        """``decode`` with the requests and their next tokens as two sequences (no entry objects)."""
+        return self.runner.decode_tokens(requests, tokens, temperatures, seeds, steps)
+
     def finish(self, request: Hashable) -> None:
         self.runner.finish(request)
 

@@ -183,27 +183,31 @@ class Scheduler:
             request.reserved_blocks = self._required_blocks(request)
             self.reserved_blocks += request.reserved_blocks
 
-        entries = []
-        sampling = []        # (request, position of the token to be sampled)
-        for request, count in selected:
-            if request.pending_token_id is not None:
-                tokens = [request.pending_token_id]
-                want = [0]
-            else:
-                start = request.prefill_cursor
-                tokens = request.prompt_token_ids[start:start + count]
-                last = start + count == len(request.prompt_token_ids)
-                want = [count - 1] if last else []           # reference: :191
-            if want:
-                sampling.append(request)
-            entries.append(StepEntry(request.request_id, tokens, want))
         decode_only = all(request.pending_token_id is not None for request, _ in selected)
-        fused_decode = getattr(self.engine, "decode", None) if decode_only else None
+        fused_decode = getattr(self.engine, "decode_tokens", None) if decode_only else None
+        entries = []
+        sampling = []        # requests whose next token is drawn in this step
+        if fused_decode is not None:
+            sampling = [request for request, _ in selected]
+        else:
+            for request, count in selected:
+                if request.pending_token_id is not None:
+                    tokens = [request.pending_token_id]
+                    want = [0]
+                else:
+                    start = request.prefill_cursor
+                    tokens = request.prompt_token_ids[start:start + count]
+                    last = start + count == len(request.prompt_token_ids)
+                    want = [count - 1] if last else []           # reference: :191
+                if want:
+                    sampling.append(request)
+                entries.append(StepEntry(request.request_id, tokens, want))
         try:
             if fused_decode is not None:
-                # every entry is one decoded token: forward and sampling run as one device step
+                # every request brings one decoded token: forward and sampling run as one device step
                 tokens = fused_decode(
-                    entries,
+                    [request.request_id for request in sampling],
+                    [request.pending_token_id for request in sampling],
                     [request.temperature for request in sampling],
                     [request.seed for request in sampling],
                     1,

@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from pagedserve_b200.cache.manager import CacheFull, CacheManager
-from pagedserve_b200.engine.batch import BatchLayout, HostBatch, StepContext, StepEntry
+from pagedserve_b200.engine.batch import BatchLayout, DeviceViews, HostBatch, StepContext, StepEntry
 
 
 class StepError(ValueError):
@@ -72,7 +72,8 @@ class ModelRunner:
         self._history = torch.zeros(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32,
                                     device=self.device)
         self._history_host = torch.empty(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32).pin_memory()
-        self._step_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._shapes = {}                 # (T, I, R) -> (BatchLayout, DeviceViews)
+        self._ramp = np.arange(cache.max_slots + 2, dtype=np.int32)
         # the persistent decode kernel, when the model's parts allow it
         self.decode_stack = None
         # (opt-in: measured on B200 its ~62 grid barriers per step cost as much as the launch gaps they
@@ -87,18 +88,19 @@ class ModelRunner:
             return
         torch.cuda.synchronize(self.device)
         self._graphs = {}                 # captured graphs point into the old buffer
+        self._shapes = {}
         self._capacity = int(needed * 1.25) + 64
         self._device_buffer = torch.empty(self._capacity, dtype=torch.int32, device=self.device)
         self._staging = [torch.empty(self._capacity, dtype=torch.int32).pin_memory()
                          for _ in range(self.STAGING_BUFFERS)]
-        self._staging_events = [None] * self.STAGING_BUFFERS
+        self._staging_numpy = [staging.numpy() for staging in self._staging]
+        self._staging_events = [torch.cuda.Event() for _ in range(self.STAGING_BUFFERS)]
+        for event in self._staging_events:
+            event.record()
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry], extra_tokens: int = 0, sampling=None) -> StepContext:
-        """Validate, take pages for the new positions, build and upload the metadata.
-
-        ``extra_tokens`` more positions per request get pages too (a run of several decode steps on
-        the device); ``sampling`` = (temperatures, seeds) per entry is uploaded with the batch."""
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Validate, take pages for the new positions, build and upload the metadata."""
         if not entries:
             raise StepError("a step cannot be empty")                 # reference: iteration.py:50-51
         cache = self.cache
@@ -120,11 +122,11 @@ class ModelRunner:
                     cache.admit(entry.request)
                     admitted.append(entry.request)
                 start = cache.length(entry.request)
-                if start + len(entry.tokens) + extra_tokens > self.max_model_len:
+                if start + len(entry.tokens) > self.max_model_len:
                     # reference: src/model/paged_decoder.py:521-522
                     raise StepError(f"request {entry.request!r} would pass the model's maximum length "
                                     f"{self.max_model_len}")
-                cache.extend(entry.request, len(entry.tokens) + extra_tokens)
+                cache.extend(entry.request, len(entry.tokens))
                 extended.append(entry.request)
         except Exception:
             for request in extended:
@@ -137,14 +139,7 @@ class ModelRunner:
         T = sum(len(entry.tokens) for entry in entries)
         I = len(entries)
         R = sum(len(entry.want) for entry in entries)
-        layout = BatchLayout(T, I, R, self.table_widths)
-        self._grow(layout.total)
-        turn = self._turn
-        self._turn = (turn + 1) % self.STAGING_BUFFERS
-        if self._staging_events[turn] is not None:
-            self._staging_events[turn].synchronize()
-        staging = self._staging[turn]
-        host = staging.numpy()
+        layout, views, staging, host = self._stage(T, I, R)
 
         token_ids = host[layout.token_ids:layout.token_ids + T]
         positions = host[layout.positions:layout.positions + T]
@@ -190,27 +185,103 @@ class ModelRunner:
             for place in entry.want:
                 logit_rows[row] = starts[source] + place
                 row += 1
+        for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
+            cache.table_rows(group_index, item_slot, host[offset:offset + I * width].reshape(I, width))
+
+        host[layout.counter] = 0
+        self._upload(layout, staging)
+        host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
+                               [entry.request for entry in laid_out])
+        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, max_q, max_kv,
+                           num_short_items, num_short_tokens, num_long_blocks, views=views)
+
+    def _stage(self, T: int, I: int, R: int):
+        """The layout of a step shape, its device views, and the pinned staging buffer of this turn."""
+        shape = self._shapes.get((T, I, R))
+        if shape is None:
+            layout = BatchLayout(T, I, R, self.table_widths)
+            self._grow(layout.total)
+            if len(self._shapes) >= 1024:
+                self._shapes.clear()
+            shape = self._shapes[(T, I, R)] = (layout, DeviceViews(layout, self._device_buffer))
+        layout, views = shape
+        turn = self._turn
+        self._turn = (turn + 1) % self.STAGING_BUFFERS
+        self._staging_events[turn].synchronize()      # the copy that last read this buffer is done
+        self._staging_turn = turn
+        return layout, views, self._staging[turn], self._staging_numpy[turn]
+
+    def _upload(self, layout: BatchLayout, staging: torch.Tensor) -> None:
+        self._device_buffer[:layout.total].copy_(staging[:layout.total], non_blocking=True)
+        self._staging_events[self._staging_turn].record()
+        self.h2d_bytes = layout.total * 4
+
+    def _prepare_single_tokens(self, requests, tokens: np.ndarray, extra_tokens: int, sampling) -> StepContext:
+        """``prepare`` for a step in which every request brings one token and wants its logits: the same
+        buffer contents, filled with whole-array operations instead of a loop over entries.  ``extra_tokens``
+        more positions per request get pages too (a run of several decode steps on the device);
+        ``sampling`` = (temperatures, seeds) per request is uploaded with the batch."""
+        cache = self.cache
+        I = len(requests)
+        if I == 0:
+            raise StepError("a step cannot be empty")
+        slot_of = cache.slot_of
+        try:
+            slots = np.fromiter((slot_of[request] for request in requests), dtype=np.int64, count=I)
+        except KeyError as missing:
+            raise StepError(f"request {missing.args[0]!r} has no prompt in the cache") from None
+        if I > 1 and np.unique(slots).size != I:
+            raise StepError("a request can appear only once in a step")
+        low, high = int(tokens.min()), int(tokens.max())
+        if low < 0 or high >= self.vocab_size:
+            raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
+                            f"{self.vocab_size}")
+        starts = cache.lengths[slots]
+        if int(starts.max()) + 1 + extra_tokens > self.max_model_len:
+            raise StepError(f"a request would pass the model's maximum length {self.max_model_len}")
+        extended: List[Hashable] = []
+        try:
+            for request in requests:
+                cache.extend(request, 1 + extra_tokens)
+                extended.append(request)
+        except Exception:
+            for request in extended:
+                cache.rollback(request)
+            raise
+        self._admitted_in_step = []
+
+        layout, views, staging, host = self._stage(I, I, I)
+        token_ids = host[layout.token_ids:layout.token_ids + I]
+        positions = host[layout.positions:layout.positions + I]
+        token_item = host[layout.token_item:layout.token_item + I]
+        item_slot = host[layout.item_slot:layout.item_slot + I]
+        q_start = host[layout.q_start:layout.q_start + I + 1]
+        kv_len = host[layout.kv_len:layout.kv_len + I]
+        logit_rows = host[layout.logit_rows:layout.logit_rows + I]
+        ramp = self._ramp[:I + 1]
+        token_ids[:] = tokens
+        positions[:] = starts
+        token_item[:] = ramp[:I]
+        item_slot[:] = slots
+        q_start[:] = ramp
+        np.add(starts, 1, out=kv_len)
+        logit_rows[:] = ramp[:I]
         if sampling is not None:
             temperatures, seeds = sampling
-            host[layout.temperature:layout.temperature + I].view(np.float32)[:] = np.asarray(
-                [temperatures[source] for source in order], dtype=np.float32)
-            host[layout.seed:layout.seed + 2 * I].view(np.uint64)[:] = np.asarray(
-                [int(seeds[source]) & 0xFFFFFFFFFFFFFFFF for source in order], dtype=np.uint64)
+            host[layout.temperature:layout.temperature + I].view(np.float32)[:] = temperatures
+            try:
+                seed_words = np.asarray(seeds, dtype=np.int64).view(np.uint64)
+            except OverflowError:
+                seed_words = np.array([int(seed) & 0xFFFFFFFFFFFFFFFF for seed in seeds], dtype=np.uint64)
+            host[layout.seed:layout.seed + 2 * I].view(np.uint64)[:] = seed_words
+        host[layout.counter] = 0
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
-            table = host[offset:offset + I * width].reshape(I, width)
-            for index, entry in enumerate(laid_out):
-                cache.table_row(group_index, entry.request, table[index])
-
-        self._device_buffer[:layout.total].copy_(staging[:layout.total], non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
-        self._staging_events[turn] = event
-        host_batch = HostBatch(token_ids.copy(), positions.copy(), token_item.copy(), item_slot.copy(),
-                               q_start.copy(), kv_len.copy(), logit_rows.copy(),
-                               [entry.request for entry in laid_out])
-        self.h2d_bytes = layout.total * 4
-        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, max_q, max_kv,
-                           num_short_items, num_short_tokens, num_long_blocks)
+            cache.table_rows(group_index, slots, host[offset:offset + I * width].reshape(I, width))
+        self._upload(layout, staging)
+        host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
+                               list(requests))
+        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, 1,
+                           int(kv_len.max()), I, I, 0, views=views)
 
     def _abandon(self, entries) -> None:
         for entry in entries:
@@ -247,28 +318,36 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ decode-only steps
     def decode(self, entries: Sequence[StepEntry], temperatures, seeds, steps: int = 1) -> np.ndarray:
+        """``decode_tokens`` for entries of one token each."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries or any(len(entry.tokens) != 1 for entry in entries):
+            raise StepError("decode takes exactly one token per request")
+        return self.decode_tokens([entry.request for entry in entries],
+                                  [int(entry.tokens[0]) for entry in entries], temperatures, seeds, steps)
+
+    def decode_tokens(self, requests: Sequence[Hashable], tokens: Sequence[int], temperatures, seeds,
+                      steps: int = 1) -> np.ndarray:
         """Run ``steps`` decode steps of a batch of single tokens without the host in between.
 
-        Every entry holds the one next token of a request whose prompt is already in the cache.
+        ``tokens[i]`` is the one next token of ``requests[i]``, whose earlier tokens are in the cache.
         Each step samples on the device (greedy or temperature), feeds the token back as the next
         input and moves the request one position on.  Returns the sampled tokens ``[steps, B]``.
         The step is replayed as a CUDA graph (reference: decode-only fast path with CUDA graphs,
         src/model/paged_decoder.py:385-496) unless graphs are disabled.
         """
-        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        if not entries or any(len(entry.tokens) != 1 for entry in entries):
+        tokens = np.asarray(tokens)
+        if tokens.ndim != 1 or tokens.size != len(requests) or tokens.size == 0:
             raise StepError("decode takes exactly one token per request")
+        if not np.issubdtype(tokens.dtype, np.integer):
+            raise StepError("token ids must be integers")
         if not (1 <= steps <= self.MAX_DEVICE_STEPS):
             raise StepError(f"steps must be between 1 and {self.MAX_DEVICE_STEPS}")
-        for entry in entries:
-            entry.want = [0]
-        ctx = self.prepare(entries, extra_tokens=steps - 1, sampling=(temperatures, seeds))
+        ctx = self._prepare_single_tokens(requests, tokens, steps - 1, (temperatures, seeds))
         B = ctx.num_items
         try:
-            self._step_counter.zero_()
             if self._stack_takes(ctx):
                 self.decode_stack.run(ctx, steps, False, True, sampled=self._sampled, history=self._history,
-                                      step_counter=self._step_counter, max_steps=self.MAX_DEVICE_STEPS,
+                                      step_counter=ctx.step_counter, max_steps=self.MAX_DEVICE_STEPS,
                                       max_kv_len=ctx.max_kv_len + steps - 1)
             elif self.enable_cuda_graphs:
                 graph = self._run_decode_graph(ctx, "sample")
@@ -281,10 +360,12 @@ class ModelRunner:
             self._history_host[:steps * B].copy_(self._history[:steps * B], non_blocking=True)
             torch.cuda.current_stream().synchronize()
         except Exception:
-            self._abandon(entries)
+            for request in requests:
+                self.cache.rollback(request)
             raise
-        for entry in entries:
-            self.cache.commit(entry.request)
+        commit = self.cache.commit
+        for request in requests:
+            commit(request)
         self.steps += steps
         self.tokens_run += steps * B
         return self._history_host[:steps * B].numpy().reshape(steps, B).copy()
@@ -298,7 +379,7 @@ class ModelRunner:
         sampled = self._sampled[:B]
         # the token drawn now will sit at position (input position + 1)
         self.ops.sample(logits, ctx.temperature, ctx.seed, ctx.positions, sampled, pos_offset=1)
-        self.ops.advance(sampled, ctx.token_ids, ctx.positions, ctx.kv_len, self._history, self._step_counter,
+        self.ops.advance(sampled, ctx.token_ids, ctx.positions, ctx.kv_len, self._history, ctx.step_counter,
                          self.MAX_DEVICE_STEPS)
         return logits
 

@@ -58,19 +58,31 @@ def bench_gemm(args):
     out_dtype = torch.float32 if args.out == "float32" else torch.bfloat16
     out = torch.empty(M, N, dtype=out_dtype, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    acc = args.accumulate
+    if args.norm:
+        from types import SimpleNamespace
+
+        from pagedserve_b200.parts.norms import DeferredNorm
+
+        norm = SimpleNamespace(weight=torch.ones(K, device="cuda"), bias=torch.zeros(K, device="cuda"),
+                               params={"eps": 1e-5, "has_mean": True})
+        x32 = [t.float() for t in a]
 
     def run(i):
         j = i % copies
-        if args.impl == "tc":
-            ops.linear_tc(a[j], w[j], bias, out, act=args.act, status=status, bn=args.bn)
+        if args.norm:
+            ops.linear_skinny_fused(DeferredNorm(norm, x32[j]), w[j], bias, out, act=args.act, accumulate=acc)
+        elif args.impl == "tc":
+            ops.linear_tc(a[j], w[j], bias, out, act=args.act, accumulate=acc, status=status, bn=args.bn)
         elif args.impl == "skinny":
-            ops.linear_skinny(a[j], w[j], bias, out, act=args.act)
+            ops.linear_skinny(a[j], w[j], bias, out, act=args.act, accumulate=acc)
         else:
-            ops.linear_simt(a[j], w[j], bias, out, act=args.act)
+            ops.linear_simt(a[j], w[j], bias, out, act=args.act, accumulate=acc)
 
     seconds = _time(run, args.iters, graph=args.graph)
     flops = 2.0 * M * N * K
-    print(f"gemm {args.impl} M={M} N={N} K={K} bn={args.bn} out={args.out}: {seconds * 1e6:.2f} us, "
+    print(f"gemm {'skinny+norm' if args.norm else args.impl} M={M} N={N} K={K} bn={args.bn} out={args.out}"
+          f"{' accumulate' if acc else ''}: {seconds * 1e6:.2f} us, "
           f"{flops / seconds / 1e12:.1f} TFLOP/s, weight stream {N * K * 2 / seconds / 1e9:.0f} GB/s, "
           f"status {int(status.item())}")
 
@@ -113,6 +125,9 @@ def main(argv=None):
     g.add_argument("--impl", default="tc", choices=("tc", "skinny", "simt"))
     g.add_argument("--act", default=None)
     g.add_argument("--out", default="bfloat16", choices=("bfloat16", "float32"))
+    g.add_argument("--accumulate", action="store_true", help="add the product to what the output holds")
+    g.add_argument("--norm", action="store_true",
+                   help="the few-rows kernel with a LayerNorm of float32 rows fused in front")
     g.add_argument("--iters", type=int, default=50)
     g.add_argument("--graph", action="store_true", help="replay the calls as one CUDA graph")
     a = sub.add_parser("attention")

@@ -249,7 +249,8 @@ class Ops:
         norm = a.norm
         # every CTA (16 output columns) recomputes the statistics: worth it only while the product is narrow
         rows = 8 if a.shape[0] <= 8 else 16 if a.shape[0] <= 16 else 32
-        if rows * (a.shape[1] + 8) * 2 > 96 * 1024:          # the normed rows are staged in shared memory
+        # the normed rows and the norm's scale and shift are staged in shared memory
+        if rows * (a.shape[1] + 8) * 2 + 8 * a.shape[1] > 96 * 1024:
             return False
         return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS and w.shape[0] <= 8192
                 and type(norm).__name__ == "LayerNorm" and a.x.dtype == torch.float32

@@ -192,7 +192,8 @@ def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
     for has_mean, has_bias, use_rows in ((True, True, False), (False, False, True), (True, True, True)):
         norm = FakeNorm(has_mean, has_bias)
         deferred = DeferredNorm(norm, x if use_rows else x[:M], rows if use_rows else None)
-        staged = (8 if M <= 8 else 16 if M <= 16 else 32) * (K + 8) * 2       # bytes of normed rows in shared memory
+        # bytes of normed rows and of the norm's scale and shift in shared memory
+        staged = (8 if M <= 8 else 16 if M <= 16 else 32) * (K + 8) * 2 + 8 * K
         assert ops._fused_norm_ok(deferred, w) == (staged <= 96 * 1024)
         if staged > 160 * 1024:
             continue                                                            # beyond what the kernel takes
@@ -209,7 +210,7 @@ def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
         else:
             normed = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5) * norm.weight.double().cpu()
         assert rel_err(fused, gemm_reference(normed, w.cpu(), bias.cpu(), "gelu_tanh", None)) < 8e-3
-    fits = (8 if M <= 8 else 16 if M <= 16 else 32) * (K + 8) * 2 <= 96 * 1024
+    fits = (8 if M <= 8 else 16 if M <= 16 else 32) * (K + 8) * 2 + 8 * K <= 96 * 1024
     if N % 3 == 0 and (N // 3) % 16 == 0 and fits:
         # packed projection: q to the buffer, k and v into pages
         width = N // 3
