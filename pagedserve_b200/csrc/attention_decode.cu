@@ -95,6 +95,29 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // ldmatrix then come from 8 different units and fall on 8 different bank groups, although each unit is a
 // plain contiguous copy. Keys outside [lo, p] have their V rows zeroed and their scores masked.
 // KS: head-dim steps of 16 the kernel is compiled for (head_dim <= 16 * KS); fewer steps, fewer registers.
+// Thread-block clusters: the CTAs of one (token, head) form a cluster along the split axis and the first
+// of them merges the partial states out of the others' shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// How the partial states of the splits of one (token, head) are merged:
+//   n_splits == 1            nothing to merge;
+//   cluster == n_splits > 1  the splits are one thread-block cluster; the first active CTA reads the others'
+//                            (max, sum, acc) from their shared memory after a cluster barrier: no trip to
+//                            global memory, no atomics;
+//   cluster <= 1 < n_splits  through part_acc / part_ml / counters in global memory, merged by the CTA that
+//                            finishes last.
+// q_start / kv_len (both or neither): with them the kernel knows which keys of a request are older than
+// this step (positions below kv_len - new tokens). A first chunk made of such keys only is fetched BEFORE
+// the wait for the kernel that writes this step's q, k and v, so the fetch overlaps that kernel.
 template <int KS>
 __global__ void __launch_bounds__(DEC_THREADS, KS == 4 ? 6 : (KS == 8 ? 4 : 2))
 paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -105,10 +128,12 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               int bt_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
                               int window, float scale_log2, int chunk_keys, int split_chunks, int n_splits,
                               float* __restrict__ part_acc, float* __restrict__ part_ml,
-                              int* __restrict__ counters, int* __restrict__ status) {
+                              int* __restrict__ counters, int* __restrict__ status,
+                              const int* __restrict__ q_start, const int* __restrict__ kv_len, int cluster) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int unit = min(page_size, chunk_keys >> 3);                                // keys per copy
-    const int n_units = chunk_keys / unit;                                           // >= 8
+    const int n_units = chunk_keys / unit;                                           // a power of two >= 8
+    const int units_log2 = 31 - __clz(n_units);
     const int unit_elems = attention_unit_stride(unit, head_dim);                    // padded unit, elements
     // One stage of chunk buffers: measured on B200, a second stage (copying the next chunk during the
     // compute of this one) halves the CTAs per SM and was slower at every batch size (batch 64: 44 vs 36 us).
@@ -117,31 +142,58 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __nv_bfloat16* p_s = v_s + (size_t)n_units * unit_elems;                         // [chunk_keys] probabilities
     float* o_s = reinterpret_cast<float*>(p_s + chunk_keys);                         // [head_dim] merged output
     __shared__ float red_a[DEC_WARPS], red_b[DEC_WARPS];
+    __shared__ float ml_pub[2];                                                      // (max, sum) for the cluster
     __shared__ __align__(8) uint64_t bar;
     __shared__ int last_flag;
+
+    // ---- before the wait: only what no kernel of this step writes (positions, tables, older keys)
+    const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int p = positions[t];
+    const int item = token_item[t];
+    const int first_new = (q_start && kv_len) ? kv_len[item] - (q_start[item + 1] - q_start[item]) : 0;
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
+    const int first_split = first_chunk / split_chunks, last_split = last_chunk / split_chunks;
+    const int n_active = last_split - first_split + 1;
+    const bool active = split >= first_split && split <= last_split;
+    const bool by_cluster = cluster > 1 && n_active > 1;
+    if (!active && !by_cluster) return;                                // no keys here and nobody waits for us
+    const int chunk_lo = active ? max(first_chunk, split * split_chunks) : 1;
+    const int chunk_hi = active ? min(last_chunk, (split + 1) * split_chunks - 1) : 0;
+
+    const int g = h / (n_heads / n_kv_heads);
+    const int* bt = block_table + (size_t)item * bt_stride;
+    const uint32_t unit_bytes = (uint32_t)unit * head_dim * 2;
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // copies of one chunk: thread u brings unit u (K and V) if it holds keys of [lo, p]
+    auto issue_chunk = [&](int chunk) {
+        const int key0 = chunk * chunk_keys;
+        const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;
+        const int u_lo = j_lo / unit, u_hi = j_hi / unit;
+        if (tid == 0) mbar_expect_tx(&bar, 2u * unit_bytes * (uint32_t)(u_hi - u_lo + 1));
+        if (tid >= u_lo && tid <= u_hi) {
+            const int key = key0 + tid * unit;
+            const int page = bt[key / page_size];
+            const long long src = (long long)page * page_stride +
+                                  ((long long)g * page_size + (key % page_size)) * head_dim;
+            bulk_copy_g2s(k_s + (size_t)tid * unit_elems, k_pool + src, unit_bytes, &bar);
+            bulk_copy_g2s(v_s + (size_t)tid * unit_elems, v_pool + src, unit_bytes, &bar);
+        }
+    };
+    const bool prefetched = active && (chunk_lo + 1) * chunk_keys <= first_new;
+    if (prefetched) issue_chunk(chunk_lo);
 
     pdl_prologue();
     q = pdl_fresh(q);
     k_pool = pdl_fresh(k_pool);
     v_pool = pdl_fresh(v_pool);
-    const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int gq = lane >> 2, tq = lane & 3;
-    const int p = positions[t];
-    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
-    const int first_split = first_chunk / split_chunks, last_split = last_chunk / split_chunks;
-    if (split < first_split || split > last_split) return;          // no keys here
-    const int n_active = last_split - first_split + 1;
-    const int chunk_lo = max(first_chunk, split * split_chunks);
-    const int chunk_hi = min(last_chunk, (split + 1) * split_chunks - 1);
 
-    const int g = h / (n_heads / n_kv_heads);
-    const int* bt = block_table + (size_t)token_item[t] * bt_stride;
-    if (tid == 0) {
-        mbar_init(&bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
     // the query as B fragments: lanes with g == 0 hold q[16 ks + 2 t .. +1] and q[16 ks + 2 t + 8 .. +9]
     const int ksteps = head_dim >> 4;                              // <= KS
     uint32_t qb[KS][2];
@@ -156,7 +208,6 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             }
         }
     }
-    __syncthreads();
 
     // this warp owns the output rows (head dims) of m-tiles warp, warp + 4, ...
     constexpr int OT = (KS + DEC_WARPS - 1) / DEC_WARPS;          // output tiles per warp
@@ -164,35 +215,29 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 #pragma unroll
     for (int i = 0; i < OT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
-    const uint32_t unit_bytes = (uint32_t)unit * head_dim * 2;
     const int key_tiles = chunk_keys >> 4;
+    const int unit_mask = n_units - 1;
+    // MMA row m of a chunk is key (m % n_units) * unit + m / n_units and lies at element
+    // (m % n_units) * unit_elems + (m / n_units) * head_dim of the chunk buffers
+    auto row_elem = [&](int m) { return (size_t)(m & unit_mask) * unit_elems + (size_t)(m >> units_log2) * head_dim; };
+    auto row_key = [&](int m) { return (m & unit_mask) * unit + (m >> units_log2); };
     uint32_t phase = 0;
     bool ok = true;
 
     for (int chunk = chunk_lo; chunk <= chunk_hi; ++chunk) {
         const int key0 = chunk * chunk_keys;
         const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;   // valid keys of the chunk
-        const int u_lo = j_lo / unit, u_hi = j_hi / unit;
-        if (tid == 0) mbar_expect_tx(&bar, 2u * unit_bytes * (uint32_t)(u_hi - u_lo + 1));
-        if (tid >= u_lo && tid <= u_hi) {
-            const int key = key0 + tid * unit;
-            const int page = bt[key / page_size];
-            const long long src = (long long)page * page_stride +
-                                  ((long long)g * page_size + (key % page_size)) * head_dim;
-            bulk_copy_g2s(k_s + (size_t)tid * unit_elems, k_pool + src, unit_bytes, &bar);
-            bulk_copy_g2s(v_s + (size_t)tid * unit_elems, v_pool + src, unit_bytes, &bar);
-        }
+        if (!(prefetched && chunk == chunk_lo)) issue_chunk(chunk);
         if (ok && !mbar_wait_bounded(&bar, phase)) {
             ok = false;
             if (status) atomicExch(status, 2);
         }
         phase ^= 1;
         if (tid < chunk_keys) {
-            // MMA row tid is key (tid % n_units) * unit + tid / n_units; rows of keys outside [j_lo, j_hi]
-            // hold stale or no data: 0 * garbage must stay 0
-            const int key = (tid % n_units) * unit + tid / n_units;
+            // rows of keys outside [j_lo, j_hi] hold stale or no data: 0 * garbage must stay 0
+            const int key = row_key(tid);
             if (key < j_lo || key > j_hi) {
-                const size_t off = (size_t)(tid % n_units) * unit_elems + (size_t)(tid / n_units) * head_dim;
+                const size_t off = row_elem(tid);
                 uint4* vz = reinterpret_cast<uint4*>(v_s + off);
                 uint4* kz = reinterpret_cast<uint4*>(k_s + off);
                 for (int c = 0; c < (head_dim >> 3); ++c) { vz[c] = make_uint4(0, 0, 0, 0); kz[c] = make_uint4(0, 0, 0, 0); }
@@ -208,18 +253,16 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             sc[i][0] = sc[i][1] = -INFINITY;
             if (mt < key_tiles) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
+                const __nv_bfloat16* arow = k_s + row_elem(16 * mt + (lane & 15)) + (lane >> 4) * 8;
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
                     if (ks < ksteps) {
                         uint32_t a[4];
-                        const int m = 16 * mt + (lane & 15);
-                        ldsm_x4(a, k_s + (size_t)(m % n_units) * unit_elems + (size_t)(m / n_units) * head_dim +
-                                       (2 * ks + (lane >> 4)) * 8);
+                        ldsm_x4(a, arow + 16 * ks);
                         mma_16816(c, a, qb[ks][0], qb[ks][1]);
                     }
                 }
-                const int ma = 16 * mt + gq, mb = ma + 8;                 // MMA rows -> keys of the chunk
-                const int ka = (ma % n_units) * unit + ma / n_units, kb = (mb % n_units) * unit + mb / n_units;
+                const int ka = row_key(16 * mt + gq), kb = row_key(16 * mt + gq + 8);   // MMA rows -> keys of the chunk
                 if (tq == 0 && ok) {
                     if (ka >= j_lo && ka <= j_hi) sc[i][0] = c[0] * scale_log2;
                     if (kb >= j_lo && kb <= j_hi) sc[i][1] = c[2] * scale_log2;
@@ -257,11 +300,11 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             const int dt = warp + DEC_WARPS * i;
             if (dt < ksteps) {
                 o_acc[i][0] *= corr; o_acc[i][1] *= corr; o_acc[i][2] *= corr; o_acc[i][3] *= corr;
+                const int col = (2 * dt + ((lane >> 3) & 1)) * 8;
+                const int r = (lane & 7) + ((lane >> 4) & 1) * 8;
                 for (int kk = 0; kk < key_tiles; ++kk) {
                     uint32_t a[4];
-                    const int m = 16 * kk + (lane & 7) + ((lane >> 4) & 1) * 8;
-                    ldsm_x4_trans(a, v_s + (size_t)(m % n_units) * unit_elems + (size_t)(m / n_units) * head_dim +
-                                         (2 * dt + ((lane >> 3) & 1)) * 8);
+                    ldsm_x4_trans(a, v_s + row_elem(16 * kk + r) + col);
                     uint32_t b0 = 0u, b1 = 0u;
                     if (gq == 0) {
                         b0 = *reinterpret_cast<const uint32_t*>(p_s + 16 * kk + 2 * tq);
@@ -283,11 +326,32 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             o_s[16 * dt + gq + 8] = o_acc[i][2];
         }
     }
+    if (tid == 0) { ml_pub[0] = m_run; ml_pub[1] = l_run; }
     __syncthreads();
     if (n_splits == 1 || n_active == 1) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         for (int d = tid; d < head_dim; d += DEC_THREADS)
             out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o_s[d] * inv);
+        return;
+    }
+    if (by_cluster) {
+        // every CTA of the cluster has published (max, sum, acc) in its shared memory (idle ones: -inf, 0, 0)
+        cluster_sync_all();
+        if (split == first_split) {
+            float M = -INFINITY;
+            for (int r = first_split; r <= last_split; ++r) M = fmaxf(M, ld_cluster_f32(&ml_pub[0], r));
+            float L = 0.f;
+            for (int r = first_split; r <= last_split; ++r)
+                L += ld_cluster_f32(&ml_pub[1], r) * exp2f(ld_cluster_f32(&ml_pub[0], r) - M);
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            for (int d = tid; d < head_dim; d += DEC_THREADS) {
+                float o = 0.f;
+                for (int r = first_split; r <= last_split; ++r)
+                    o += ld_cluster_f32(&o_s[d], r) * exp2f(ld_cluster_f32(&ml_pub[0], r) - M);
+                out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
+            }
+        }
+        cluster_sync_all();                                   // nobody's shared memory goes away before it was read
         return;
     }
     // several splits hold keys of this token: publish the partial state
@@ -350,13 +414,16 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
                                    const int* positions, const int* block_table, int bt_stride, int T, int n_heads,
                                    int n_kv_heads, int head_dim, int page_size, int window, float scale,
                                    int split_tiles, int n_splits, float* part_acc, float* part_ml, int* counters,
-                                   int* status, void* stream) {
+                                   int* status, void* stream, const int* q_start = nullptr,
+                                   const int* kv_len = nullptr, int cluster = 1) {
     if (T <= 0) return PS_OK;
+    if ((q_start == nullptr) != (kv_len == nullptr)) return PS_ERR_BAD_ARGUMENT;
+    if (cluster > 1 && (cluster != n_splits || cluster > 8 || (cluster & (cluster - 1)))) return PS_ERR_BAD_ARGUMENT;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return PS_ERR_BAD_ARGUMENT;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return PS_ERR_UNSUPPORTED;
     if (page_size <= 0 || page_size > 64 || (page_size & (page_size - 1))) return PS_ERR_UNSUPPORTED;
     if (n_heads > 65535 || n_splits > 65535 || n_splits < 1 || split_tiles < 1) return PS_ERR_UNSUPPORTED;
-    if (n_splits > 1 && (!part_acc || !part_ml || !counters)) return PS_ERR_BAD_ARGUMENT;
+    if (n_splits > 1 && cluster <= 1 && (!part_acc || !part_ml || !counters)) return PS_ERR_BAD_ARGUMENT;
     if (q_stride % 8 != 0 || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || page_stride % 8 != 0)
         return PS_ERR_UNSUPPORTED;
     const int chunk_keys = ps::attention_chunk_keys(head_dim, page_size);
@@ -376,12 +443,12 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
                 return PS_ERR_LAUNCH;                                                                                \
             raised = smem;                                                                                           \
         }                                                                                                            \
-        return ps::launch_pdl(kernel, grid, dim3(ps::DEC_THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,       \
-                              (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,                          \
-                              (const __nv_bfloat16*)v_pool, page_stride, token_item, positions, block_table,          \
-                              bt_stride, n_heads, n_kv_heads, head_dim, page_size, window,                            \
-                              scale * 1.4426950408889634f, chunk_keys, split_chunks, n_splits, part_acc, part_ml,     \
-                              counters, status);                                                                      \
+        return ps::launch_pdl_cluster(kernel, grid, dim3(ps::DEC_THREADS), smem, s, cluster,                         \
+                                      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,             \
+                                      (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride,        \
+                                      token_item, positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim,   \
+                                      page_size, window, scale * 1.4426950408889634f, chunk_keys, split_chunks,       \
+                                      n_splits, part_acc, part_ml, counters, status, q_start, kv_len, cluster);       \
     }
     if (head_dim <= 64) PS_DECODE_LAUNCH(4)
     if (head_dim <= 128) PS_DECODE_LAUNCH(8)
@@ -411,6 +478,24 @@ PS_EXPORT int ps_paged_attention_decode_checked(const void* q, int q_stride, voi
     return launch_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
                                    block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window, scale,
                                    split_tiles, n_splits, part_acc, part_ml, counters, status, stream);
+}
+
+// The general entry. cluster > 1: the n_splits = cluster (2, 4 or 8) splits of a (token, head) are one
+// thread-block cluster and merge through shared memory (no scratch needed); cluster <= 1: any n_splits, merged
+// through the scratch arrays. q_start / kv_len (per item, may both be null) tell which keys are older than
+// this step, so that a first chunk of such keys is fetched before the wait on the kernel before.
+PS_EXPORT int ps_paged_attention_decode_ex(const void* q, int q_stride, void* out, int out_stride,
+                                           const void* k_pool, const void* v_pool, long long page_stride,
+                                           const int* token_item, const int* positions, const int* block_table,
+                                           int bt_stride, const int* q_start, const int* kv_len, int T,
+                                           int n_heads, int n_kv_heads, int head_dim, int page_size, int window,
+                                           float scale, int split_tiles, int n_splits, int cluster,
+                                           float* part_acc, float* part_ml, int* counters, int* status,
+                                           void* stream) {
+    return launch_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
+                                   block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window, scale,
+                                   split_tiles, n_splits, part_acc, part_ml, counters, status, stream, q_start, kv_len,
+                                   cluster < 1 ? 1 : cluster);
 }
 
 // ------------------------------------------------------------------------------------------------

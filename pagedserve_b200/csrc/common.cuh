@@ -112,8 +112,8 @@ inline bool pdl_enabled_for(const void* kernel) {
 // Launch with the programmatic-stream-serialization attribute (kept when a stream is captured into a
 // CUDA graph, where it becomes a programmatic dependency edge).
 template <typename... KArgs, typename... Args>
-inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                      Args... args) {
+inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_z, Args... args) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
@@ -123,13 +123,30 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     // 414 us without. (A first form, in which every kernel let its successor launch before its own wait, so
     // that many kernels sat resident at once, was slower than no early launch at all.)
     static const bool enabled = pdl_enabled_for((const void*)kernel);
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attribute[2];
+    int count = 0;
+    if (enabled) {
+        attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    if (cluster_z > 1) {             // thread-block clusters of (1, 1, cluster_z) CTAs
+        attribute[count].id = cudaLaunchAttributeClusterDimension;
+        attribute[count].val.clusterDim.x = 1;
+        attribute[count].val.clusterDim.y = 1;
+        attribute[count].val.clusterDim.z = (unsigned)cluster_z;
+        ++count;
+    }
     config.attrs = attribute;
-    config.numAttrs = enabled ? 1 : 0;
+    config.numAttrs = count;
     cudaError_t e = cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
     return e == cudaSuccess ? PS_OK : PS_ERR_LAUNCH;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      Args... args) {
+    return launch_pdl_cluster(kernel, grid, block, smem, stream, 1, args...);
 }
 
 inline int launch_status() {

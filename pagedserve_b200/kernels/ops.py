@@ -54,6 +54,8 @@ _SIGNATURES = {
                                  _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_paged_attention_decode_checked": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                               _F, _I, _I, _P, _P, _P, _P, _P],
+        "ps_paged_attention_decode_ex": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
+                                         _I, _I, _F, _I, _I, _I, _P, _P, _P, _P, _P],
         "ps_prefill_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     },
     "tc": {
@@ -361,28 +363,59 @@ class Ops:
         n_splits = -(-chunks // split_chunks)
         return split_chunks * chunk // 32, n_splits
 
+    def attention_cluster_plan(self, T, n_heads, head_dim, page_size, max_kv_len, target_ctas=1184, largest=8):
+        """(split_tiles, cluster) if the splits of a (token, head) can be one thread-block cluster of at most
+        ``largest`` CTAs without leaving much of the GPU idle, else None."""
+        chunk = self.attention_chunk_keys(head_dim, page_size)
+        chunks = max(1, -(-int(max_kv_len) // chunk))
+        wanted = min(chunks, max(1, target_ctas // max(1, T * n_heads)))
+        if wanted > largest and chunks > 2 * largest:
+            return None                                  # a long context at a small batch: more splits pay
+        cluster = 1
+        while cluster < min(largest, wanted):
+            cluster *= 2                                 # the power of two at or above the wanted splits ...
+        if cluster > 1 and T * n_heads * cluster > target_ctas:
+            cluster //= 2                                # ... unless that makes more CTAs than are resident at once
+        split_chunks = -(-chunks // cluster)
+        return split_chunks * chunk // 32, cluster
+
     def paged_attention_decode(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
                                n_heads, n_kv_heads, head_dim, page_size, window, scale, max_kv_len,
-                               target_ctas=1184, status=None):
+                               target_ctas=1184, status=None, q_start=None, kv_len=None, merge="global",
+                               largest_cluster=8):
         """Split-key attention for few query tokens (bfloat16).  ``max_kv_len`` bounds the context of
-        every token in the call; it fixes the grid, so a CUDA graph passes the model's maximum."""
+        every token in the call; it fixes the grid, so a CUDA graph passes the model's maximum.
+        ``q_start`` / ``kv_len`` (the step's per-item arrays) let the kernel fetch keys older than this step
+        before the kernel that precedes it has finished.  ``merge``: "global" (the splits of a token and head
+        merge through scratch in global memory) or "cluster" (they are a thread-block cluster and merge
+        through shared memory; falls back to "global" where more than ``largest_cluster`` splits pay)."""
         T = q.shape[0]
         _require(q, "q", torch.bfloat16)
         _require(out, "out", torch.bfloat16)
-        split_tiles, n_splits = self.attention_split_plan(T, n_heads, head_dim, page_size, max_kv_len, target_ctas)
+        plan = None
+        if merge == "cluster":
+            plan = self.attention_cluster_plan(T, n_heads, head_dim, page_size, max_kv_len, target_ctas,
+                                               largest_cluster)
         part_acc = part_ml = counters = None
-        if n_splits > 1:
-            if self._counters is None or self._counters.numel() < T * n_heads:
-                self._counters = torch.zeros(max(1024, T * n_heads), dtype=torch.int32, device=q.device)
-            counters = self._counters
-            part_acc = torch.empty((T * n_heads * n_splits, head_dim), dtype=torch.float32, device=q.device)
-            part_ml = torch.empty((T * n_heads * n_splits, 2), dtype=torch.float32, device=q.device)
+        if plan is not None:
+            split_tiles, cluster = plan
+            n_splits = cluster
+        else:
+            cluster = 1
+            split_tiles, n_splits = self.attention_split_plan(T, n_heads, head_dim, page_size, max_kv_len,
+                                                              target_ctas)
+            if n_splits > 1:
+                if self._counters is None or self._counters.numel() < T * n_heads:
+                    self._counters = torch.zeros(max(1024, T * n_heads), dtype=torch.int32, device=q.device)
+                counters = self._counters
+                part_acc = torch.empty((T * n_heads * n_splits, head_dim), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((T * n_heads * n_splits, 2), dtype=torch.float32, device=q.device)
         self.launches += 1
-        _check(self.fast.ps_paged_attention_decode_checked(
+        _check(self.fast.ps_paged_attention_decode_ex(
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
             page_stride, _ptr(token_item), _ptr(positions), _ptr(block_table),
-            block_table.stride(0), T, n_heads, n_kv_heads, head_dim,
-            page_size, window or 0, scale, split_tiles, n_splits,
+            block_table.stride(0), _ptr(q_start), _ptr(kv_len), T, n_heads, n_kv_heads, head_dim,
+            page_size, window or 0, scale, split_tiles, n_splits, cluster,
             _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(status), _stream()), "paged_attention_decode")
         return out
 

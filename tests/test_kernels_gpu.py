@@ -361,19 +361,63 @@ def test_attention_simt_float32(heads, kv_heads, head_dim, page, window):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (2, 2, 48, 8), (12, 12, 64, 16),
                                                           (8, 2, 128, 32), (2, 1, 256, 64)])
 @pytest.mark.parametrize("window", [None, 70])
-@pytest.mark.parametrize("target_ctas", [1, 1184, 10 ** 7])
-def test_attention_decode_bfloat16(heads, kv_heads, head_dim, page, window, target_ctas):
-    """Contexts around page and chunk edges, fragmented tables, one split up to a split per chunk."""
+@pytest.mark.parametrize("target_ctas,merge", [(1, "global"), (1184, "global"), (10 ** 7, "global"),
+                                               (1184, "cluster"), (10 ** 7, "cluster")])
+def test_attention_decode_bfloat16(heads, kv_heads, head_dim, page, window, target_ctas, merge):
+    """Contexts around page and chunk edges, fragmented tables, one split up to a split per chunk; the splits
+    merged through global memory or inside a thread-block cluster."""
     ops = ops_for(torch.bfloat16)
     lengths = [1, 15, 16, 17, 31, 32, 33, 64, 65, 127, 128, 129, 512, 1024]
     case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=7 + head_dim)
     out = torch.empty(sum(lengths), heads * head_dim, dtype=torch.bfloat16, device=DEV)
     ops.paged_attention_decode(case.q.to(DEV), out, case.k_pool, case.v_pool, case.page_stride, case.token_item,
                                case.positions, case.table, heads, kv_heads, head_dim, page, window,
-                               head_dim ** -0.5, max(lengths), target_ctas=target_ctas)
+                               head_dim ** -0.5, max(lengths), target_ctas=target_ctas, merge=merge)
     assert torch.isfinite(out.float()).all()
     assert rel_err(out, case.reference(window)) < 8e-3
     assert int(ops._counters.abs().sum()) == 0 if ops._counters is not None else True
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (12, 12, 64, 16), (8, 2, 128, 32),
+                                                          (2, 2, 48, 8)])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("target_ctas", [1, 400, 10 ** 7])
+@pytest.mark.parametrize("merge", ["global", "cluster"])
+def test_attention_decode_with_older_keys_fetched_early(heads, kv_heads, head_dim, page, window, target_ctas, merge):
+    """Decode tokens and short portions at the end of long requests: with q_start / kv_len the kernel may
+    fetch a chunk made of older keys only before it waits for the kernel in front of it. The newest keys are
+    written by a kernel launched right before, so a chunk fetched too early would show stale (NaN) rows."""
+    ops = ops_for(torch.bfloat16)
+    lengths = [1, 16, 17, 128, 129, 300, 640, 1024]
+    fresh = [1, 1, 3, 1, 2, 5, 1, 15]
+    case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=11 + head_dim)
+    rows, item_of, q_start = [], [], [0]
+    start = 0
+    for item, (length, new) in enumerate(zip(lengths, fresh)):
+        rows += list(range(start + length - new, start + length))
+        item_of += [item] * new
+        q_start.append(q_start[-1] + new)
+        start += length
+    rows_dev = torch.tensor(rows, device=DEV)
+    q = case.q.to(DEV)[rows_dev].contiguous()
+    token_item = torch.tensor(item_of, dtype=torch.int32, device=DEV)
+    positions = case.positions[rows_dev].contiguous()
+    # poison the new keys, then write them again right before the attention launch
+    k_new, v_new = case.k.to(DEV)[rows_dev].contiguous(), case.v.to(DEV)[rows_dev].contiguous()
+    poison = torch.full_like(k_new, float("nan"))
+    ops.kv_append(poison, poison, token_item, positions, case.table, case.k_pool, case.v_pool, case.page_stride,
+                  kv_heads, head_dim, page)
+    torch.cuda.synchronize()
+    out = torch.empty(len(rows), heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    ops.kv_append(k_new, v_new, token_item, positions, case.table, case.k_pool, case.v_pool, case.page_stride,
+                  kv_heads, head_dim, page)
+    ops.paged_attention_decode(q, out, case.k_pool, case.v_pool, case.page_stride, token_item, positions,
+                               case.table, heads, kv_heads, head_dim, page, window, head_dim ** -0.5, max(lengths),
+                               target_ctas=target_ctas, merge=merge,
+                               q_start=torch.tensor(q_start, dtype=torch.int32, device=DEV),
+                               kv_len=torch.tensor(lengths, dtype=torch.int32, device=DEV))
+    assert torch.isfinite(out.float()).all()
+    assert rel_err(out, case.reference(window)[rows]) < 8e-3
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (2, 2, 48, 8), (12, 12, 64, 16),
