@@ -437,7 +437,7 @@ int pick_warps_fused(const NormInput& in, const void* W, int ldw, const float* b
     // UNROLL: the k steps of a warp whose weights are fetched before anything else
     int steps = (K + 31) / 32;
     if (steps <= 24) return launch_skinny_fused<MT, 8, 3, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
-    if (steps <= 48) return launch_skinny_fused<MT, 8, 6, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    if (steps <= 64) return launch_skinny_fused<MT, 8, 6, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
     return launch_skinny_fused<MT, 16, 6, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
 }
 

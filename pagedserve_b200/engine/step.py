@@ -69,9 +69,9 @@ class ModelRunner:
         self._shape_seen = {}             # step shape -> times seen (a shape is captured when it comes back)
         self.graph_replays = 0
         self._sampled = torch.zeros(cache.max_slots, dtype=torch.int32, device=self.device)
-        self._history = torch.zeros(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32,
-                                    device=self.device)
-        self._history_host = torch.empty(self.MAX_DEVICE_STEPS * cache.max_slots, dtype=torch.int32).pin_memory()
+        # the sampled tokens of a run of decode steps: page-locked host memory that the token feedback kernel
+        # writes directly (no device-to-host copy after the step)
+        self._history = self.ops.mapped_host_buffer(self.MAX_DEVICE_STEPS * cache.max_slots)
         self._shapes = {}                 # (T, I, R) -> (BatchLayout, DeviceViews)
         self._ramp = np.arange(cache.max_slots + 2, dtype=np.int32)
         # the persistent decode kernel, when the model's parts allow it
@@ -94,6 +94,7 @@ class ModelRunner:
         self._staging = [torch.empty(self._capacity, dtype=torch.int32).pin_memory()
                          for _ in range(self.STAGING_BUFFERS)]
         self._staging_numpy = [staging.numpy() for staging in self._staging]
+        self._staging_ptr = [staging.data_ptr() for staging in self._staging]
         self._staging_events = [torch.cuda.Event() for _ in range(self.STAGING_BUFFERS)]
         for event in self._staging_events:
             event.record()
@@ -211,9 +212,12 @@ class ModelRunner:
         self._staging_turn = turn
         return layout, views, self._staging[turn], self._staging_numpy[turn]
 
-    def _upload(self, layout: BatchLayout, staging: torch.Tensor) -> None:
-        self._device_buffer[:layout.total].copy_(staging[:layout.total], non_blocking=True)
-        self._staging_events[self._staging_turn].record()
+    def _upload(self, layout: BatchLayout, staging: torch.Tensor, record: bool = True) -> None:
+        """The step's one host-to-device copy.  ``record=False``: the caller synchronises the stream before
+        it returns, so the staging buffer needs no event of its own."""
+        self.ops.copy_h2d(self._device_buffer, self._staging_ptr[self._staging_turn], layout.total * 4)
+        if record:
+            self._staging_events[self._staging_turn].record()
         self.h2d_bytes = layout.total * 4
 
     def _prepare_single_tokens(self, requests, tokens: np.ndarray, extra_tokens: int, sampling) -> StepContext:
@@ -277,7 +281,7 @@ class ModelRunner:
         host[layout.counter] = 0
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
             cache.table_rows(group_index, slots, host[offset:offset + I * width].reshape(I, width))
-        self._upload(layout, staging)
+        self._upload(layout, staging, record=False)
         host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
                                list(requests))
         return StepContext(layout, self._device_buffer, host_batch, cache, self._status, 1,
@@ -357,8 +361,7 @@ class ModelRunner:
             else:
                 for _ in range(steps):
                     self._forward_and_sample(ctx)
-            self._history_host[:steps * B].copy_(self._history[:steps * B], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            torch.cuda.current_stream().synchronize()          # the tokens are in host memory now
         except Exception:
             for request in requests:
                 self.cache.rollback(request)
@@ -368,7 +371,7 @@ class ModelRunner:
             commit(request)
         self.steps += steps
         self.tokens_run += steps * B
-        return self._history_host[:steps * B].numpy().reshape(steps, B).copy()
+        return self._history.array[:steps * B].reshape(steps, B).copy()
 
     def _stack_takes(self, ctx: StepContext) -> bool:
         return self.decode_stack is not None and ctx.decode_only and ctx.num_items <= self.decode_stack.MAX_BATCH

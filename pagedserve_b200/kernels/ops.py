@@ -12,6 +12,7 @@ from __future__ import annotations
 import ctypes
 from typing import Optional
 
+import numpy as np
 import torch
 
 from pagedserve_b200.kernels.build import load as _load_library
@@ -31,8 +32,39 @@ class KernelError(RuntimeError):
     pass
 
 
-def _ptr(tensor: Optional[torch.Tensor]):
-    return tensor.data_ptr() if tensor is not None else None
+def _ptr(tensor):
+    """Device address of a tensor (or of a :class:`MappedHostBuffer`); None stays a null pointer."""
+    if tensor is None:
+        return None
+    if isinstance(tensor, MappedHostBuffer):
+        return tensor.device_ptr
+    return tensor.data_ptr()
+
+
+class MappedHostBuffer:
+    """Page-locked host memory of ``count`` int32 that kernels write directly (see csrc/host_io.cu);
+    ``array`` is the host's numpy view of it."""
+
+    def __init__(self, lib, count: int):
+        host, device = ctypes.c_void_p(), ctypes.c_void_p()
+        _check(lib.ps_host_alloc_mapped(count * 4, ctypes.byref(host), ctypes.byref(device)), "host_alloc_mapped")
+        self._lib = lib
+        self.host_ptr = host.value
+        self.device_ptr = device.value
+        self.count = count
+        self.array = np.ctypeslib.as_array((ctypes.c_int32 * count).from_address(self.host_ptr))
+
+    def close(self):
+        if self.host_ptr:
+            self.array = None
+            self._lib.ps_host_free(self.host_ptr)
+            self.host_ptr = self.device_ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 # Argument types of the entry points, declared once: ctypes then converts plain Python ints, floats and
@@ -47,6 +79,9 @@ _SIGNATURES = {
         "ps_paged_attention_simt": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
         "ps_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+        "ps_host_alloc_mapped": [_L, _P, _P],
+        "ps_host_free": [_P],
+        "ps_copy_h2d": [_P, _P, _L, _P],
     },
     "bf16": {
         "ps_gemm_skinny": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -246,6 +281,7 @@ class Ops:
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
     FUSED_NORM_ROWS = 32          # most rows for which the norm is folded into the skinny product
+    FUSED_NORM_COLUMNS = 16 * 2 * 148   # and most output columns
 
     def _fused_norm_ok(self, a, w):
         norm = a.norm
@@ -254,7 +290,10 @@ class Ops:
         # the normed rows and the norm's scale and shift are staged in shared memory
         if rows * (a.shape[1] + 8) * 2 + 8 * a.shape[1] > 96 * 1024:
             return False
-        return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS and w.shape[0] <= 8192
+        # one CTA per 16 output columns, two CTAs per SM: beyond one wave of CTAs the repeated norm costs more
+        # than a norm kernel of its own
+        return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS
+                and w.shape[0] <= self.FUSED_NORM_COLUMNS
                 and type(norm).__name__ == "LayerNorm" and a.x.dtype == torch.float32
                 and a.shape[1] % 8 == 0 and a.x.stride(0) % 4 == 0 and a.x.stride(1) == 1
                 and w.stride(0) % 8 == 0 and w.stride(1) == 1 and w.dtype == torch.bfloat16
@@ -498,6 +537,16 @@ class Ops:
                                    _ptr(seed), _ptr(position), pos_offset, _ptr(out), _stream()),
                "sample")
         return out
+
+    def mapped_host_buffer(self, count: int) -> MappedHostBuffer:
+        """``count`` int32 of page-locked host memory that kernels can write (a result the host reads in
+        place after a stream synchronisation, without a copy of its own)."""
+        return MappedHostBuffer(self.core, count)
+
+    def copy_h2d(self, dst: torch.Tensor, src_host_ptr: int, nbytes: int) -> None:
+        """One asynchronous copy of ``nbytes`` from page-locked host memory into ``dst`` on the current
+        stream (the plain runtime call: a fraction of the host time of a tensor ``copy_``)."""
+        _check(self.core.ps_copy_h2d(dst.data_ptr(), src_host_ptr, nbytes, _stream()), "copy_h2d")
 
     def advance(self, sampled, token_ids, positions, kv_len, history, step_counter, max_steps):
         """Feed sampled tokens back as the next inputs of a decode-only batch and move it one position on."""

@@ -1,7 +1,8 @@
 """The bfloat16 paths of the matrix product and of attention.
 
 ``linear``    out = act(a @ w.T + bias) with bfloat16 operands and float32 accumulation:
-              at most 64 rows -> the weight-streaming kernel (csrc/gemm_skinny.cu);
+              at most 64 rows -> the weight-streaming kernel (csrc/gemm_skinny.cu), except 17 to 64
+                                 rows with 4,096 or more output columns;
               more rows       -> the tcgen05 / TMA / TMEM kernel (csrc/gemm_tc.cu);
               shapes neither takes (K not a multiple of 8, unaligned rows) -> the CUDA-core kernel.
 ``attention`` causal attention over the paged cache for bfloat16 queries.
@@ -13,6 +14,12 @@ import torch
 
 
 def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
+    # The weight-streaming kernel re-reads the rows of ``a`` for every 16 output columns: from 17 rows on and
+    # 4,096 columns up (a vocabulary, the wide projections of large models) that traffic costs more than the
+    # half-empty 128-row tiles of the tcgen05 kernel (64 rows x 50,257 x 768: 46 vs 85 us; 64 x 4,800 x 1,600:
+    # 12 vs 37 us; 16 rows: the streaming kernel wins at every shape).
+    if a.shape[0] > 16 and w.shape[0] >= 4096 and ops.tc_ok(a, w):
+        return ops.linear_tc(a, w, bias, out, act, accumulate, status=status)
     if ops.skinny_ok(a, w):
         return ops.linear_skinny(a, w, bias, out, act, accumulate)
     if ops.tc_ok(a, w):
