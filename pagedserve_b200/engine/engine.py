@@ -117,9 +117,10 @@ class Engine:
         return self.runner.decode(entries, temperatures, seeds, steps)
 
     def decode_tokens(self, requests: Sequence[Hashable], tokens: Sequence[int], temperatures, seeds,
-                      steps: int = 1):
-        """``decode`` with the requests and their next tokens as two sequences (no entry objects)."""
-        return self.runner.decode_tokens(requests, tokens, temperatures, seeds, steps)
+                      steps: int = 1, stage_next: bool = False):
+        """``decode`` with the requests and their next tokens as two sequences (no entry objects);
+        ``stage_next`` announces one more step of the same requests."""
+        return self.runner.decode_tokens(requests, tokens, temperatures, seeds, steps, stage_next)
 
     def finish(self, request: Hashable) -> None:
         self.runner.finish(request)

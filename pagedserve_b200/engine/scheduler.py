@@ -205,12 +205,16 @@ class Scheduler:
         try:
             if fused_decode is not None:
                 # every request brings one decoded token: forward and sampling run as one device step
+                # the same batch comes back next step unless a request reaches its limit now (an end-of-
+                # sequence token cannot be foreseen: then what was staged ahead is simply dropped)
+                comes_back = not self.waiting and all(
+                    len(request.generated_token_ids) + 1 < request.max_new_tokens for request in sampling)
                 tokens = fused_decode(
                     [request.request_id for request in sampling],
                     [request.pending_token_id for request in sampling],
                     [request.temperature for request in sampling],
                     [request.seed for request in sampling],
-                    1,
+                    1, comes_back,
                 )[0].tolist()
             else:
                 logits = self.engine.step(entries)

@@ -37,6 +37,17 @@ class _DecodeGraph:
         self.graph.replay()
 
 
+class _StagedStep:
+    """A decode step prepared ahead of its tokens: its pages are taken, its buffer is filled."""
+
+    def __init__(self, requests, temperatures, seeds, ctx, turn):
+        self.requests = requests
+        self.temperatures = temperatures
+        self.seeds = seeds
+        self.ctx = ctx
+        self.turn = turn
+
+
 class ModelRunner:
     """Owns the device metadata buffers and drives ``model.forward`` for one step."""
 
@@ -73,6 +84,7 @@ class ModelRunner:
         # writes directly (no device-to-host copy after the step)
         self._history = self.ops.mapped_host_buffer(self.MAX_DEVICE_STEPS * cache.max_slots)
         self._shapes = {}                 # (T, I, R) -> (BatchLayout, DeviceViews)
+        self._staged = None               # a decode step staged ahead of its tokens
         self._ramp = np.arange(cache.max_slots + 2, dtype=np.int32)
         # the persistent decode kernel, when the model's parts allow it
         self.decode_stack = None
@@ -104,6 +116,7 @@ class ModelRunner:
         """Validate, take pages for the new positions, build and upload the metadata."""
         if not entries:
             raise StepError("a step cannot be empty")                 # reference: iteration.py:50-51
+        self._drop_staged()
         cache = self.cache
         seen = set()
         for entry in entries:
@@ -220,11 +233,12 @@ class ModelRunner:
             self._staging_events[self._staging_turn].record()
         self.h2d_bytes = layout.total * 4
 
-    def _prepare_single_tokens(self, requests, tokens: np.ndarray, extra_tokens: int, sampling) -> StepContext:
+    def _prepare_single_tokens(self, requests, tokens, extra_tokens: int, sampling) -> StepContext:
         """``prepare`` for a step in which every request brings one token and wants its logits: the same
         buffer contents, filled with whole-array operations instead of a loop over entries.  ``extra_tokens``
         more positions per request get pages too (a run of several decode steps on the device);
-        ``sampling`` = (temperatures, seeds) per request is uploaded with the batch."""
+        ``sampling`` = (temperatures, seeds) per request is uploaded with the batch.
+        ``tokens=None`` stages everything but the token ids and uploads nothing (see ``_stage_ahead``)."""
         cache = self.cache
         I = len(requests)
         if I == 0:
@@ -236,10 +250,8 @@ class ModelRunner:
             raise StepError(f"request {missing.args[0]!r} has no prompt in the cache") from None
         if I > 1 and np.unique(slots).size != I:
             raise StepError("a request can appear only once in a step")
-        low, high = int(tokens.min()), int(tokens.max())
-        if low < 0 or high >= self.vocab_size:
-            raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
-                            f"{self.vocab_size}")
+        if tokens is not None:
+            self._check_vocabulary(tokens)
         starts = cache.lengths[slots]
         if int(starts.max()) + 1 + extra_tokens > self.max_model_len:
             raise StepError(f"a request would pass the model's maximum length {self.max_model_len}")
@@ -263,7 +275,8 @@ class ModelRunner:
         kv_len = host[layout.kv_len:layout.kv_len + I]
         logit_rows = host[layout.logit_rows:layout.logit_rows + I]
         ramp = self._ramp[:I + 1]
-        token_ids[:] = tokens
+        if tokens is not None:
+            token_ids[:] = tokens
         positions[:] = starts
         token_item[:] = ramp[:I]
         item_slot[:] = slots
@@ -281,11 +294,35 @@ class ModelRunner:
         host[layout.counter] = 0
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
             cache.table_rows(group_index, slots, host[offset:offset + I * width].reshape(I, width))
-        self._upload(layout, staging, record=False)
+        if tokens is not None:
+            self._upload(layout, staging, record=False)
         host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
                                list(requests))
         return StepContext(layout, self._device_buffer, host_batch, cache, self._status, 1,
                            int(kv_len.max()), I, I, 0, views=views)
+
+    def _check_vocabulary(self, tokens: np.ndarray) -> None:
+        low, high = int(tokens.min()), int(tokens.max())
+        if low < 0 or high >= self.vocab_size:
+            raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
+                            f"{self.vocab_size}")
+
+    # A decode step is followed, most of the time, by a decode step of the same requests.  While the device
+    # runs step n the host therefore stages step n+1 (pages, positions, tables: everything but the token ids,
+    # which step n has yet to produce).  If the next call brings the same requests, only its tokens are
+    # written and the buffer goes up; if anything else is called first, the staged step is undone.
+    def _stage_ahead(self, requests, temperatures, seeds):
+        try:
+            ctx = self._prepare_single_tokens(requests, None, 0, (temperatures, seeds))
+        except (StepError, CacheFull):
+            return None                       # no room or no length left: the real call will say so
+        return _StagedStep(list(requests), list(temperatures), list(seeds), ctx, self._staging_turn)
+
+    def _drop_staged(self) -> None:
+        staged, self._staged = self._staged, None
+        if staged is not None:
+            for request in staged.requests:
+                self.cache.rollback(request)
 
     def _abandon(self, entries) -> None:
         for entry in entries:
@@ -330,7 +367,7 @@ class ModelRunner:
                                   [int(entry.tokens[0]) for entry in entries], temperatures, seeds, steps)
 
     def decode_tokens(self, requests: Sequence[Hashable], tokens: Sequence[int], temperatures, seeds,
-                      steps: int = 1) -> np.ndarray:
+                      steps: int = 1, stage_next: bool = False) -> np.ndarray:
         """Run ``steps`` decode steps of a batch of single tokens without the host in between.
 
         ``tokens[i]`` is the one next token of ``requests[i]``, whose earlier tokens are in the cache.
@@ -338,6 +375,8 @@ class ModelRunner:
         input and moves the request one position on.  Returns the sampled tokens ``[steps, B]``.
         The step is replayed as a CUDA graph (reference: decode-only fast path with CUDA graphs,
         src/model/paged_decoder.py:385-496) unless graphs are disabled.
+        ``stage_next``: the caller expects to come back with the same requests for one more step; the host
+        side of that step is prepared while the device runs this one.
         """
         tokens = np.asarray(tokens)
         if tokens.ndim != 1 or tokens.size != len(requests) or tokens.size == 0:
@@ -346,7 +385,19 @@ class ModelRunner:
             raise StepError("token ids must be integers")
         if not (1 <= steps <= self.MAX_DEVICE_STEPS):
             raise StepError(f"steps must be between 1 and {self.MAX_DEVICE_STEPS}")
-        ctx = self._prepare_single_tokens(requests, tokens, steps - 1, (temperatures, seeds))
+        staged, self._staged = self._staged, None
+        if (staged is not None and steps == 1 and staged.requests == list(requests)
+                and staged.temperatures == list(temperatures) and staged.seeds == list(seeds)):
+            self._check_vocabulary(tokens)
+            ctx = staged.ctx
+            ctx.host.token_ids[:] = tokens
+            self._staging_turn = staged.turn
+            self._upload(ctx.layout, self._staging[staged.turn], record=False)
+        else:
+            if staged is not None:
+                self._staged = staged
+                self._drop_staged()
+            ctx = self._prepare_single_tokens(requests, tokens, steps - 1, (temperatures, seeds))
         B = ctx.num_items
         try:
             if self._stack_takes(ctx):
@@ -361,16 +412,19 @@ class ModelRunner:
             else:
                 for _ in range(steps):
                     self._forward_and_sample(ctx)
-            torch.cuda.current_stream().synchronize()          # the tokens are in host memory now
         except Exception:
             for request in requests:
                 self.cache.rollback(request)
             raise
+        # the step is on its way: what follows runs on the host while the device works
         commit = self.cache.commit
         for request in requests:
             commit(request)
         self.steps += steps
         self.tokens_run += steps * B
+        if stage_next and steps == 1:
+            self._staged = self._stage_ahead(requests, temperatures, seeds)
+        torch.cuda.current_stream().synchronize()          # the tokens are in host memory now
         return self._history.array[:steps * B].reshape(steps, B).copy()
 
     def _stack_takes(self, ctx: StepContext) -> bool:
@@ -447,6 +501,7 @@ class ModelRunner:
 
     def finish(self, request: Hashable) -> None:
         """The request is done: its pages and its slot are given back."""
+        self._drop_staged()
         self.cache.free(request)
 
     def check_status(self) -> None:

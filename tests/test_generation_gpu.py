@@ -174,3 +174,52 @@ def test_graph_replay_equals_eager_and_device_loop_equals_stepwise(dtype):
             scores = plain_gpt2.temperature_scores(logits, 0.9, 42, len(sequence))
             assert scores[drawn] >= scores.max() - 1e-4
             sequence.append(drawn)
+
+
+def test_a_step_staged_ahead_is_used_or_undone():
+    """While a decode step runs, the host stages the next one of the same requests.  The staged step must be
+    used when the batch comes back, and undone (its pages returned) when a request ends on an end-of-sequence
+    token, when another request joins, and when something else is called in between."""
+    from pagedserve_b200.engine.batch import StepEntry
+
+    config, weights = helpers.plain_model("a")
+    vocab = helpers.TINY["a"][0]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=40 + n) for n in (14, 15, 16, 30)]
+    want = [plain_gpt2.generate(config, weights, prompt, 12) for prompt in prompts]
+    # request 1 ends early on its 4th token; request 3 joins after two decode steps
+    eos = want[1][3]
+    for i in range(4):
+        if eos in want[i]:
+            want[i] = want[i][:want[i].index(eos) + 1]
+    engine = make_engine("a", "float32")
+    scheduler = engine.make_scheduler(strategy="orca", max_num_seqs=4, eos_token_id=eos)
+    ids = [scheduler.add_token_request(prompt, max_new_tokens=12) for prompt in prompts[:3]]
+    staged_seen = 0
+    for step in range(64):
+        if step == 3:
+            ids.append(scheduler.add_token_request(prompts[3], max_new_tokens=12))
+        if not (scheduler.waiting or scheduler.active):
+            break
+        scheduler.step()
+        staged_seen += engine.runner._staged is not None
+        engine.cache.check_invariants()
+    assert staged_seen > 0                                   # the path under test was taken
+    got = [scheduler.finished[i].generated_token_ids for i in ids]
+    assert got == want
+    assert engine.runner._staged is None
+    assert engine.cache.live_requests == 0 and engine.cache.free_pages() == engine.cache.total_pages()
+
+    # a staged step is undone when a different call comes in between
+    engine = make_engine("a", "float32")
+    first = engine.step([StepEntry(i, p, [len(p) - 1]) for i, p in enumerate(prompts[:2])])
+    tokens = [int(t) for t in first.argmax(-1).tolist()]
+    free_before = engine.cache.free_pages()
+    out = engine.decode_tokens([0, 1], tokens, [0.0, 0.0], [0, 0], 1, stage_next=True)
+    assert engine.runner._staged is not None
+    logits = engine.step([StepEntry(0, [int(out[0, 0])], [0])])          # not the staged batch
+    assert engine.runner._staged is None
+    assert int(logits.argmax(-1).item()) == want[0][2] or eos in want[0][:2]
+    engine.finish(0)
+    engine.finish(1)
+    assert engine.cache.free_pages() == engine.cache.total_pages() >= free_before
+    engine.cache.check_invariants()
