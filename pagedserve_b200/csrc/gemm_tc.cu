@@ -152,7 +152,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    pdl_prologue();
+    // Set-up (barriers, tensor memory) and the first weight tiles do not depend on the kernel before this one:
+    // they happen before the wait and overlap its end.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
     const int num_tiles = tiles_m * tiles_n;
@@ -177,21 +178,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
+            // the weight tiles of the first stages (of this CTA's first tile) go out before the wait
+            const uint32_t early = ((int)blockIdx.x < num_tiles) ? (uint32_t)min(STAGES, num_kb) : 0u;
+            for (uint32_t kb = 0; kb < early; ++kb) {
+                const int n0 = ((int)blockIdx.x % tiles_n) * BN;
+                mbar_expect_tx(&full[kb], Cfg::STAGE_BYTES);
+                tma_load_2d(tiles + (size_t)kb * Cfg::STAGE_BYTES + BM * BK * 2, &map_w, (int)kb * BK, n0, &full[kb]);
+            }
+            pdl_prologue();
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; atomicExch(status, 11); break; }
                     unsigned char* a_dst = tiles + (size_t)s * Cfg::STAGE_BYTES;
-                    mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                    if (it >= early) {
+                        if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; atomicExch(status, 11); break; }
+                        mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                        tma_load_2d(a_dst + BM * BK * 2, &map_w, kb * BK, n0, &full[s]);
+                    }
                     tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
-                    tma_load_2d(a_dst + BM * BK * 2, &map_w, kb * BK, n0, &full[s]);
                 }
             }
+        } else {
+            pdl_prologue();
         }
     } else if (warp == 1) {
+        pdl_prologue();
         // ------------------------------------------------ MMA issuer
         if (lane == 0) {
             // instruction descriptor: D = f32, A = B = bf16, both K-major, N = BN, M = 128
@@ -220,6 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         // ------------------------------------------------ epilogue: warps 2..9
+        pdl_prologue();
         const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31
         const int team = (warp - 2) >> 2;                   // which column groups this warp takes
         uint32_t local = 0;
