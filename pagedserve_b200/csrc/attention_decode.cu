@@ -131,9 +131,11 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               int* __restrict__ counters, int* __restrict__ status,
                               const int* __restrict__ q_start, const int* __restrict__ kv_len, int cluster) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    // page_size, chunk_keys and the unit are powers of two: shifts and masks instead of divisions
     const int unit = min(page_size, chunk_keys >> 3);                                // keys per copy
-    const int n_units = chunk_keys / unit;                                           // a power of two >= 8
-    const int units_log2 = 31 - __clz(n_units);
+    const int unit_log2 = 31 - __clz(unit), page_log2 = 31 - __clz(page_size), chunk_log2 = 31 - __clz(chunk_keys);
+    const int n_units = chunk_keys >> unit_log2;                                     // a power of two >= 8
+    const int units_log2 = chunk_log2 - unit_log2;
     const int unit_elems = attention_unit_stride(unit, head_dim);                    // padded unit, elements
     // One stage of chunk buffers: measured on B200, a second stage (copying the next chunk during the
     // compute of this one) halves the CTAs per SM and was slower at every batch size (batch 64: 44 vs 36 us).
@@ -154,7 +156,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int item = token_item[t];
     const int first_new = (q_start && kv_len) ? kv_len[item] - (q_start[item + 1] - q_start[item]) : 0;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
+    const int first_chunk = lo >> chunk_log2, last_chunk = p >> chunk_log2;
     const int first_split = first_chunk / split_chunks, last_split = last_chunk / split_chunks;
     const int n_active = last_split - first_split + 1;
     const bool active = split >= first_split && split <= last_split;
@@ -171,28 +173,35 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    // copies of one chunk: thread u brings unit u (K and V) if it holds keys of [lo, p]
-    auto issue_chunk = [&](int chunk) {
-        const int key0 = chunk * chunk_keys;
+    // Copies of one chunk: thread u brings unit u (K and V) if it holds keys of [lo, p]. `part` selects the
+    // units made only of keys older than this step (0: fetched before the wait), the others (1: after it),
+    // or all (2). The chunk's barrier expects the bytes of all its units once.
+    auto issue_chunk = [&](int chunk, int part) {
+        const int key0 = chunk << chunk_log2;
         const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;
-        const int u_lo = j_lo / unit, u_hi = j_hi / unit;
-        if (tid == 0) mbar_expect_tx(&bar, 2u * unit_bytes * (uint32_t)(u_hi - u_lo + 1));
+        const int u_lo = j_lo >> unit_log2, u_hi = j_hi >> unit_log2;
+        if (tid == 0 && part != 1) mbar_expect_tx(&bar, 2u * unit_bytes * (uint32_t)(u_hi - u_lo + 1));
         if (tid >= u_lo && tid <= u_hi) {
-            const int key = key0 + tid * unit;
-            const int page = bt[key / page_size];
-            const long long src = (long long)page * page_stride +
-                                  ((long long)g * page_size + (key % page_size)) * head_dim;
-            bulk_copy_g2s(k_s + (size_t)tid * unit_elems, k_pool + src, unit_bytes, &bar);
-            bulk_copy_g2s(v_s + (size_t)tid * unit_elems, v_pool + src, unit_bytes, &bar);
+            const int key = key0 + (tid << unit_log2);
+            const bool old = key + unit <= first_new;
+            if (part == 2 || (part == 0) == old) {
+                const int page = bt[key >> page_log2];
+                const long long src = (long long)page * page_stride +
+                                      ((long long)g * page_size + (key & (page_size - 1))) * head_dim;
+                bulk_copy_g2s(k_s + (size_t)tid * unit_elems, k_pool + src, unit_bytes, &bar);
+                bulk_copy_g2s(v_s + (size_t)tid * unit_elems, v_pool + src, unit_bytes, &bar);
+            }
         }
     };
-    const bool prefetched = active && (chunk_lo + 1) * chunk_keys <= first_new;
-    if (prefetched) issue_chunk(chunk_lo);
+    // the first chunk's older units go out now, the rest of it after the wait
+    const bool early = active && (chunk_lo << chunk_log2) < first_new;
+    if (early) issue_chunk(chunk_lo, 0);
 
     pdl_prologue();
     q = pdl_fresh(q);
     k_pool = pdl_fresh(k_pool);
     v_pool = pdl_fresh(v_pool);
+    if (active) issue_chunk(chunk_lo, early ? 1 : 2);
 
     // the query as B fragments: lanes with g == 0 hold q[16 ks + 2 t .. +1] and q[16 ks + 2 t + 8 .. +9]
     const int ksteps = head_dim >> 4;                              // <= KS
@@ -220,14 +229,14 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // MMA row m of a chunk is key (m % n_units) * unit + m / n_units and lies at element
     // (m % n_units) * unit_elems + (m / n_units) * head_dim of the chunk buffers
     auto row_elem = [&](int m) { return (size_t)(m & unit_mask) * unit_elems + (size_t)(m >> units_log2) * head_dim; };
-    auto row_key = [&](int m) { return (m & unit_mask) * unit + (m >> units_log2); };
+    auto row_key = [&](int m) { return ((m & unit_mask) << unit_log2) + (m >> units_log2); };
     uint32_t phase = 0;
     bool ok = true;
 
     for (int chunk = chunk_lo; chunk <= chunk_hi; ++chunk) {
-        const int key0 = chunk * chunk_keys;
+        const int key0 = chunk << chunk_log2;
         const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;   // valid keys of the chunk
-        if (!(prefetched && chunk == chunk_lo)) issue_chunk(chunk);
+        if (chunk != chunk_lo) issue_chunk(chunk, 2);
         if (ok && !mbar_wait_bounded(&bar, phase)) {
             ok = false;
             if (status) atomicExch(status, 2);
@@ -368,31 +377,62 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __syncthreads();
     if (!last_flag) return;
     __threadfence();
-    const size_t base = ((size_t)t * n_heads + h) * n_splits;
-    // all (max, sum) pairs at once into shared memory (one trip to L2, not one per split)
-    float* ml_s = reinterpret_cast<float*>(k_s);              // the K buffer is free now
-    const bool staged = 2 * n_active <= chunk_keys;
+    const size_t base = ((size_t)t * n_heads + h) * n_splits + first_split;
+    // the partial accumulators are asked for first (they do not depend on the maxima), then the (max, sum)
+    // pairs; the weight of each split is computed once and shared
+    constexpr int HOLD = 8;                                   // splits whose values a thread keeps in flight
+    const int d0 = tid;                                       // head dims d0, d0 + 128, ... belong to this thread
+    float held[HOLD];
+    if (d0 < head_dim) {
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i)
+            held[i] = i < n_active ? ldcg_f32(part_acc + (base + i) * head_dim + d0) : 0.f;
+    }
+    float* w_s = reinterpret_cast<float*>(k_s);               // the K buffer is free now: [n_active] weights
+    float* ml_s = w_s + n_active;                             // then [n_active][2]
+    const bool staged = 3 * n_active * 4 <= 2 * chunk_keys * head_dim;      // always, unless a huge split count
     if (staged) {
-        if (tid < 2 * n_active) ml_s[tid] = ldcg_f32(part_ml + (base + first_split) * 2 + tid);
+        for (int i = tid; i < 2 * n_active; i += DEC_THREADS) ml_s[i] = ldcg_f32(part_ml + base * 2 + i);
         __syncthreads();
+        if (warp == 0) {
+            float M = -INFINITY;
+            for (int i = lane; i < n_active; i += 32) M = fmaxf(M, ml_s[2 * i]);
+            M = warp_max(M);
+            float L = 0.f;
+            for (int i = lane; i < n_active; i += 32) {
+                const float w = exp2f(ml_s[2 * i] - M);
+                w_s[i] = w;
+                L += ml_s[2 * i + 1] * w;
+            }
+            L = warp_sum(L);
+            if (lane == 0) red_a[0] = L > 0.f ? 1.f / L : 0.f;
+        }
+        __syncthreads();
+        const float inv = red_a[0];
+        for (int d = d0, round = 0; d < head_dim; d += DEC_THREADS, ++round) {
+            float o = 0.f;
+            if (round == 0) {
+#pragma unroll
+                for (int i = 0; i < HOLD; ++i)
+                    if (i < n_active) o += held[i] * w_s[i];
+                for (int i = HOLD; i < n_active; ++i) o += ldcg_f32(part_acc + (base + i) * head_dim + d) * w_s[i];
+            } else {
+                for (int i = 0; i < n_active; ++i) o += ldcg_f32(part_acc + (base + i) * head_dim + d) * w_s[i];
+            }
+            out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
+        }
+        return;
     }
     float M = -INFINITY;
-    for (int i = 0; i < n_active; ++i)
-        M = fmaxf(M, staged ? ml_s[2 * i] : ldcg_f32(part_ml + (base + first_split + i) * 2));
+    for (int i = 0; i < n_active; ++i) M = fmaxf(M, ldcg_f32(part_ml + (base + i) * 2));
     float L = 0.f;
-    for (int i = 0; i < n_active; ++i) {
-        const float mi = staged ? ml_s[2 * i] : ldcg_f32(part_ml + (base + first_split + i) * 2);
-        const float li = staged ? ml_s[2 * i + 1] : ldcg_f32(part_ml + (base + first_split + i) * 2 + 1);
-        L += li * exp2f(mi - M);
-    }
+    for (int i = 0; i < n_active; ++i)
+        L += ldcg_f32(part_ml + (base + i) * 2 + 1) * exp2f(ldcg_f32(part_ml + (base + i) * 2) - M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int d = tid; d < head_dim; d += DEC_THREADS) {
         float o = 0.f;
-#pragma unroll 4
-        for (int i = 0; i < n_active; ++i) {
-            const float mi = staged ? ml_s[2 * i] : ldcg_f32(part_ml + (base + first_split + i) * 2);
-            o += ldcg_f32(part_acc + (base + first_split + i) * head_dim + d) * exp2f(mi - M);
-        }
+        for (int i = 0; i < n_active; ++i)
+            o += ldcg_f32(part_acc + (base + i) * head_dim + d) * exp2f(ldcg_f32(part_ml + (base + i) * 2) - M);
         out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
     }
 }
