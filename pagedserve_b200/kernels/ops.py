@@ -96,7 +96,7 @@ _SIGNATURES = {
     "tc": {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
         "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
-                                    _I, _F, _P, _P],
+                                    _I, _F, _I, _P, _P],
     },
 }
 
@@ -483,10 +483,11 @@ class Ops:
 
     def prefill_attention_tc(self, q, out, pool, cache_layer_local, q_start, kv_len, block_table, first_item,
                              n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                             status=None):
+                             status=None, row_threads=0):
         """tcgen05 causal attention of prompt portions (bfloat16, head size 64 or 128).  ``pool`` is the cache
         group's whole pool ``[pages, layers, 2, kv heads, page size, head dim]``; ``cache_layer_local`` the
-        layer's index inside it; ``max_blocks`` >= the number of 128-query blocks of the items."""
+        layer's index inside it; ``max_blocks`` >= the number of 128-query blocks of the items.
+        ``row_threads``: 1 or 2 threads per query row (0: the kernel's launcher decides)."""
         _require(q, "q", torch.bfloat16)
         _require(out, "out", torch.bfloat16)
         if self._tc is None:
@@ -503,7 +504,7 @@ class Ops:
             _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(pool), pages * page_rows,
             (cache_layer_local * 2) * rows_per_tensor, (cache_layer_local * 2 + 1) * rows_per_tensor, page_rows,
             _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), first_item, n_items, max_blocks,
-            n_heads, n_kv_heads, head_dim, page_size, window or 0, scale, _ptr(status), _stream()),
+            n_heads, n_kv_heads, head_dim, page_size, window or 0, scale, row_threads, _ptr(status), _stream()),
             "prefill_attention_tc")
         return out
 

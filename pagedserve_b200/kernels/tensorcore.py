@@ -47,9 +47,14 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
     if long_items:
         if ops.prefill_tc_ok(head_dim, layer.page_size, q, out, getattr(layer, "pool", None)):
             # blocks of 128 queries: never more than the count of 64-query blocks
+            # Two threads per query row halve the chain of each 128-key tile but leave one CTA per SM: worth it
+            # when all blocks are resident at once, or nearly so while some block runs over many tiles.
+            blocks = -(-ctx.num_long_blocks // 2) * n_heads          # an upper bound of the 128-query blocks
+            two = blocks <= 148 or (blocks <= 296 and ctx.max_kv_len >= 768)
             ops.prefill_attention_tc(q, out, layer.pool, layer.pool_layer, ctx.q_start, ctx.kv_len, layer.block_table,
                                      ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads, n_kv_heads,
-                                     head_dim, layer.page_size, window, scale, status=ctx.status)
+                                     head_dim, layer.page_size, window, scale, status=ctx.status,
+                                     row_threads=2 if two else 1)
         else:
             ops.prefill_attention(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.q_start, ctx.kv_len,
                                   layer.block_table, ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads,

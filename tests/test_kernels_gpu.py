@@ -459,10 +459,12 @@ def test_prefill_attention_bfloat16(heads, kv_heads, head_dim, page, window):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(12, 12, 64, 16), (8, 2, 128, 32), (3, 1, 64, 8),
                                                           (2, 2, 128, 64)])
 @pytest.mark.parametrize("window", [None, 70])
-def test_prefill_attention_tcgen05(heads, kv_heads, head_dim, page, window):
+@pytest.mark.parametrize("row_threads", [1, 2])
+def test_prefill_attention_tcgen05(heads, kv_heads, head_dim, page, window, row_threads):
     """The tcgen05 kernel (S, P and O_j in TMEM) on whole prompts and on portions that continue a cached
     prompt, lengths around the 128-row and 128-key block edges, fragmented tables, a poisoned pool (NaN in
-    every slot that was never written), items before ``first_item`` left alone."""
+    every slot that was never written), items before ``first_item`` left alone; one thread per query row and
+    two (which exchange the row's maximum and sum through shared memory)."""
     ops = ops_for(torch.bfloat16)
     lengths = [40, 16, 127, 128, 129, 255, 256, 257, 300, 1000]
     case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=5 + head_dim)
@@ -484,7 +486,7 @@ def test_prefill_attention_tcgen05(heads, kv_heads, head_dim, page, window):
     ops.prefill_attention_tc(q, out, case.pool, 0, torch.tensor(q_start, dtype=torch.int32, device=DEV),
                              torch.tensor(kv_len, dtype=torch.int32, device=DEV), case.table, first_item,
                              len(lengths) - first_item, blocks + 2, heads, kv_heads, head_dim, page, window,
-                             head_dim ** -0.5, status=status)
+                             head_dim ** -0.5, status=status, row_threads=row_threads)
     assert int(status.item()) == 0
     assert torch.isnan(out[:portions[0]].float()).all()        # untouched
     got = out[portions[0]:]
