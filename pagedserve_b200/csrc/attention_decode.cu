@@ -95,19 +95,6 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // ldmatrix then come from 8 different units and fall on 8 different bank groups, although each unit is a
 // plain contiguous copy. Keys outside [lo, p] have their V rows zeroed and their scores masked.
 // KS: head-dim steps of 16 the kernel is compiled for (head_dim <= 16 * KS); fewer steps, fewer registers.
-// Thread-block clusters: the CTAs of one (token, head) form a cluster along the split axis and the first
-// of them merges the partial states out of the others' shared memory.
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
-
 // How the partial states of the splits of one (token, head) are merged:
 //   n_splits == 1            nothing to merge;
 //   cluster == n_splits > 1  the splits are one thread-block cluster; the first active CTA reads the others'

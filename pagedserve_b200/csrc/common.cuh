@@ -62,6 +62,21 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Thread-block clusters: CTAs of a cluster read each other's shared memory after a cluster barrier.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(const void* local, int rank) {
+    uint32_t remote, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
+    return __uint_as_float(ld_cluster_u32(local, rank));
+}
+
 // Programmatic dependent launch (on unless PAGEDSERVE_B200_PDL=0). A kernel calls pdl_wait() before it
 // touches memory that an earlier kernel wrote: it returns when all earlier kernels have completed and their
 // writes are visible. What a kernel does before pdl_wait() (reading weights, which no kernel writes) overlaps

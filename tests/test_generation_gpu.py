@@ -110,6 +110,19 @@ def test_sampler_kernel_alone():
         else:
             scores = plain_gpt2.temperature_scores(logits[r], temperatures[r], seeds[r], positions[r])
             assert scores[got[r]] >= scores.max() - 1e-4
+    # a wide vocabulary (a row shared out over a cluster of CTAs), not a multiple of anything, ties across shares
+    wide = torch.randn(5, 50257, generator=generator)
+    wide[1, 40000] = wide[1, 7] = 11.0
+    wide[3, 50256] = 12.0
+    device_wide = wide.cuda()
+    temperatures, seeds, positions = [0.0, 0.0, 0.9, 0.0, 1.7], [3, 4, 5, 6, 7], [1, 2, 3, 4, 1000]
+    got = sampler.sample(device_wide, temperatures, seeds, positions)
+    for r in range(5):
+        if temperatures[r] == 0:
+            assert got[r] == (7 if r == 1 else 50256 if r == 3 else int(torch.argmax(wide[r])))
+        else:
+            scores = plain_gpt2.temperature_scores(wide[r], temperatures[r], seeds[r], positions[r])
+            assert scores[got[r]] >= scores.max() - 1e-4
     # the draw is a sample of softmax(logits / T): empirical frequencies over many positions
     row = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).cuda().repeat(4000, 1)
     draws = sampler.sample(row, [1.0] * 4000, [9] * 4000, list(range(4000)))
