@@ -19,7 +19,14 @@ TINY_A = dict(n_layer=2, n_embd=64, n_head=4, n_inner=256, vocab_size=512, n_pos
               layer_norm_epsilon=1e-5, activation_function="gelu_new")
 TINY_B = dict(n_layer=3, n_embd=96, n_head=2, n_inner=320, vocab_size=1000, n_positions=256,
               layer_norm_epsilon=1e-6, activation_function="gelu")
-TINY = {"a": (TINY_A, 0, 16), "b": (TINY_B, 1, 8)}     # config, seed, block size
+# Two more with the head sizes of the tcgen05 attention kernel (64, 128), widths that are no multiple of 64 or
+# 128 and prompts of several 128-key tiles: they are not "tiny configurations of record", they take the
+# engine through the kernels that A and B (head sizes 16 and 48) never reach.
+TINY_C = dict(n_layer=2, n_embd=192, n_head=3, n_inner=520, vocab_size=777, n_positions=384,
+              layer_norm_epsilon=1e-5, activation_function="gelu_new")
+TINY_D = dict(n_layer=2, n_embd=256, n_head=2, n_inner=264, vocab_size=1031, n_positions=320,
+              layer_norm_epsilon=1e-6, activation_function="gelu")
+TINY = {"a": (TINY_A, 0, 16), "b": (TINY_B, 1, 8), "c": (TINY_C, 2, 16), "d": (TINY_D, 3, 32)}     # config, seed, block size
 
 _FOLDERS = {}
 

@@ -7,7 +7,8 @@ import helpers
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"a": [5, 17, 33, 64, 100, 128], "b": [1, 9, 40, 64, 100, 200]}
+LENGTHS = {"a": [5, 17, 33, 64, 100, 128], "b": [1, 9, 40, 64, 100, 200], "c": [3, 70, 129, 260, 384],
+           "d": [2, 127, 128, 257, 300]}
 
 
 def sequences(which):
@@ -17,7 +18,7 @@ def sequences(which):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["a", "b"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "d"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 def test_replay_matches_plain(which, dtype, mode):
     seqs = sequences(which)
