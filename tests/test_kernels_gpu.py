@@ -105,7 +105,8 @@ def test_gemm_simt_float32(M, N, K, act):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 40, 64])
-@pytest.mark.parametrize("N,K", [(48, 64), (1003, 96), (300, 320), (2304, 768), (770, 3072), (33, 4104)])
+@pytest.mark.parametrize("N,K", [(48, 64), (1003, 96), (300, 320), (2304, 768), (770, 3072), (33, 4104),
+                                 (160, 6400), (768, 768)])
 def test_gemm_skinny(M, N, K):
     ops = ops_for(torch.bfloat16)
     g = torch.Generator().manual_seed(M + N + K)
