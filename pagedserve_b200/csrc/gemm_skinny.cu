@@ -30,14 +30,14 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
-// MT: token tiles of 8. WARPS: warps per CTA. UNROLL: k steps whose loads are issued together.
-template <int MT, int WARPS, typename TOut>
+// MT: token tiles of 8. WARPS: warps per CTA. UNROLL: k steps whose loads a warp issues together (a round);
+// WARPS * UNROLL * 32 >= K makes it one round, so that the latency of the weights is paid once.
+template <int MT, int WARPS, int UNROLL, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, int ldw,
                    const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K,
                    int act, int accumulate) {
     extern __shared__ float red[];                 // [WARPS][16][8*MT]
-    constexpr int UNROLL = 6;                      // K = 3072 over 16 warps is one round of loads
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -133,11 +133,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     }
 }
 
-template <int MT, int WARPS, typename TOut>
+template <int MT, int WARPS, int UNROLL, typename TOut>
 int launch_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo,
                   int M, int N, int K, int act, int accumulate, cudaStream_t s) {
     size_t smem = (size_t)WARPS * 16 * 8 * MT * sizeof(float);
-    auto kernel = gemm_skinny_kernel<MT, WARPS, TOut>;
+    auto kernel = gemm_skinny_kernel<MT, WARPS, UNROLL, TOut>;
     if (smem > 48 * 1024) {
         static bool raised = false;
         if (!raised) {
@@ -153,12 +153,23 @@ int launch_skinny(const void* A, int lda, const void* W, int ldw, const float* b
 template <int MT, typename TOut>
 int pick_warps(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
                int N, int K, int act, int accumulate, cudaStream_t s) {
-    int steps = (K + 31) / 32;
-    if (steps <= 32)
-        return launch_skinny<MT, 4, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
-    if (steps <= 64)
-        return launch_skinny<MT, 8, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
-    return launch_skinny<MT, 16, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
+    // warps and steps per round such that the k steps of a warp are one round of loads where that is possible
+    // (K up to 4,096, at most 8 rows); more token tiles keep the rounds short, their accumulators need the
+    // registers
+    const int steps = (K + 31) / 32;
+#define PS_SKINNY(W_, U_) \
+    return launch_skinny<MT, W_, U_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s)
+    if (MT >= 2) {
+        if (steps <= 32) PS_SKINNY(4, 6);
+        if (steps <= 64) PS_SKINNY(8, 6);
+        PS_SKINNY(16, 6);
+    }
+    if (steps <= 24) PS_SKINNY(4, 6);
+    if (steps <= 32) PS_SKINNY(8, 4);
+    if (steps <= 64) PS_SKINNY(8, 8);
+    if (steps <= 96) PS_SKINNY(16, 6);
+    PS_SKINNY(16, 8);
+#undef PS_SKINNY
 }
 
 template <typename TOut>
