@@ -12,7 +12,7 @@ simply an entry of one token.  The device side is one packed int32 buffer
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Hashable, List, Sequence
 
 import numpy as np
 import torch

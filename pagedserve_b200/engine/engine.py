@@ -14,7 +14,6 @@ import torch
 from pagedserve_b200.cache.manager import CacheManager
 from pagedserve_b200.config.engine_config import EngineConfig
 from pagedserve_b200.config.registry import ModelConfig, load_config_dict, resolve_architecture
-from pagedserve_b200.engine.batch import StepEntry
 from pagedserve_b200.engine.step import ModelRunner
 from pagedserve_b200.kernels.ops import Ops
 from pagedserve_b200.models.model import Model

@@ -24,7 +24,6 @@ import json
 import os
 import sys
 
-import numpy as np
 
 
 def build_parser() -> argparse.ArgumentParser:

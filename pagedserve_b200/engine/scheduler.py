@@ -32,7 +32,6 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 from pagedserve_b200.config.engine_config import (
     ORCA_STRATEGY,
-    SARATHI_STRATEGY,
     SUPPORTED_SCHEDULING_STRATEGIES,
 )
 from pagedserve_b200.engine.batch import StepEntry

@@ -12,8 +12,6 @@ from __future__ import annotations
 
 from typing import Hashable, List, Sequence
 
-import os
-
 import numpy as np
 import torch
 
@@ -86,14 +84,6 @@ class ModelRunner:
         self._shapes = {}                 # (T, I, R) -> (BatchLayout, DeviceViews)
         self._staged = None               # a decode step staged ahead of its tokens
         self._ramp = np.arange(cache.max_slots + 2, dtype=np.int32)
-        # the persistent decode kernel, when the model's parts allow it
-        self.decode_stack = None
-        # (opt-in: measured on B200 its ~62 grid barriers per step cost as much as the launch gaps they
-        # replace, and the graph of separate kernels is currently faster)
-        if enable_cuda_graphs and os.environ.get("PAGEDSERVE_B200_DECODE_STACK") is not None:
-            from pagedserve_b200.kernels.decode_stack import DecodeStack
-
-            self.decode_stack = DecodeStack.build_if_possible(model, cache, self.device)
 
     def _grow(self, needed: int) -> None:
         if needed <= self._capacity:
@@ -336,9 +326,7 @@ class ModelRunner:
         ctx = self.prepare(entries)
         decode_only = ctx.decode_only and all(entry.want == [0] for entry in entries)
         try:
-            if decode_only and self._stack_takes(ctx):
-                logits = self.decode_stack.run(ctx, 1, True, False, max_kv_len=ctx.max_kv_len)
-            elif decode_only and self.enable_cuda_graphs:
+            if decode_only and self.enable_cuda_graphs:
                 logits = self._run_decode_graph(ctx, "logits").logits.clone()
             elif self.enable_cuda_graphs:
                 logits = self._run_mixed_step(ctx)
@@ -400,11 +388,7 @@ class ModelRunner:
             ctx = self._prepare_single_tokens(requests, tokens, steps - 1, (temperatures, seeds))
         B = ctx.num_items
         try:
-            if self._stack_takes(ctx):
-                self.decode_stack.run(ctx, steps, False, True, sampled=self._sampled, history=self._history,
-                                      step_counter=ctx.step_counter, max_steps=self.MAX_DEVICE_STEPS,
-                                      max_kv_len=ctx.max_kv_len + steps - 1)
-            elif self.enable_cuda_graphs:
+            if self.enable_cuda_graphs:
                 graph = self._run_decode_graph(ctx, "sample")
                 for _ in range(steps - 1):
                     graph.replay()
@@ -426,9 +410,6 @@ class ModelRunner:
             self._staged = self._stage_ahead(requests, temperatures, seeds)
         torch.cuda.current_stream().synchronize()          # the tokens are in host memory now
         return self._history.array[:steps * B].reshape(steps, B).copy()
-
-    def _stack_takes(self, ctx: StepContext) -> bool:
-        return self.decode_stack is not None and ctx.decode_only and ctx.num_items <= self.decode_stack.MAX_BATCH
 
     def _forward_and_sample(self, ctx: StepContext) -> torch.Tensor:
         logits = self.model.forward(ctx)

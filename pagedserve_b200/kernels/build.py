@@ -35,7 +35,6 @@ LIBRARIES: Dict[str, List[str]] = {
     "core": ["embed_norm.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu", "host_io.cu"],
     "bf16": ["gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu"],
     "tc": ["gemm_tc.cu", "attention_prefill_tc.cu"],
-    "stack": ["decode_stack.cu"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

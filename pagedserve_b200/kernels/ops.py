@@ -10,7 +10,6 @@ an error.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
 
 import numpy as np
 import torch

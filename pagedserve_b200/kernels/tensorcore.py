@@ -10,8 +10,6 @@
 
 from __future__ import annotations
 
-import torch
-
 
 def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
     # The weight-streaming kernel re-reads the rows of ``a`` for every 16 output columns: from 17 rows on and

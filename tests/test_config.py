@@ -1,7 +1,6 @@
 """Configuration and the architecture registry."""
 
 import json
-import os
 
 import pytest
 

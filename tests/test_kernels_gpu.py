@@ -3,7 +3,6 @@
 import math
 import random
 
-import numpy as np
 import pytest
 import torch
 

@@ -2,7 +2,6 @@
 a toy mixer with state of its own, a toy architecture with different layers and a schedule that
 runs a layer twice, all registered from here without touching the package."""
 
-import math
 import tempfile
 from dataclasses import dataclass
 

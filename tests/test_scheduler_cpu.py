@@ -1,7 +1,6 @@
 """The scheduler's decisions, with a fake engine (no GPU): admission, portions under a token
 budget, decode priority, finishing and freeing, and what happens when pages run out."""
 
-import numpy as np
 import pytest
 
 from pagedserve_b200.cache import CacheManager, KVNeed
