@@ -53,6 +53,9 @@ class ModelRunner:
 
     MAX_DEVICE_STEPS = 1024          # most decode steps one ``decode`` call runs without the host
     MAX_GRAPHS = 96
+    # A capture costs about 15 ms (synchronise, collect, capture): a shape must come back this often before
+    # it is worth one. Steady chunked prefill and benchmarks repeat shapes; random traffic does not.
+    MIXED_SHAPE_SIGHTINGS = 4
 
     def __init__(self, model, cache: CacheManager, device, max_step_tokens: int = 8192,
                  enable_cuda_graphs: bool = True):
@@ -108,29 +111,30 @@ class ModelRunner:
             raise StepError("a step cannot be empty")                 # reference: iteration.py:50-51
         self._drop_staged()
         cache = self.cache
-        seen = set()
-        for entry in entries:
-            if entry.request in seen:
-                raise StepError("a request can appear only once in a step")   # reference: iteration.py:62-63
-            seen.add(entry.request)
-            low, high = int(entry.tokens.min()), int(entry.tokens.max())
-            if low < 0 or high >= self.vocab_size:
-                raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
-                                f"{self.vocab_size}")
+        I = len(entries)
+        requests = [entry.request for entry in entries]
+        if len(set(requests)) != I:
+            raise StepError("a request can appear only once in a step")       # reference: iteration.py:62-63
+        counts = np.fromiter((len(entry.tokens) for entry in entries), dtype=np.int64, count=I)
+        # layout order: short entries (decode tokens, short portions) first, prompt portions after them
+        is_long = counts >= StepContext.LONG_ENTRY
+        order = np.concatenate([np.flatnonzero(~is_long), np.flatnonzero(is_long)])
+        num_short_items = I - int(is_long.sum())
+        tokens = np.concatenate([entries[source].tokens for source in order])
+        self._check_vocabulary(tokens)
 
         admitted: List[Hashable] = []
         extended: List[Hashable] = []
         try:
-            for entry in entries:
+            for entry, count in zip(entries, counts.tolist()):
                 if entry.request not in cache:
                     cache.admit(entry.request)
                     admitted.append(entry.request)
-                start = cache.length(entry.request)
-                if start + len(entry.tokens) > self.max_model_len:
+                if cache.length(entry.request) + count > self.max_model_len:
                     # reference: src/model/paged_decoder.py:521-522
                     raise StepError(f"request {entry.request!r} would pass the model's maximum length "
                                     f"{self.max_model_len}")
-                cache.extend(entry.request, len(entry.tokens))
+                cache.extend(entry.request, count)
                 extended.append(entry.request)
         except Exception:
             for request in extended:
@@ -140,11 +144,9 @@ class ModelRunner:
             raise
         self._admitted_in_step = admitted
 
-        T = sum(len(entry.tokens) for entry in entries)
-        I = len(entries)
+        T = int(counts.sum())
         R = sum(len(entry.want) for entry in entries)
         layout, views, staging, host = self._stage(T, I, R)
-
         token_ids = host[layout.token_ids:layout.token_ids + T]
         positions = host[layout.positions:layout.positions + T]
         token_item = host[layout.token_item:layout.token_item + T]
@@ -152,52 +154,37 @@ class ModelRunner:
         q_start = host[layout.q_start:layout.q_start + I + 1]
         kv_len = host[layout.kv_len:layout.kv_len + I]
         logit_rows = host[layout.logit_rows:layout.logit_rows + R]
-        # layout order: short entries (decode tokens, short portions) first, prompt portions after them
-        long_entry = StepContext.LONG_ENTRY
-        order = [i for i, e in enumerate(entries) if len(e.tokens) < long_entry] + \
-                [i for i, e in enumerate(entries) if len(e.tokens) >= long_entry]
-        num_short_items = sum(1 for e in entries if len(e.tokens) < long_entry)
-        cursor = 0
-        max_q = 0
-        max_kv = 0
-        num_short_tokens = 0
-        num_long_blocks = 0
-        starts = [0] * I
-        laid_out = []
-        for index, source in enumerate(order):
-            entry = entries[source]
-            count = len(entry.tokens)
-            start = cache.length(entry.request)
-            token_ids[cursor:cursor + count] = entry.tokens
-            positions[cursor:cursor + count] = np.arange(start, start + count, dtype=np.int32)
-            token_item[cursor:cursor + count] = index
-            item_slot[index] = cache.slot_of[entry.request]
-            q_start[index] = cursor
-            kv_len[index] = start + count
-            starts[source] = cursor
-            laid_out.append(entry)
-            max_q = max(max_q, count)
-            max_kv = max(max_kv, start + count)
-            cursor += count
-            if index < num_short_items:
-                num_short_tokens = cursor
-            else:
-                num_long_blocks += -(-count // 64)
-        q_start[I] = cursor
-        row = 0
-        for source, entry in enumerate(entries):          # logits rows keep the caller's order
-            for place in entry.want:
-                logit_rows[row] = starts[source] + place
-                row += 1
+
+        # whole-array fills, in layout order
+        slot_of = cache.slot_of
+        slots = np.fromiter((slot_of[requests[source]] for source in order), dtype=np.int64, count=I)
+        laid_counts = counts[order]
+        starts = cache.lengths[slots].astype(np.int64)                 # cached length of each laid-out item
+        first = np.zeros(I + 1, dtype=np.int64)
+        np.cumsum(laid_counts, out=first[1:])                          # first token of each laid-out item
+        token_ids[:] = tokens
+        item_of_token = np.repeat(np.arange(I, dtype=np.int64), laid_counts)
+        token_item[:] = item_of_token
+        positions[:] = np.arange(T, dtype=np.int64) + (starts - first[:-1])[item_of_token]
+        item_slot[:] = slots
+        q_start[:] = first
+        kv_len[:] = starts + laid_counts
+        num_short_tokens = int(first[num_short_items])
+        num_long_blocks = int((-(-laid_counts[num_short_items:] // 64)).sum())
+        first_of_source = np.empty(I, dtype=np.int64)
+        first_of_source[order] = first[:-1]
+        if R:                                                          # logits rows keep the caller's order
+            logit_rows[:] = [int(first_of_source[source]) + place
+                             for source, entry in enumerate(entries) for place in entry.want]
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
-            cache.table_rows(group_index, item_slot, host[offset:offset + I * width].reshape(I, width))
+            cache.table_rows(group_index, slots, host[offset:offset + I * width].reshape(I, width))
 
         host[layout.counter] = 0
         self._upload(layout, staging)
         host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
-                               [entry.request for entry in laid_out])
-        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, max_q, max_kv,
-                           num_short_items, num_short_tokens, num_long_blocks, views=views)
+                               [requests[source] for source in order])
+        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, int(laid_counts.max()),
+                           int(kv_len.max()), num_short_items, num_short_tokens, num_long_blocks, views=views)
 
     def _stage(self, T: int, I: int, R: int):
         """The layout of a step shape, its device views, and the pinned staging buffer of this turn."""
@@ -425,7 +412,7 @@ class ModelRunner:
         """A step with prompt portions.  Its ~100 launches cost the host about as much time as the device
         needs to run them, so a step shape that comes back (same counts of tokens, entries, wanted rows,
         short entries and query blocks: a steady chunked-prefill budget, a benchmark) is captured as a CUDA
-        graph the second time it is seen and replayed from then on."""
+        graph once it has been seen ``MIXED_SHAPE_SIGHTINGS`` times and replayed from then on."""
         bucket = -(-ctx.max_kv_len // 256) * 256
         ctx.max_kv_len = min(bucket, self.max_model_len)
         key = (ctx.num_tokens, ctx.num_items, ctx.num_logit_rows, ctx.num_short_items, ctx.num_short_tokens,
@@ -438,7 +425,7 @@ class ModelRunner:
         seen = self._shape_seen.get(key, 0) + 1
         self._shape_seen[key] = seen
         logits = self.model.forward(ctx)
-        if seen < 2:
+        if seen < self.MIXED_SHAPE_SIGHTINGS:
             if len(self._shape_seen) > 4096:
                 self._shape_seen.clear()
             return logits
