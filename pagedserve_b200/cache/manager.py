@@ -113,7 +113,7 @@ class CacheGroup:
     """Layers with the same :class:`KVNeed`: one pool, one free list, one set of tables."""
 
     def __init__(self, need: KVNeed, cache_layers: Sequence[int], page_size: int, num_pages: int,
-                 max_pages_per_request: int, dtype=None, device=None):
+                 max_pages_per_request: int, dtype=None, device=None, scratch_pages: int = 0):
         self.need = need
         self.cache_layers = list(cache_layers)      # global cache-layer ids, in pool order
         self.page_size = page_size
@@ -123,8 +123,11 @@ class CacheGroup:
         self.tables: Dict[Hashable, List[int]] = {}
         self.rows = None                            # [slots, max pages] int32 mirror of the tables, -1 = no page
         self.pool = None
+        # pages behind the allocator's range that belong to no request (padding tokens of a step write there)
+        self.scratch_pages = list(range(num_pages, num_pages + scratch_pages))
         if device is not None:
-            shape = (num_pages, len(self.cache_layers), 2, need.n_kv_heads, page_size, need.head_dim)
+            shape = (num_pages + scratch_pages, len(self.cache_layers), 2, need.n_kv_heads, page_size,
+                     need.head_dim)
             self.pool = torch.empty(shape, dtype=dtype, device=device)
 
     # strides in elements, used by the kernels
@@ -158,7 +161,7 @@ class CacheManager:
 
     def __init__(self, kv_needs: Sequence[Optional[KVNeed]], state_needs: Sequence[Optional[StateNeed]],
                  page_size: int, num_pages: int, max_slots: int, max_model_len: int,
-                 dtype=None, device=None):
+                 dtype=None, device=None, scratch_tokens: int = 0):
         if page_size <= 0 or (page_size & (page_size - 1)) or page_size > 64:
             raise CacheError("page_size must be a power of two, at most 64")
         if max_slots <= 0:
@@ -174,13 +177,19 @@ class CacheManager:
         for layer, need in enumerate(kv_needs):
             if need is not None:
                 by_need.setdefault(need, []).append(layer)
+        # A scratch slot (index max_slots) with pages for ``scratch_tokens`` positions, outside the allocator and
+        # the slot list: a step that pads its batch to a recurring shape sends the padding there.
+        self.scratch_tokens = min(scratch_tokens, max_model_len)
+        scratch_pages = -(-self.scratch_tokens // page_size)
+        self.scratch_slot = max_slots
         self.groups: List[CacheGroup] = [
-            CacheGroup(need, layers, page_size, num_pages, self.max_pages_per_request, dtype, device)
+            CacheGroup(need, layers, page_size, num_pages, self.max_pages_per_request, dtype, device, scratch_pages)
             for need, layers in by_need.items()
         ]
         for group in self.groups:
             # the tables once more as one array by slot, so that a step gathers its rows in one operation
-            group.rows = np.full((max_slots, self.max_pages_per_request), -1, dtype=np.int32)
+            group.rows = np.full((max_slots + 1, self.max_pages_per_request), -1, dtype=np.int32)
+            group.rows[max_slots, :scratch_pages] = group.scratch_pages
         self.group_of_layer: Dict[int, int] = {
             layer: index for index, group in enumerate(self.groups) for layer in group.cache_layers
         }
@@ -195,7 +204,7 @@ class CacheManager:
         if device is not None:
             for layer, need in enumerate(state_needs):
                 if need is not None:
-                    self.state[layer] = torch.zeros((max_slots, *need.shape), dtype=getattr(torch, need.dtype),
+                    self.state[layer] = torch.zeros((max_slots + 1, *need.shape), dtype=getattr(torch, need.dtype),
                                                     device=device)
 
     # ------------------------------------------------------------------ queries

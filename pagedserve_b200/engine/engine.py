@@ -95,7 +95,8 @@ class Engine:
             affordable = int(free * 0.5) // max(bytes_per_page, 1)
             num_pages = max(1, min(wanted, affordable))
         return CacheManager(kv_needs, state_needs, cfg.block_size, int(num_pages), cfg.max_num_seqs,
-                            self.spec.max_model_len, dtype=self.dtype, device=self.device)
+                            self.spec.max_model_len, dtype=self.dtype, device=self.device,
+                            scratch_tokens=ModelRunner.PAD_LONG)
 
     # ------------------------------------------------------------------ the calls a user makes
     @property

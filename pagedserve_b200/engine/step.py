@@ -53,9 +53,13 @@ class ModelRunner:
 
     MAX_DEVICE_STEPS = 1024          # most decode steps one ``decode`` call runs without the host
     MAX_GRAPHS = 96
-    # A capture costs about 15 ms (synchronise, collect, capture): a shape must come back this often before
-    # it is worth one. Steady chunked prefill and benchmarks repeat shapes; random traffic does not.
-    MIXED_SHAPE_SIGHTINGS = 4
+    # A capture costs about as much as two eager steps: a shape must come back before it is worth one.
+    MIXED_SHAPE_SIGHTINGS = 2
+    # Mixed steps are padded to recurring shapes so that their graphs are found again: short tokens to a
+    # multiple of PAD_SHORT, tokens of prompt portions to a multiple of PAD_LONG, entries and wanted rows to
+    # multiples of 8 and 4. The padding tokens belong to the cache's scratch slot.
+    PAD_SHORT = 16
+    PAD_LONG = 128
 
     def __init__(self, model, cache: CacheManager, device, max_step_tokens: int = 8192,
                  enable_cuda_graphs: bool = True):
@@ -76,6 +80,9 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.enable_cuda_graphs = enable_cuda_graphs and model.graph_safe
+        # padding needs the scratch slot's pages and positions 0 .. PAD_LONG - 1 to exist in the model
+        self._pad_mixed = (self.enable_cuda_graphs and cache.scratch_tokens >= self.PAD_LONG
+                           and self.max_model_len >= 2 * self.PAD_LONG)
         self.ops = model.env.ops
         self._graphs = {}                 # (batch size, kind) or step shape -> _DecodeGraph
         self._shape_seen = {}             # step shape -> times seen (a shape is captured when it comes back)
@@ -86,6 +93,8 @@ class ModelRunner:
         self._history = self.ops.mapped_host_buffer(self.MAX_DEVICE_STEPS * cache.max_slots)
         self._shapes = {}                 # (T, I, R) -> (BatchLayout, DeviceViews)
         self._staged = None               # a decode step staged ahead of its tokens
+        self._capture_stream = None       # made at the first capture
+        self._graph_pool = None
         self._ramp = np.arange(cache.max_slots + 2, dtype=np.int32)
 
     def _grow(self, needed: int) -> None:
@@ -105,8 +114,9 @@ class ModelRunner:
             event.record()
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Validate, take pages for the new positions, build and upload the metadata."""
+    def prepare(self, entries: Sequence[StepEntry], pad: bool = False) -> StepContext:
+        """Validate, take pages for the new positions, build and upload the metadata.  ``pad``: bring the
+        batch to a recurring shape with padding tokens and empty entries (see PAD_SHORT)."""
         if not entries:
             raise StepError("a step cannot be empty")                 # reference: iteration.py:50-51
         self._drop_staged()
@@ -146,6 +156,44 @@ class ModelRunner:
 
         T = int(counts.sum())
         R = sum(len(entry.want) for entry in entries)
+        slot_of = cache.slot_of
+        slots = np.fromiter((slot_of[requests[source]] for source in order), dtype=np.int64, count=I)
+        laid_counts = counts[order]
+        starts = cache.lengths[slots].astype(np.int64)                 # cached length of each laid-out item
+        num_long_items = I - num_short_items
+        short_tokens = int(laid_counts[:num_short_items].sum())
+        long_tokens = T - short_tokens
+        real_items, real_rows = I, R
+        if pad:
+            # one padding entry behind the short entries and one behind the long ones take the padding tokens
+            # (positions 0.. of the scratch slot); further entries are empty
+            up = lambda value, step: -(-value // step) * step
+            pad_short = up(short_tokens, self.PAD_SHORT) - short_tokens
+            pad_long = up(long_tokens, self.PAD_LONG) - long_tokens
+            short_items = up(num_short_items + (pad_short > 0), 8) if short_tokens else 0
+            long_items = up(num_long_items + (pad_long > 0), 4) if long_tokens else 0
+            scratch = cache.scratch_slot
+            pieces = lambda real, extra, total: np.concatenate(
+                [real, np.full(1 if extra else 0, extra, dtype=np.int64),
+                 np.zeros(total - len(real) - (1 if extra else 0), dtype=np.int64)])
+            laid_counts = np.concatenate([pieces(laid_counts[:num_short_items], pad_short, short_items),
+                                          pieces(laid_counts[num_short_items:], pad_long, long_items)])
+            fill = lambda real, total: np.concatenate([real, np.full(total - len(real), scratch, dtype=np.int64)])
+            slots = np.concatenate([fill(slots[:num_short_items], short_items),
+                                    fill(slots[num_short_items:], long_items)])
+            zeros = lambda real, total: np.concatenate([real, np.zeros(total - len(real), dtype=np.int64)])
+            starts = np.concatenate([zeros(starts[:num_short_items], short_items),
+                                     zeros(starts[num_short_items:], long_items)])
+            tokens = np.concatenate([tokens[:short_tokens], np.zeros(pad_short, dtype=np.int64),
+                                     tokens[short_tokens:], np.zeros(pad_long, dtype=np.int64)])
+            # where the real entries went: item index and first token of each source entry
+            new_index = np.concatenate([np.arange(num_short_items),
+                                        short_items + np.arange(num_long_items)])
+            num_short_items, I = short_items, short_items + long_items
+            T = short_tokens + pad_short + long_tokens + pad_long
+            R = up(R, 8)
+        else:
+            new_index = np.arange(I)
         layout, views, staging, host = self._stage(T, I, R)
         token_ids = host[layout.token_ids:layout.token_ids + T]
         positions = host[layout.positions:layout.positions + T]
@@ -156,10 +204,6 @@ class ModelRunner:
         logit_rows = host[layout.logit_rows:layout.logit_rows + R]
 
         # whole-array fills, in layout order
-        slot_of = cache.slot_of
-        slots = np.fromiter((slot_of[requests[source]] for source in order), dtype=np.int64, count=I)
-        laid_counts = counts[order]
-        starts = cache.lengths[slots].astype(np.int64)                 # cached length of each laid-out item
         first = np.zeros(I + 1, dtype=np.int64)
         np.cumsum(laid_counts, out=first[1:])                          # first token of each laid-out item
         token_ids[:] = tokens
@@ -170,12 +214,16 @@ class ModelRunner:
         q_start[:] = first
         kv_len[:] = starts + laid_counts
         num_short_tokens = int(first[num_short_items])
-        num_long_blocks = int((-(-laid_counts[num_short_items:] // 64)).sum())
-        first_of_source = np.empty(I, dtype=np.int64)
-        first_of_source[order] = first[:-1]
+        if pad:                                                        # a bound that depends on the padded shape alone
+            num_long_blocks = int(laid_counts[num_short_items:].sum()) // 64 + (I - num_short_items)
+        else:
+            num_long_blocks = int((-(-laid_counts[num_short_items:] // 64)).sum())
+        first_of_source = np.empty(real_items, dtype=np.int64)
+        first_of_source[order] = first[new_index]
         if R:                                                          # logits rows keep the caller's order
-            logit_rows[:] = [int(first_of_source[source]) + place
-                             for source, entry in enumerate(entries) for place in entry.want]
+            rows = [int(first_of_source[source]) + place
+                    for source, entry in enumerate(entries) for place in entry.want]
+            logit_rows[:] = rows + [rows[0] if rows else 0] * (R - real_rows)
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
             cache.table_rows(group_index, slots, host[offset:offset + I * width].reshape(I, width))
 
@@ -183,8 +231,10 @@ class ModelRunner:
         self._upload(layout, staging)
         host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
                                [requests[source] for source in order])
-        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, int(laid_counts.max()),
-                           int(kv_len.max()), num_short_items, num_short_tokens, num_long_blocks, views=views)
+        ctx = StepContext(layout, self._device_buffer, host_batch, cache, self._status, int(laid_counts.max()),
+                          int(kv_len.max()), num_short_items, num_short_tokens, num_long_blocks, views=views)
+        ctx.real_logit_rows = real_rows
+        return ctx
 
     def _stage(self, T: int, I: int, R: int):
         """The layout of a step shape, its device views, and the pinned staging buffer of this turn."""
@@ -310,8 +360,8 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one step; returns float32 logits ``[R, V]`` (R may be 0)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        ctx = self.prepare(entries)
-        decode_only = ctx.decode_only and all(entry.want == [0] for entry in entries)
+        decode_only = all(len(entry.tokens) == 1 and entry.want == [0] for entry in entries)
+        ctx = self.prepare(entries, pad=self._pad_mixed and not decode_only)
         try:
             if decode_only and self.enable_cuda_graphs:
                 logits = self._run_decode_graph(ctx, "logits").logits.clone()
@@ -417,27 +467,44 @@ class ModelRunner:
         ctx.max_kv_len = min(bucket, self.max_model_len)
         key = (ctx.num_tokens, ctx.num_items, ctx.num_logit_rows, ctx.num_short_items, ctx.num_short_tokens,
                ctx.num_long_blocks, ctx.max_kv_len, "mixed")
+        rows = ctx.real_logit_rows                   # the rest are padding
         graph = self._graphs.get(key)
         if graph is not None:
             graph.replay()
             self.graph_replays += 1
-            return graph.logits.clone()
+            return graph.logits[:rows].clone()
         seen = self._shape_seen.get(key, 0) + 1
         self._shape_seen[key] = seen
-        logits = self.model.forward(ctx)
+        logits = self.model.forward(ctx)[:rows]
         if seen < self.MIXED_SHAPE_SIGHTINGS:
             if len(self._shape_seen) > 4096:
                 self._shape_seen.clear()
             return logits
         if len(self._graphs) >= self.MAX_GRAPHS:
             self._graphs.pop(next(iter(self._graphs)))
-        torch.cuda.current_stream().synchronize()
         launches_before = self.ops.launches
-        captured = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(captured):
-            static_logits = self.model.forward(ctx)
+        captured, static_logits = self._capture(lambda: self.model.forward(ctx))
         self._graphs[key] = _DecodeGraph(captured, static_logits, self.ops.launches - launches_before)
         return logits
+
+    def _capture(self, run):
+        """Capture the launches of ``run()`` as a CUDA graph: on a side stream, into the pool that all graphs
+        of this runner share. (``torch.cuda.graph`` would also synchronise the device, collect garbage and
+        empty the allocator's cache, about 15 ms and a slow restart of every eager step after it.)"""
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(self.device)
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        side, main = self._capture_stream, torch.cuda.current_stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                result = run()
+            finally:
+                graph.capture_end()
+        main.wait_stream(side)
+        return graph, result
 
     def _run_decode_graph(self, ctx: StepContext, kind: str):
         """Run the decode-only step ``ctx`` once: eagerly the first time a batch size is seen
@@ -456,11 +523,9 @@ class ModelRunner:
             self._forward_and_sample(ctx)
         else:
             warm = self.model.forward(ctx)
-        torch.cuda.current_stream().synchronize()
         launches_before = self.ops.launches
-        captured = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(captured):
-            logits = self._forward_and_sample(ctx) if kind == "sample" else self.model.forward(ctx)
+        captured, logits = self._capture(
+            lambda: self._forward_and_sample(ctx) if kind == "sample" else self.model.forward(ctx))
         graph = _DecodeGraph(captured, logits, self.ops.launches - launches_before)
         self._graphs[key] = graph
         if kind == "logits":

@@ -78,3 +78,39 @@ def test_a_reused_page_never_leaks_and_page_edges_hold(dtype, tol):
         engine.finish("new")
         pool[table].mul_(50.0) if dtype == "float32" else None
     engine.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_padded_mixed_steps_replay_as_graphs(dtype):
+    """Mixed steps are padded to recurring shapes (padding tokens go to the cache's scratch slot) and replayed
+    as CUDA graphs once a shape has come back.  Steps of different real sizes that share a padded shape must
+    give the logits of an engine that runs every step eagerly and unpadded."""
+    from pagedserve_b200.engine.batch import StepEntry
+    from test_generation_gpu import make_engine
+
+    vocab = helpers.TINY["c"][0]["vocab_size"]
+    padded = make_engine("c", dtype, num_blocks=96)
+    eager = make_engine("c", dtype, num_blocks=96, enable_cuda_graphs=False)
+    assert padded.runner._pad_mixed and not eager.runner._pad_mixed
+    scale = None
+    for round_index, (long_len, short_len, decode_count) in enumerate([(100, 5, 3), (97, 3, 2), (120, 7, 3),
+                                                                      (101, 2, 1), (99, 9, 3)]):
+        # a prompt portion, a short portion and a few single tokens of requests that already have a prompt
+        results = []
+        for engine in (padded, eager):
+            base = 1000 * round_index
+            prompts = {base + i: helpers.random_tokens(vocab, 20 + 7 * i, seed=base + i) for i in range(decode_count)}
+            engine.step([StepEntry(name, tokens, []) for name, tokens in prompts.items()])
+            entries = [StepEntry(base + 50, helpers.random_tokens(vocab, long_len, seed=base + 50), [long_len - 1]),
+                       StepEntry(base + 51, helpers.random_tokens(vocab, short_len, seed=base + 51), [0, short_len - 1])]
+            entries += [StepEntry(name, [len(tokens) % vocab], [0]) for name, tokens in prompts.items()]
+            results.append(engine.step(entries).float().cpu())
+            for entry in entries:
+                engine.finish(entry.request)
+            engine.cache.check_invariants()
+        got, want = results
+        scale = float(want.abs().max())
+        assert got.shape == want.shape
+        assert float((got - want).abs().max()) <= helpers.TOLERANCE[dtype] * scale, f"round {round_index}"
+    assert padded.runner.graph_replays > 0            # the rounds shared padded shapes
+    assert padded.cache.free_pages() == padded.cache.total_pages()
