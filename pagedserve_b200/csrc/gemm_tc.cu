@@ -129,7 +129,8 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 template <int BN> struct Config {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 5 : 6);
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    // two accumulators of BN columns; an allocation is a power of two of at least 32 columns
+    static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
     static constexpr int STAGING_BYTES = 2 * BM * 128;           // two buffers of 128 rows x 128 bytes
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
@@ -506,12 +507,20 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
         const int tiles_m = (M + BM - 1) / BM;
         // widest tile that still gives the SMs enough tiles (measured on B200: 128 wide wins until the
         // grid falls below half the SMs; 256 wide needs two full waves)
+        const int t128 = tiles_m * ((N + 127) / 128), t96 = tiles_m * ((N + 95) / 96);
         if (tiles_m * ((N + 255) / 256) >= 2 * sm_count()) bn = 256;
-        else if (2 * tiles_m * ((N + 127) / 128) >= sm_count()) bn = 128;
+        // float32 output (the products that add into the residual stream, N = the model width): 96 wide when
+        // that fills more of one wave (2,048 x 768: 128 CTAs instead of 96)
+        else if (sizeof(TOut) == 4 && t128 < sm_count() && t96 <= sm_count() && t96 > t128 && 2 * t128 >= sm_count())
+            bn = 96;
+        else if (2 * t128 >= sm_count()) bn = 128;
         else bn = 64;
     }
     if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
     if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    if constexpr (sizeof(TOut) == 4) {      // 96 columns are three 32-column groups of float32; bfloat16 groups are 64 wide
+        if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    }
     if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
     return PS_ERR_BAD_ARGUMENT;
 }

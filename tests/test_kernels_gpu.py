@@ -163,6 +163,35 @@ def test_gemm_tcgen05(M, N, K, bn):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 768, 768), (257, 770, 3072), (130, 1003, 96), (300, 96, 64)])
+def test_gemm_tcgen05_96_wide(M, N, K):
+    """Tiles of 96 columns exist for float32 outputs (three 32-column groups of the epilogue); a bfloat16
+    output is refused at that width."""
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for act in (None, "gelu_erf"):
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        ops.linear_tc(a.to(DEV), w.to(DEV), bias.to(DEV), out, act=act, status=status, bn=96)
+        assert rel_err(out, gemm_reference(a, w, bias, act, None)) < 2e-5
+    base = torch.randn(M, N, generator=g)
+    stream = base.clone().to(DEV)
+    ops.linear_tc(a.to(DEV), w.to(DEV), bias.to(DEV), stream, accumulate=True, status=status, bn=96)
+    assert rel_err(stream, gemm_reference(a, w, bias, None, base)) < 2e-5
+    other = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_tc(a.to(DEV), w.to(DEV), bias.to(DEV), out, status=status, bn=96)
+    ops.linear_tc(a.to(DEV), w.to(DEV), bias.to(DEV), other, status=status, bn=128)
+    assert torch.equal(out, other)                        # the tile width does not change a sum
+    assert int(status.item()) == 0
+    from pagedserve_b200.kernels.ops import KernelError
+    with pytest.raises(KernelError):
+        ops.linear_tc(a.to(DEV), w.to(DEV), bias.to(DEV), torch.empty(M, N, dtype=torch.bfloat16, device=DEV),
+                      status=status, bn=96)
+
+
 @pytest.mark.parametrize("M", [1, 8, 9, 16, 25, 32])
 @pytest.mark.parametrize("N,K", [(288, 96), (2304, 768), (1000, 320), (768, 3072)])
 def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
