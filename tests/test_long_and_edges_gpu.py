@@ -114,3 +114,60 @@ def test_padded_mixed_steps_replay_as_graphs(dtype):
         assert float((got - want).abs().max()) <= helpers.TOLERANCE[dtype] * scale, f"round {round_index}"
     assert padded.runner.graph_replays > 0            # the rounds shared padded shapes
     assert padded.cache.free_pages() == padded.cache.total_pages()
+
+
+@pytest.mark.parametrize("which", ["b", "d"])
+def test_random_mixed_steps_padded_graphs_equal_eager(which):
+    """Random traffic: every step a random mix of new prompts, portions that continue a prompt, short portions
+    and single tokens, with random wanted places; requests end at random.  The engine that pads and replays
+    graphs must return what the engine that runs every step eagerly and unpadded returns."""
+    import random
+
+    from pagedserve_b200.engine.batch import StepEntry
+    from test_generation_gpu import make_engine
+
+    config, _, block = helpers.TINY[which]
+    vocab, limit = config["vocab_size"], config["n_positions"]
+    engines = [make_engine(which, "bfloat16", num_blocks=4096 // block, max_num_seqs=12),
+               make_engine(which, "bfloat16", num_blocks=4096 // block, max_num_seqs=12, enable_cuda_graphs=False)]
+    assert engines[0].runner._pad_mixed
+    rng = random.Random(17)
+    live = {}                          # request -> tokens so far
+    next_name = 0
+    for step_index in range(60):
+        entries = []
+        for name in list(live):
+            if rng.random() < 0.15:
+                if live[name]:                                     # it has run at least once
+                    for engine in engines:
+                        engine.finish(name)
+                del live[name]
+        while len(live) < 12 and rng.random() < 0.5:
+            live[next_name] = 0
+            next_name += 1
+        for name, held in live.items():
+            if rng.random() < 0.2:
+                continue                                           # left out of this step
+            room = limit - held
+            if room <= 0:
+                continue
+            kind = rng.random()
+            count = 1 if kind < 0.5 else rng.randint(2, 15) if kind < 0.7 else rng.randint(16, 90)
+            count = min(count, room)
+            tokens = [rng.randrange(vocab) for _ in range(count)]
+            want = sorted(rng.sample(range(count), rng.randint(0, min(count, 3))))
+            if count == 1:
+                want = [0]
+            entries.append((name, tokens, want))
+        if not entries:
+            continue
+        outputs = [engine.step([StepEntry(*entry) for entry in entries]).float().cpu() for engine in engines]
+        for name, tokens, _ in entries:
+            live[name] += len(tokens)
+        assert outputs[0].shape == outputs[1].shape
+        if outputs[0].numel():
+            scale = float(outputs[1].abs().max())
+            assert float((outputs[0] - outputs[1]).abs().max()) <= 1e-2 * scale, f"step {step_index}"
+    for engine in engines:
+        engine.cache.check_invariants()
+    assert engines[0].runner.graph_replays > 0
