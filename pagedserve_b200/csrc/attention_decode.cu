@@ -375,6 +375,38 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int i = 0; i < HOLD; ++i)
             held[i] = i < n_active ? ldcg_f32(part_acc + (base + i) * head_dim + d0) : 0.f;
     }
+    if (n_active <= HOLD) {
+        // few splits (the usual case): every thread takes the (max, sum) pairs too and weighs for itself:
+        // one trip to L2 for everything, no shared memory, no barrier
+        float mh[HOLD], lh[HOLD];
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            mh[i] = -INFINITY;
+            lh[i] = 0.f;
+            if (i < n_active)
+                asm volatile("ld.global.cg.v2.f32 {%0, %1}, [%2];" : "=f"(mh[i]), "=f"(lh[i]) : "l"(part_ml + (base + i) * 2));
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) M = fmaxf(M, mh[i]);
+        float L = 0.f;
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            mh[i] = (i < n_active) ? exp2f(mh[i] - M) : 0.f;           // now the weight of split i
+            L += lh[i] * mh[i];
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int d = d0, round = 0; d < head_dim; d += DEC_THREADS, ++round) {
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < HOLD; ++i) {
+                if (i < n_active)
+                    o += (round == 0 ? held[i] : ldcg_f32(part_acc + (base + i) * head_dim + d)) * mh[i];
+            }
+            out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
+        }
+        return;
+    }
     float* w_s = reinterpret_cast<float*>(k_s);               // the K buffer is free now: [n_active] weights
     float* ml_s = w_s + n_active;                             // then [n_active][2]
     const bool staged = 3 * n_active * 4 <= 2 * chunk_keys * head_dim;      // always, unless a huge split count
