@@ -171,3 +171,45 @@ def test_random_mixed_steps_padded_graphs_equal_eager(which):
     for engine in engines:
         engine.cache.check_invariants()
     assert engines[0].runner.graph_replays > 0
+
+
+def test_benchmark_sizes_match_plain():
+    """The layer sizes the benchmark runs (GPT-2 124M: 12 layers, width 768, 12 heads of 64, inner 3,072,
+    vocabulary 50,257) with random weights: a 150-token prompt whole, then decoded tokens, against the plain
+    implementation, in float32 and in bfloat16 (whose decode steps run the fused few-rows kernels, the
+    tcgen05 products and both attention kernels at their real shapes)."""
+    import torch
+
+    from pagedserve_b200.config.engine_config import EngineConfig
+    from pagedserve_b200.config.gpt2 import named_config
+    from pagedserve_b200.engine.batch import StepEntry
+    from pagedserve_b200.engine.engine import Engine
+    from pagedserve_b200.weights.random_init import random_tensors
+
+    config = named_config("gpt2-124m")
+    tensors = random_tensors(config, 0)
+    weights = {name[len("transformer."):] if name.startswith("transformer.") else name: tensor.double()
+               for name, tensor in tensors.items()}
+    tokens = helpers.random_tokens(config.vocab_size, 156, seed=99)
+    want = plain_gpt2.forward_logits(config.to_dict(), weights, tokens)[-7:].numpy()
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine(config, EngineConfig(dtype=dtype, num_blocks=128, max_num_seqs=8), tensors=tensors)
+        got = [engine.step([StepEntry("r", tokens[:150], [149])]).cpu().numpy()]
+        for place in range(150, 156):
+            got.append(engine.step([StepEntry("r", [tokens[place]], [0])]).cpu().numpy())
+        helpers.assert_close(np.concatenate(got), want, dtype, f"gpt2-124m/{dtype}")
+        engine.finish("r")
+        if dtype == "bfloat16":
+            # the benchmark's step: eight requests decode together (a replayed graph from the second step on)
+            prompts = [helpers.random_tokens(config.vocab_size, 24 + 19 * i, seed=7 + i) for i in range(8)]
+            tails = [helpers.random_tokens(config.vocab_size, 3, seed=70 + i) for i in range(8)]
+            engine.step([StepEntry(i, prompt, []) for i, prompt in enumerate(prompts)])
+            rows = [engine.step([StepEntry(i, [tails[i][place]], [0]) for i in range(8)]).cpu().numpy()
+                    for place in range(3)]
+            assert engine.runner.graph_replays > 0
+            for i in range(8):
+                plain = plain_gpt2.forward_logits(config.to_dict(), weights, prompts[i] + tails[i])[-3:].numpy()
+                helpers.assert_close(np.stack([rows[place][i] for place in range(3)]), plain, dtype,
+                                     f"gpt2-124m/batch 8/request {i}")
+        del engine
+        torch.cuda.empty_cache()
