@@ -66,11 +66,14 @@ def reference_logits(reference_root, config, weights, token_ids):
 
 
 def main():
-    reference_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of a checkout of jainalphin/pagedserve>")
+    reference_root = sys.argv[1]
     from pagedserve_b200.config.gpt2 import GPT2Config
     from pagedserve_b200.weights.random_init import write_random_model
 
-    for which, (values, seed, _) in TINY.items():
+    for which in ("a", "b"):
+        values, seed, _ = TINY[which]
         with tempfile.TemporaryDirectory() as folder:
             write_random_model(folder, GPT2Config(**values), seed)
             config, weights = plain_gpt2.read_folder(folder, dtype=torch.float32)
