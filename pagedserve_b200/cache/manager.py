@@ -97,6 +97,21 @@ class PageAllocator:
         self.peak_used = max(self.peak_used, self.used_pages)
         return page
 
+    def allocate_many(self, count: int) -> List[int]:
+        """``count`` pages in the order that ``allocate`` would hand them out, or none at all."""
+        if count > len(self._free):
+            raise CacheFull("KV cache full")
+        if count <= 0:
+            return []
+        pages = self._free[-count:][::-1]
+        del self._free[-count:]
+        taken = np.asarray(pages, dtype=np.int64)
+        if self._held[taken].any():
+            raise CacheError("a page was handed out twice")
+        self._held[taken] = True
+        self.peak_used = max(self.peak_used, self.used_pages)
+        return pages
+
     def release(self, page: int) -> None:
         if not (0 <= page < self.num_pages):
             raise CacheError(f"page id {page} is outside the pool")
@@ -280,13 +295,13 @@ class CacheManager:
         try:
             for group in self.groups:
                 table = group.tables[request]
+                old_len = len(table)
                 fresh: List[int] = []
-                taken.append((group, fresh, len(table)))
-                while len(table) < needed:
-                    page = group.allocator.allocate()
-                    fresh.append(page)
-                    group.rows[slot, len(table)] = page
-                    table.append(page)
+                taken.append((group, fresh, old_len))
+                if needed > old_len:
+                    fresh.extend(group.allocator.allocate_many(needed - old_len))
+                    group.rows[slot, old_len:needed] = fresh
+                    table.extend(fresh)
         except CacheFull:
             for group, fresh, old_len in taken:
                 del group.tables[request][old_len:]

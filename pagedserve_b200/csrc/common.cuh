@@ -62,6 +62,22 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Where the key and value columns of a packed q|k|v projection go when the product's own epilogue writes them
+// into the pages (k_pool null = nowhere: everything goes to the output buffer).
+struct KvScatter {
+    __nv_bfloat16* k_pool;
+    __nv_bfloat16* v_pool;
+    long long page_stride;
+    const int* token_item;
+    const int* positions;
+    const int* block_table;
+    int bt_stride;
+    int q_width;       // columns [0, q_width) are queries and go to `out`
+    int kv_width;      // then kv_width key columns, then kv_width value columns
+    int head_dim;
+    int page_size;
+};
+
 // Thread-block clusters: CTAs of a cluster read each other's shared memory after a cluster barrier.
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -190,19 +190,6 @@ int pick_tiles(const void* A, int lda, const void* W, int ldw, const float* bias
 //   columns n >= q_width of the result are keys and values: they are written straight into the
 //             request's page (cache layout of attention_simt.cu) instead of the output buffer.
 // This removes the norm launch and the kv-append launch of a decode step.
-struct KvScatter {
-    __nv_bfloat16* k_pool;
-    __nv_bfloat16* v_pool;
-    long long page_stride;
-    const int* token_item;
-    const int* positions;
-    const int* block_table;
-    int bt_stride;
-    int q_width;       // columns [0, q_width) are queries and go to `out`
-    int kv_width;      // then kv_width key columns, then kv_width value columns
-    int head_dim;
-    int page_size;
-};
 
 struct NormInput {
     const float* x;    // float32 rows

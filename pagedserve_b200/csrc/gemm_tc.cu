@@ -139,7 +139,7 @@ template <int BN, typename TOut, bool TMA_OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias, TOut* __restrict__ out,
-               int ldo, int M, int N, int K, int act, int accumulate, int* __restrict__ status) {
+               int ldo, int M, int N, int K, int act, int accumulate, int* __restrict__ status, KvScatter kv) {
     using Cfg = Config<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -243,6 +243,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             const int buf = local & 1;
+            // a q|k|v product whose key and value columns go straight into the pages: where this row's go
+            // (offset of page, head 0, position in page, 0), looked up while the tile is still being computed
+            long long kv_base = -1;
+            if constexpr (TMA_OUT && sizeof(TOut) == 2) {
+                const int row = m0 + quarter * 32 + lane;
+                if (kv.k_pool && row < M && n0 + BN > kv.q_width) {
+                    const int p = kv.positions[row];
+                    const int page = kv.block_table[(size_t)kv.token_item[row] * kv.bt_stride + p / kv.page_size];
+                    if (page >= 0) kv_base = (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim;
+                }
+            }
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) { ok = false; if (lane == 0) atomicExch(status, 14); break; }
             tc_fence_after();
             const int m = m0 + quarter * 32 + lane;
@@ -286,6 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                         // 16-byte pieces of the row, XOR-swizzled by the row as the tensor map expects
                         if constexpr (sizeof(TOut) == 2) {
+                            const bool to_pages = kv.k_pool && n >= kv.q_width;      // key / value columns
 #pragma unroll
                             for (int piece = 0; piece < 4; ++piece) {
                                 uint4 pack;
@@ -295,8 +307,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * piece + 6], v[8 * piece + 7]);
                                 pack.x = *reinterpret_cast<uint32_t*>(&p0); pack.y = *reinterpret_cast<uint32_t*>(&p1);
                                 pack.z = *reinterpret_cast<uint32_t*>(&p2); pack.w = *reinterpret_cast<uint32_t*>(&p3);
-                                const int slot = (4 * half + piece) ^ (r & 7);
-                                *reinterpret_cast<uint4*>(stage_buf + r * 128 + slot * 16) = pack;
+                                if (to_pages) {
+                                    // 8 columns of one head (head sizes are multiples of 16, pieces start on multiples of 8)
+                                    int idx = n + 8 * piece - kv.q_width;
+                                    __nv_bfloat16* pool = kv.k_pool;
+                                    if (idx >= kv.kv_width) { idx -= kv.kv_width; pool = kv.v_pool; }
+                                    const int head = idx / kv.head_dim, d = idx - head * kv.head_dim;
+                                    if (kv_base >= 0 && n + 8 * piece < N)
+                                        *reinterpret_cast<uint4*>(pool + kv_base + (long long)head * kv.page_size * kv.head_dim + d) = pack;
+                                } else {
+                                    const int slot = (4 * half + piece) ^ (r & 7);
+                                    *reinterpret_cast<uint4*>(stage_buf + r * 128 + slot * 16) = pack;
+                                }
                             }
                         } else {
 #pragma unroll
@@ -310,7 +332,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     team_sync(team);
                     if (leader) {
-                        if (n0 + c < N) {
+                        // (key and value columns of a scattering q|k|v product were written by the rows themselves;
+                        // the query width is a multiple of the 64-column group, so a group is all one or the other)
+                        if (n0 + c < N && !(sizeof(TOut) == 2 && kv.k_pool && n0 + c >= kv.q_width)) {
                             if (accumulate) tma_reduce_add_2d(&map_out, stage_buf, n0 + c, m0);
                             else tma_store_2d(&map_out, stage_buf, n0 + c, m0);
                         }
@@ -471,7 +495,8 @@ static int sm_count() {
 
 template <int BN, typename TOut, bool TMA_OUT>
 int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_out, const float* bias,
-                  void* out, int ldo, int M, int N, int K, int act, int accumulate, int* status, cudaStream_t stream) {
+                  void* out, int ldo, int M, int N, int K, int act, int accumulate, int* status, const KvScatter& kv,
+                  cudaStream_t stream) {
     auto kernel = gemm_tc_kernel<BN, TOut, TMA_OUT>;
     static bool raised = false;
     if (!raised) {
@@ -483,26 +508,27 @@ int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUte
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     return launch_pdl(kernel, dim3(grid), dim3(THREADS), Config<BN>::SMEM, stream, map_a, map_w, map_out, bias,
-                      (TOut*)out, ldo, M, N, K, act, accumulate, status);
+                      (TOut*)out, ldo, M, N, K, act, accumulate, status, kv);
 }
 
 template <int BN, typename TOut>
 int launch(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
-           int act, int accumulate, int* status, cudaStream_t stream) {
+           int act, int accumulate, int* status, const KvScatter& kv, cudaStream_t stream) {
     CUtensorMap map_a, map_w, map_out;
     if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_w, W, N, K, ldw, BN)) return PS_ERR_LAUNCH;
     // TMA can write the output when its rows start on 16-byte boundaries
     const bool tma_out = (((uintptr_t)out & 15) == 0) && (((size_t)ldo * sizeof(TOut)) % 16 == 0) &&
                          make_out_map(&map_out, out, M, N, ldo, (int)sizeof(TOut));
     if (tma_out)
-        return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+        return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+    if (kv.k_pool) return PS_ERR_UNSUPPORTED;      // the cache write lives in the TMA-store epilogue only
     map_out = map_a;    // unused
-    return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
 }
 
 template <typename TOut>
 int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
-         int act, int accumulate, int* status, int bn, cudaStream_t stream) {
+         int act, int accumulate, int* status, int bn, const KvScatter& kv, cudaStream_t stream) {
     if (bn == 0) {
         const int tiles_m = (M + BM - 1) / BM;
         // widest tile that still gives the SMs enough tiles (measured on B200: 128 wide wins until the
@@ -516,12 +542,12 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
         else if (2 * t128 >= sm_count()) bn = 128;
         else bn = 64;
     }
-    if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
-    if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+    if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
     if constexpr (sizeof(TOut) == 4) {      // 96 columns are three 32-column groups of float32; bfloat16 groups are 64 wide
-        if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+        if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
     }
-    if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, stream);
+    if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
     return PS_ERR_BAD_ARGUMENT;
 }
 
@@ -530,8 +556,9 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
 
 // status: device int32 that a bounded wait sets when it runs out (must not be null).
 // bn: 0 = choose, else 64, 128 or 256 (the N extent of the MMA tile).
-PS_EXPORT int ps_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
-                         int N, int K, int out_dtype, int act, int accumulate, int* status, int bn, void* stream) {
+static int gemm_tc_entry(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
+                         int N, int K, int out_dtype, int act, int accumulate, int* status, int bn,
+                         const ps::KvScatter& kv, void* stream) {
     if (M <= 0 || N <= 0) return PS_OK;
     if (!status) return PS_ERR_BAD_ARGUMENT;
     // TMA: 16-byte aligned base, row stride a multiple of 16 bytes
@@ -540,9 +567,33 @@ PS_EXPORT int ps_gemm_tc(const void* A, int lda, const void* W, int ldw, const f
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return PS_ERR_UNSUPPORTED;
     if (accumulate && out_dtype != PS_F32) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == PS_F32)
-        return ps::tc::pick<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, s);
+    if (out_dtype == PS_F32) {
+        if (kv.k_pool) return PS_ERR_UNSUPPORTED;
+        return ps::tc::pick<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s);
+    }
     if (out_dtype == PS_BF16)
-        return ps::tc::pick<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, s);
+        return ps::tc::pick<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s);
     return PS_ERR_UNSUPPORTED;
+}
+
+PS_EXPORT int ps_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
+                         int N, int K, int out_dtype, int act, int accumulate, int* status, int bn, void* stream) {
+    ps::KvScatter none = {};
+    return gemm_tc_entry(A, lda, W, ldw, bias, out, ldo, M, N, K, out_dtype, act, accumulate, status, bn, none, stream);
+}
+
+// The packed q|k|v projection of a step with prompt portions: columns [0, q_width) go to `out` (bfloat16), the
+// key and value columns (kv_width each) go straight into the pages of each row's request. q_width must be a
+// multiple of 64 and head_dim of 8; `out` rows must start on 16-byte boundaries.
+PS_EXPORT int ps_gemm_tc_qkv(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo,
+                             int M, int N, int K, int* status, void* k_pool, void* v_pool, long long page_stride,
+                             const int* token_item, const int* positions, const int* block_table, int bt_stride,
+                             int q_width, int kv_width, int head_dim, int page_size, void* stream) {
+    if (!k_pool || !v_pool || !token_item || !positions || !block_table) return PS_ERR_BAD_ARGUMENT;
+    if (q_width + 2 * kv_width != N || q_width % 64 != 0 || head_dim <= 0 || head_dim % 8 != 0 ||
+        kv_width % head_dim != 0 || page_size <= 0)
+        return PS_ERR_UNSUPPORTED;
+    ps::KvScatter kv{(__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride, token_item, positions, block_table,
+                     bt_stride, q_width, kv_width, head_dim, page_size};
+    return gemm_tc_entry(A, lda, W, ldw, bias, out, ldo, M, N, K, PS_BF16, PS_ACT_NONE, 0, status, 0, kv, stream);
 }

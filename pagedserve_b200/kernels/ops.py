@@ -94,6 +94,7 @@ _SIGNATURES = {
     },
     "tc": {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+        "ps_gemm_tc_qkv": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                     _I, _F, _I, _P, _P],
     },
@@ -330,11 +331,40 @@ class Ops:
     def linear_qkv(self, a, w, bias, out, ctx, layer, q_width, kv_width, head_dim, scatter=True):
         """The packed q|k|v projection.  Returns True when the key and value columns were written into
         the pages by the product's own epilogue (then no separate cache write is needed)."""
-        if scatter and hasattr(a, "materialize") and self._fused_norm_ok(a, w) and layer.k_pool is not None:
-            self.linear_skinny_fused(a, w, bias, out, kv=(ctx, layer, q_width, kv_width, head_dim))
-            return True
+        if scatter and layer.k_pool is not None and self.dtype == torch.bfloat16:
+            if hasattr(a, "materialize") and self._fused_norm_ok(a, w):
+                self.linear_skinny_fused(a, w, bias, out, kv=(ctx, layer, q_width, kv_width, head_dim))
+                return True
+            if hasattr(a, "materialize"):
+                a = a.materialize()
+            # many rows: the tcgen05 product, whose TMA-store epilogue sends the key and value columns to the pages
+            if (not self.skinny_ok(a, w) and self.tc_ok(a, w) and q_width % 64 == 0 and head_dim % 8 == 0
+                    and out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 and out.dtype == torch.bfloat16):
+                self.linear_tc_qkv(a, w, bias, out, ctx, layer, q_width, kv_width, head_dim)
+                return True
         self.linear(a, w, bias, out)
         return False
+
+    def linear_tc_qkv(self, a, w, bias, out, ctx, layer, q_width, kv_width, head_dim):
+        """tcgen05 q|k|v projection: query columns to ``out``, key and value columns into the pages."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError("linear_tc_qkv: shapes do not match")
+        _require(a, "a", torch.bfloat16)
+        _require(w, "w", torch.bfloat16)
+        _require(out, "out", torch.bfloat16)
+        if self._tc is None:
+            self._tc = _declare(_load_library("tc"), "tc")
+        if self._tc_status is None:
+            self._tc_status = torch.zeros(1, dtype=torch.int32, device=a.device)
+        self.launches += 1
+        _check(self._tc.ps_gemm_tc_qkv(
+            _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
+            _ptr(self._tc_status), _ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride,
+            _ptr(ctx.token_item), _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
+            q_width, kv_width, head_dim, layer.page_size, _stream()), "gemm_tc_qkv")
+        return out
 
     def linear(self, a, w, bias, out, act=None, accumulate=False):
         """The matrix product of the model: float32 runs on FFMA, bfloat16 on tensor cores.
