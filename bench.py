@@ -125,6 +125,9 @@ def main():
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--small", action="store_true", help="profiling aid: only the default decode measurement")
     parser.add_argument("--prefill-only", action="store_true", help="profiling aid: only the prefill measurement")
+    parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
+                        help="instead of the decode measurement: this many requests (prompts U[64,1024), outputs "
+                             "U[32,256]) through the scheduler, chunked prefill under a 2,048-token budget")
     args = parser.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -151,8 +154,8 @@ def main():
         sizes["n_layer"] = args.layers
     config = GPT2Config(**sizes)
     context_len = config.n_positions
-    if args.prompt_len + warmup + steps + 1 > context_len:
-        steps = context_len - args.prompt_len - warmup - 1
+    if args.prompt_len + warmup + steps + 2 > context_len:
+        steps = context_len - args.prompt_len - warmup - 2
     peaks = load_peaks()
 
     max_batch = max(64, args.batch)
@@ -267,8 +270,43 @@ def main():
         return {"value": T / (ms / 1e3), "tokens": T, "ms": ms, "frac": flops / (ms / 1e3) / peak,
                 "gflop": flops / 1e9}
 
+    def measure_serving(requests, max_seqs=64):
+        """Continuous batching: every request is queued at time 0; a step holds the decode tokens of the running
+        requests and prompt portions of waiting ones under the token budget.  The second of two passes is
+        reported (the first one meets the step shapes for the first time)."""
+        for _ in range(2):
+            scheduler = engine.make_scheduler(strategy="sarathi", max_num_seqs=max_seqs, max_num_batched_tokens=2048,
+                                              prefill_chunk_size=512, max_prefills_per_step=4)
+            prompt_tokens = 0
+            for _ in range(requests):
+                prompt_len = int(rng.integers(64, 1024))
+                output_len = max(1, min(int(rng.integers(32, 257)), context_len - prompt_len))
+                scheduler.add_token_request(rng.integers(0, config.vocab_size, prompt_len).tolist(),
+                                            max_new_tokens=output_len)
+                prompt_tokens += prompt_len
+            step_ms, produced = [], 0
+            torch.cuda.synchronize()
+            began = time.perf_counter()
+            while scheduler.waiting or scheduler.active:
+                before = time.perf_counter()
+                produced += len(scheduler.step())
+                step_ms.append((time.perf_counter() - before) * 1e3)
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - began
+            engine.cache.check_invariants()
+        step_ms.sort()
+        return {"impl": "ours", "workload": "continuous batching", "model": args.model, "dtype": args.dtype,
+                "requests": requests, "max_num_seqs": max_seqs, "max_num_batched_tokens": 2048,
+                "prompt_tokens": prompt_tokens, "output_tokens": produced, "seconds": seconds,
+                "output_tok_s": produced / seconds, "total_tok_s": (prompt_tokens + produced) / seconds,
+                "steps": len(step_ms), "step_ms_median": step_ms[len(step_ms) // 2],
+                "step_ms_p90": step_ms[int(len(step_ms) * 0.9)], "step_ms_max": step_ms[-1]}
+
     if args.prefill_only:
         print(json.dumps({"impl": "ours", "prefill": measure_prefill(repeats=3)}))
+        return 0
+    if args.serving:
+        print(json.dumps(measure_serving(args.serving)))
         return 0
     main_run = measure_decode(args.batch, steps)
     e2e = measure_e2e(args.batch, steps)

@@ -38,6 +38,116 @@ class StepEntry:
                 raise ValueError(f"wanted place {place} is outside the entry's {len(self.tokens)} tokens")
 
 
+def layout_order(counts: np.ndarray, long_entry: int):
+    """The order in which a step's entries are laid out: short entries (decode tokens, short portions)
+    first, prompt portions of ``long_entry`` or more tokens after them, each kind in the caller's order.
+    Returns (source index of each laid-out item, number of short items)."""
+    is_long = np.asarray(counts) >= long_entry
+    order = np.concatenate([np.flatnonzero(~is_long), np.flatnonzero(is_long)])
+    return order, len(order) - int(is_long.sum())
+
+
+def _round_up(value: int, step: int) -> int:
+    return -(-value // step) * step
+
+
+@dataclass
+class Arrangement:
+    """The flat batch of one step as host arrays (int64), before it is packed for the device."""
+
+    token_ids: np.ndarray         # [T]
+    positions: np.ndarray         # [T]
+    token_item: np.ndarray        # [T]
+    item_slot: np.ndarray         # [I]
+    q_start: np.ndarray           # [I + 1]
+    kv_len: np.ndarray            # [I]
+    logit_rows: np.ndarray        # [R]
+    num_short_items: int
+    num_short_tokens: int
+    num_long_blocks: int
+    real_rows: int                # rows of logits that the caller asked for (the rest is padding)
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.token_ids)
+
+    @property
+    def num_items(self) -> int:
+        return len(self.item_slot)
+
+    @property
+    def num_rows(self) -> int:
+        return len(self.logit_rows)
+
+
+def arrange_step(order: np.ndarray, num_short_items: int, counts: np.ndarray, tokens: np.ndarray,
+                 slots: np.ndarray, starts: np.ndarray, wants: Sequence[Sequence[int]], *,
+                 pad: bool = False, pad_short: int = 16, pad_long: int = 128, scratch_slot: int = -1) -> Arrangement:
+    """Lay a step out as one flat batch.
+
+    ``order``/``num_short_items`` come from :func:`layout_order`; ``counts`` and ``wants`` are in the caller's
+    order; ``tokens`` (all tokens), ``slots`` and ``starts`` (cached length of each request before the step) are
+    in layout order.  With ``pad`` the batch is brought to a recurring shape: the short tokens to a multiple of
+    ``pad_short`` and the long ones to a multiple of ``pad_long`` by one padding entry behind each kind (at
+    positions 0.. of ``scratch_slot``), the items to multiples of 8 and 4 by empty entries of that slot, and
+    the logits rows to a multiple of 8 by repeating the first row.
+    """
+    counts = np.asarray(counts, dtype=np.int64)
+    real_items = len(order)
+    laid_counts = counts[order]
+    num_long_items = real_items - num_short_items
+    short_tokens = int(laid_counts[:num_short_items].sum())
+    long_tokens = int(laid_counts.sum()) - short_tokens
+    real_rows = sum(len(want) for want in wants)
+    num_rows = real_rows
+    if pad:
+        extra_short = _round_up(short_tokens, pad_short) - short_tokens
+        extra_long = _round_up(long_tokens, pad_long) - long_tokens
+        short_items = _round_up(num_short_items + (extra_short > 0), 8) if short_tokens else 0
+        long_items = _round_up(num_long_items + (extra_long > 0), 4) if long_tokens else 0
+
+        def with_padding(real, extra, total, fill):
+            """``real`` values, then the padding entry's value if it exists, then ``fill`` up to ``total``."""
+            head = [real, np.full(1, extra, dtype=np.int64)] if extra is not None else [real]
+            used = sum(len(piece) for piece in head)
+            return np.concatenate(head + [np.full(total - used, fill, dtype=np.int64)])
+
+        pad_count = lambda extra: extra if extra else None
+        laid_counts = np.concatenate([
+            with_padding(laid_counts[:num_short_items], pad_count(extra_short), short_items, 0),
+            with_padding(laid_counts[num_short_items:], pad_count(extra_long), long_items, 0)])
+        slots = np.concatenate([with_padding(slots[:num_short_items], None, short_items, scratch_slot),
+                                with_padding(slots[num_short_items:], None, long_items, scratch_slot)])
+        starts = np.concatenate([with_padding(starts[:num_short_items], None, short_items, 0),
+                                 with_padding(starts[num_short_items:], None, long_items, 0)])
+        tokens = np.concatenate([tokens[:short_tokens], np.zeros(extra_short, dtype=np.int64),
+                                 tokens[short_tokens:], np.zeros(extra_long, dtype=np.int64)])
+        # where the real entries went
+        new_index = np.concatenate([np.arange(num_short_items), short_items + np.arange(num_long_items)])
+        num_short_items = short_items
+        num_rows = _round_up(real_rows, 8)
+    else:
+        new_index = np.arange(real_items)
+    num_items = len(laid_counts)
+    num_tokens = len(tokens)
+
+    first = np.zeros(num_items + 1, dtype=np.int64)
+    np.cumsum(laid_counts, out=first[1:])                              # first token of each laid-out item
+    item_of_token = np.repeat(np.arange(num_items, dtype=np.int64), laid_counts)
+    positions = np.arange(num_tokens, dtype=np.int64) + (starts - first[:-1])[item_of_token]
+    if pad:                                                            # a bound that depends on the padded shape alone
+        num_long_blocks = int(laid_counts[num_short_items:].sum()) // 64 + (num_items - num_short_items)
+    else:
+        num_long_blocks = int((-(-laid_counts[num_short_items:] // 64)).sum())
+    first_of_source = np.empty(real_items, dtype=np.int64)
+    first_of_source[order] = first[new_index]
+    rows = [int(first_of_source[source]) + place for source, want in enumerate(wants) for place in want]
+    rows += [rows[0] if rows else 0] * (num_rows - real_rows)          # logits rows keep the caller's order
+    return Arrangement(np.asarray(tokens, dtype=np.int64), positions, item_of_token, np.asarray(slots, dtype=np.int64),
+                       first, starts + laid_counts, np.asarray(rows, dtype=np.int64), num_short_items,
+                       int(first[num_short_items]), num_long_blocks, real_rows)
+
+
 def _pad4(n: int) -> int:
     return (n + 3) & ~3
 

@@ -16,7 +16,8 @@ import numpy as np
 import torch
 
 from pagedserve_b200.cache.manager import CacheFull, CacheManager
-from pagedserve_b200.engine.batch import BatchLayout, DeviceViews, HostBatch, StepContext, StepEntry
+from pagedserve_b200.engine.batch import (BatchLayout, DeviceViews, HostBatch, StepContext, StepEntry, arrange_step,
+                                           layout_order)
 
 
 class StepError(ValueError):
@@ -126,10 +127,7 @@ class ModelRunner:
         if len(set(requests)) != I:
             raise StepError("a request can appear only once in a step")       # reference: iteration.py:62-63
         counts = np.fromiter((len(entry.tokens) for entry in entries), dtype=np.int64, count=I)
-        # layout order: short entries (decode tokens, short portions) first, prompt portions after them
-        is_long = counts >= StepContext.LONG_ENTRY
-        order = np.concatenate([np.flatnonzero(~is_long), np.flatnonzero(is_long)])
-        num_short_items = I - int(is_long.sum())
+        order, num_short_items = layout_order(counts, StepContext.LONG_ENTRY)
         tokens = np.concatenate([entries[source].tokens for source in order])
         self._check_vocabulary(tokens)
 
@@ -154,86 +152,39 @@ class ModelRunner:
             raise
         self._admitted_in_step = admitted
 
-        T = int(counts.sum())
-        R = sum(len(entry.want) for entry in entries)
         slot_of = cache.slot_of
         slots = np.fromiter((slot_of[requests[source]] for source in order), dtype=np.int64, count=I)
-        laid_counts = counts[order]
         starts = cache.lengths[slots].astype(np.int64)                 # cached length of each laid-out item
-        num_long_items = I - num_short_items
-        short_tokens = int(laid_counts[:num_short_items].sum())
-        long_tokens = T - short_tokens
-        real_items, real_rows = I, R
-        if pad:
-            # one padding entry behind the short entries and one behind the long ones take the padding tokens
-            # (positions 0.. of the scratch slot); further entries are empty
-            up = lambda value, step: -(-value // step) * step
-            pad_short = up(short_tokens, self.PAD_SHORT) - short_tokens
-            pad_long = up(long_tokens, self.PAD_LONG) - long_tokens
-            short_items = up(num_short_items + (pad_short > 0), 8) if short_tokens else 0
-            long_items = up(num_long_items + (pad_long > 0), 4) if long_tokens else 0
-            scratch = cache.scratch_slot
-            pieces = lambda real, extra, total: np.concatenate(
-                [real, np.full(1 if extra else 0, extra, dtype=np.int64),
-                 np.zeros(total - len(real) - (1 if extra else 0), dtype=np.int64)])
-            laid_counts = np.concatenate([pieces(laid_counts[:num_short_items], pad_short, short_items),
-                                          pieces(laid_counts[num_short_items:], pad_long, long_items)])
-            fill = lambda real, total: np.concatenate([real, np.full(total - len(real), scratch, dtype=np.int64)])
-            slots = np.concatenate([fill(slots[:num_short_items], short_items),
-                                    fill(slots[num_short_items:], long_items)])
-            zeros = lambda real, total: np.concatenate([real, np.zeros(total - len(real), dtype=np.int64)])
-            starts = np.concatenate([zeros(starts[:num_short_items], short_items),
-                                     zeros(starts[num_short_items:], long_items)])
-            tokens = np.concatenate([tokens[:short_tokens], np.zeros(pad_short, dtype=np.int64),
-                                     tokens[short_tokens:], np.zeros(pad_long, dtype=np.int64)])
-            # where the real entries went: item index and first token of each source entry
-            new_index = np.concatenate([np.arange(num_short_items),
-                                        short_items + np.arange(num_long_items)])
-            num_short_items, I = short_items, short_items + long_items
-            T = short_tokens + pad_short + long_tokens + pad_long
-            R = up(R, 8)
-        else:
-            new_index = np.arange(I)
+        batch = arrange_step(order, num_short_items, counts, tokens, slots, starts,
+                             [entry.want for entry in entries], pad=pad, pad_short=self.PAD_SHORT,
+                             pad_long=self.PAD_LONG, scratch_slot=cache.scratch_slot)
+        T, I, R = batch.num_tokens, batch.num_items, batch.num_rows
         layout, views, staging, host = self._stage(T, I, R)
-        token_ids = host[layout.token_ids:layout.token_ids + T]
-        positions = host[layout.positions:layout.positions + T]
-        token_item = host[layout.token_item:layout.token_item + T]
-        item_slot = host[layout.item_slot:layout.item_slot + I]
-        q_start = host[layout.q_start:layout.q_start + I + 1]
-        kv_len = host[layout.kv_len:layout.kv_len + I]
-        logit_rows = host[layout.logit_rows:layout.logit_rows + R]
 
-        # whole-array fills, in layout order
-        first = np.zeros(I + 1, dtype=np.int64)
-        np.cumsum(laid_counts, out=first[1:])                          # first token of each laid-out item
-        token_ids[:] = tokens
-        item_of_token = np.repeat(np.arange(I, dtype=np.int64), laid_counts)
-        token_item[:] = item_of_token
-        positions[:] = np.arange(T, dtype=np.int64) + (starts - first[:-1])[item_of_token]
-        item_slot[:] = slots
-        q_start[:] = first
-        kv_len[:] = starts + laid_counts
-        num_short_tokens = int(first[num_short_items])
-        if pad:                                                        # a bound that depends on the padded shape alone
-            num_long_blocks = int(laid_counts[num_short_items:].sum()) // 64 + (I - num_short_items)
-        else:
-            num_long_blocks = int((-(-laid_counts[num_short_items:] // 64)).sum())
-        first_of_source = np.empty(real_items, dtype=np.int64)
-        first_of_source[order] = first[new_index]
-        if R:                                                          # logits rows keep the caller's order
-            rows = [int(first_of_source[source]) + place
-                    for source, entry in enumerate(entries) for place in entry.want]
-            logit_rows[:] = rows + [rows[0] if rows else 0] * (R - real_rows)
+        def section(offset, values):
+            view = host[offset:offset + len(values)]
+            view[:] = values
+            return view
+
+        token_ids = section(layout.token_ids, batch.token_ids)
+        positions = section(layout.positions, batch.positions)
+        token_item = section(layout.token_item, batch.token_item)
+        item_slot = section(layout.item_slot, batch.item_slot)
+        q_start = section(layout.q_start, batch.q_start)
+        kv_len = section(layout.kv_len, batch.kv_len)
+        logit_rows = section(layout.logit_rows, batch.logit_rows)
         for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
-            cache.table_rows(group_index, slots, host[offset:offset + I * width].reshape(I, width))
+            cache.table_rows(group_index, batch.item_slot, host[offset:offset + I * width].reshape(I, width))
 
         host[layout.counter] = 0
         self._upload(layout, staging)
         host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
                                [requests[source] for source in order])
+        laid_counts = np.diff(batch.q_start)
         ctx = StepContext(layout, self._device_buffer, host_batch, cache, self._status, int(laid_counts.max()),
-                          int(kv_len.max()), num_short_items, num_short_tokens, num_long_blocks, views=views)
-        ctx.real_logit_rows = real_rows
+                          int(batch.kv_len.max()), batch.num_short_items, batch.num_short_tokens,
+                          batch.num_long_blocks, views=views)
+        ctx.real_logit_rows = batch.real_rows
         return ctx
 
     def _stage(self, T: int, I: int, R: int):

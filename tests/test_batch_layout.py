@@ -1,0 +1,141 @@
+"""The flat layout of a step (host arithmetic only): order, positions, wanted rows, padding."""
+
+import numpy as np
+import pytest
+
+from pagedserve_b200.engine.batch import BatchLayout, StepContext, StepEntry, arrange_step, layout_order
+
+LONG = StepContext.LONG_ENTRY
+SCRATCH = 99
+
+
+def random_step(rng, items, longest):
+    """Entries with random counts (many single tokens, some portions), distinct slots, random cached lengths."""
+    entries, slots, starts = [], [], []
+    for index in range(items):
+        kind = rng.integers(0, 3)
+        count = 1 if kind == 0 else int(rng.integers(2, LONG)) if kind == 1 else int(rng.integers(LONG, longest + 1))
+        tokens = rng.integers(0, 1000, size=count)
+        want = sorted(set(int(place) for place in rng.integers(0, count, size=rng.integers(0, 3))))
+        entries.append(StepEntry(f"r{index}", tokens, want))
+        slots.append(index)
+        starts.append(int(rng.integers(0, 500)))
+    return entries, np.asarray(slots), np.asarray(starts)
+
+
+def arrange(entries, slots, starts, **options):
+    counts = np.asarray([len(entry.tokens) for entry in entries])
+    order, num_short = layout_order(counts, LONG)
+    tokens = np.concatenate([entries[source].tokens for source in order])
+    batch = arrange_step(order, num_short, counts, tokens, slots[order], starts[order],
+                         [entry.want for entry in entries], scratch_slot=SCRATCH, **options)
+    return order, batch
+
+
+def check_real_entries(entries, slots, starts, order, batch, item_of_source):
+    for source, entry in enumerate(entries):
+        item = item_of_source[source]
+        first, last = int(batch.q_start[item]), int(batch.q_start[item + 1])
+        count = len(entry.tokens)
+        assert last - first == count
+        assert np.array_equal(batch.token_ids[first:last], entry.tokens)
+        assert np.array_equal(batch.positions[first:last], starts[source] + np.arange(count))
+        assert np.all(batch.token_item[first:last] == item)
+        assert batch.item_slot[item] == slots[source]
+        assert batch.kv_len[item] == starts[source] + count
+        assert (item < batch.num_short_items) == (count < LONG)
+    # rows of logits in the caller's order
+    expected = [int(batch.q_start[item_of_source[source]]) + place
+                for source, entry in enumerate(entries) for place in entry.want]
+    assert batch.logit_rows[:batch.real_rows].tolist() == expected
+    assert batch.real_rows == len(expected)
+
+
+def test_layout_order_keeps_the_callers_order_within_a_kind():
+    order, num_short = layout_order(np.asarray([40, 1, 16, 15, 1, 100]), 16)
+    assert order.tolist() == [1, 3, 4, 0, 2, 5]
+    assert num_short == 3
+
+
+@pytest.mark.parametrize("seed", range(20))
+def test_unpadded_arrangement(seed):
+    rng = np.random.default_rng(seed)
+    entries, slots, starts = random_step(rng, int(rng.integers(1, 12)), 200)
+    order, batch = arrange(entries, slots, starts)
+    assert batch.num_items == len(entries)
+    assert batch.num_tokens == sum(len(entry.tokens) for entry in entries)
+    assert batch.num_rows == batch.real_rows
+    item_of_source = np.empty(len(entries), dtype=np.int64)
+    item_of_source[order] = np.arange(len(entries))
+    check_real_entries(entries, slots, starts, order, batch, item_of_source)
+    long_counts = np.diff(batch.q_start)[batch.num_short_items:]
+    assert batch.num_long_blocks == int(sum(-(-count // 64) for count in long_counts))
+    assert batch.num_short_tokens == int(batch.q_start[batch.num_short_items])
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_padded_arrangement(seed):
+    rng = np.random.default_rng(100 + seed)
+    entries, slots, starts = random_step(rng, int(rng.integers(1, 12)), 300)
+    pad_short, pad_long = 16, 128
+    order, batch = arrange(entries, slots, starts, pad=True, pad_short=pad_short, pad_long=pad_long)
+    counts = np.diff(batch.q_start)
+    short_tokens = batch.num_short_tokens
+    long_tokens = batch.num_tokens - short_tokens
+    assert short_tokens % pad_short == 0 and long_tokens % pad_long == 0
+    assert batch.num_short_items % 8 == 0 and (batch.num_items - batch.num_short_items) % 4 == 0
+    assert batch.num_rows % 8 == 0 and batch.num_rows - batch.real_rows < 8
+
+    num_short_real = sum(len(entry.tokens) < LONG for entry in entries)
+    num_long_real = len(entries) - num_short_real
+    item_of_source = np.empty(len(entries), dtype=np.int64)
+    item_of_source[order] = np.concatenate([np.arange(num_short_real),
+                                            batch.num_short_items + np.arange(num_long_real)])
+    check_real_entries(entries, slots, starts, order, batch, item_of_source)
+
+    # everything else is padding: the scratch slot from position 0, at most one entry with tokens per kind
+    real = set(item_of_source.tolist())
+    padding = [item for item in range(batch.num_items) if item not in real]
+    for kind in (range(0, batch.num_short_items), range(batch.num_short_items, batch.num_items)):
+        with_tokens = [item for item in kind if item in padding and counts[item] > 0]
+        assert len(with_tokens) <= 1
+    for item in padding:
+        assert batch.item_slot[item] == SCRATCH
+        first, last = int(batch.q_start[item]), int(batch.q_start[item + 1])
+        assert np.array_equal(batch.positions[first:last], np.arange(last - first))
+        assert np.all(batch.token_ids[first:last] == 0)
+        assert batch.kv_len[item] == last - first < max(pad_short, pad_long)
+        if item < batch.num_short_items:
+            assert last - first < LONG
+    # padded rows repeat a real row; the bound on 64-query blocks covers every long item
+    if batch.real_rows:
+        assert np.all(batch.logit_rows[batch.real_rows:] == batch.logit_rows[0])
+    assert batch.num_long_blocks >= int(sum(-(-count // 64) for count in counts[batch.num_short_items:]))
+
+
+def test_padded_shape_depends_on_rounded_sizes_only():
+    """Two steps whose sizes round to the same numbers get the same shape and the same block bound."""
+    def shape(counts):
+        entries = [StepEntry(index, np.zeros(count, dtype=np.int64), [count - 1]) for index, count in enumerate(counts)]
+        slots = np.arange(len(counts))
+        _, batch = arrange(entries, slots, np.zeros(len(counts), dtype=np.int64), pad=True)
+        return (batch.num_tokens, batch.num_items, batch.num_rows, batch.num_short_items, batch.num_short_tokens,
+                batch.num_long_blocks)
+
+    assert shape([1, 1, 1, 100]) == shape([1, 1, 1, 1, 1, 120]) == shape([1, 2, 3, 64, 40])
+    assert shape([1] * 16) == (16, 16, 16, 16, 16, 0)            # already a recurring shape: nothing is added
+    assert shape([128]) == (128, 4, 8, 0, 0, 128 // 64 + 4)
+
+
+def test_packed_sections_do_not_overlap_and_are_aligned():
+    layout = BatchLayout(37, 5, 3, [7, 11])
+    names = ["token_ids", "positions", "token_item", "item_slot", "q_start", "kv_len", "logit_rows", "temperature",
+             "seed", "counter"]
+    sizes = [37, 37, 37, 5, 6, 5, 3, 5, 10, 1]
+    spans = [(getattr(layout, name), getattr(layout, name) + size) for name, size in zip(names, sizes)]
+    spans += [(offset, offset + 5 * width) for offset, width in zip(layout.tables, layout.table_widths)]
+    spans.sort()
+    for (start, end), (next_start, _) in zip(spans, spans[1:]):
+        assert end <= next_start
+    assert all(start % 4 == 0 for start, _ in spans)             # 16-byte sections: vector loads are legal
+    assert spans[-1][1] <= layout.total
