@@ -36,8 +36,9 @@ template <int MT, int WARPS, int UNROLL, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, int ldw,
                    const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K,
-                   int act, int accumulate) {
-    extern __shared__ float red[];                 // [WARPS][16][8*MT]
+                   int act, int accumulate, KvScatter kv) {
+    // cross-warp sums [WARPS][16][8*MT] floats, then the cache address of each row [8*MT] (64-bit)
+    extern __shared__ __align__(16) float red[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -61,9 +62,18 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     // what the output holds (to be added to) is fetched right after the wait, long before the epilogue needs it
     constexpr int TOK = 8 * MT;
     constexpr int EPT = (16 * TOK + WARPS * 32 - 1) / (WARPS * 32);      // epilogue elements per thread
+    long long* dst_s = reinterpret_cast<long long*>(red + (size_t)WARPS * 16 * TOK);
     float prev[EPT];
     auto after_wait = [&]() {
         pdl_prologue();
+        if (kv.k_pool) {
+            // where a row's keys and values go: offset of (page, head 0, position in page, 0), or -1
+            for (int m = threadIdx.x; m < M; m += WARPS * 32) {
+                const int p = kv.positions[m];
+                const int page = kv.block_table[(size_t)kv.token_item[m] * kv.bt_stride + p / kv.page_size];
+                dst_s[m] = page >= 0 ? (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim : -1;
+            }
+        }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) arow[mt] = pdl_fresh(arow[mt]);
 #pragma unroll
@@ -128,6 +138,15 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * 16 * TOK + r * TOK + m];
         if (bias) v += bias[n];
         v = apply_act(v, act);
+        if (kv.k_pool && n >= kv.q_width) {        // a key or value column: into the row's page
+            int c = n - kv.q_width;
+            __nv_bfloat16* pool = kv.k_pool;
+            if (c >= kv.kv_width) { c -= kv.kv_width; pool = kv.v_pool; }
+            int head = c / kv.head_dim, d = c - head * kv.head_dim;
+            const long long base = dst_s[m];
+            if (base >= 0) pool[base + (long long)head * kv.page_size * kv.head_dim + d] = __float2bfloat16_rn(v);
+            continue;
+        }
         v += prev[j];
         out[(size_t)m * ldo + n] = from_float<TOut>(v);
     }
@@ -135,8 +154,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
 
 template <int MT, int WARPS, int UNROLL, typename TOut>
 int launch_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo,
-                  int M, int N, int K, int act, int accumulate, cudaStream_t s) {
-    size_t smem = (size_t)WARPS * 16 * 8 * MT * sizeof(float);
+                  int M, int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+    size_t smem = (size_t)WARPS * 16 * 8 * MT * sizeof(float) + (size_t)8 * MT * sizeof(long long);
     auto kernel = gemm_skinny_kernel<MT, WARPS, UNROLL, TOut>;
     if (smem > 48 * 1024) {
         static bool raised = false;
@@ -147,38 +166,50 @@ int launch_skinny(const void* A, int lda, const void* W, int ldw, const float* b
         }
     }
     return launch_pdl(kernel, dim3((N + 15) / 16), dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)A, lda,
-                      (const __nv_bfloat16*)W, ldw, bias, (TOut*)out, ldo, M, N, K, act, accumulate);
+                      (const __nv_bfloat16*)W, ldw, bias, (TOut*)out, ldo, M, N, K, act, accumulate, kv);
 }
 
 template <int MT, typename TOut>
 int pick_warps(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
-               int N, int K, int act, int accumulate, cudaStream_t s) {
+               int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
     // warps and steps per round such that the k steps of a warp are one round of loads where that is possible
     // (K up to 4,096, at most 8 rows); more token tiles keep the rounds short, their accumulators need the
     // registers
     const int steps = (K + 31) / 32;
 #define PS_SKINNY(W_, U_) \
-    return launch_skinny<MT, W_, U_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s)
-    if (MT >= 2) {
+    return launch_skinny<MT, W_, U_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s)
+    if constexpr (MT >= 2) {
         if (steps <= 32) PS_SKINNY(4, 6);
         if (steps <= 64) PS_SKINNY(8, 6);
         PS_SKINNY(16, 6);
+    } else {
+        if (steps <= 24) PS_SKINNY(4, 6);
+        if (steps <= 32) PS_SKINNY(8, 4);
+        if (steps <= 64) PS_SKINNY(8, 8);
+        if (steps <= 96) PS_SKINNY(16, 6);
+        PS_SKINNY(16, 8);
     }
-    if (steps <= 24) PS_SKINNY(4, 6);
-    if (steps <= 32) PS_SKINNY(8, 4);
-    if (steps <= 64) PS_SKINNY(8, 8);
-    if (steps <= 96) PS_SKINNY(16, 6);
-    PS_SKINNY(16, 8);
 #undef PS_SKINNY
 }
 
 template <typename TOut>
 int pick_tiles(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
-               int N, int K, int act, int accumulate, cudaStream_t s) {
-    if (M <= 8) return pick_warps<1, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
-    if (M <= 16) return pick_warps<2, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
-    if (M <= 32) return pick_warps<4, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
-    return pick_warps<8, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
+               int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+    // the MMAs of a CTA grow with the token tiles, and from 17 rows on they are what the kernel waits for:
+    // every count of tiles has its own instance
+#define PS_TILES(MT_) \
+    return pick_warps<MT_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s)
+    switch ((M + 7) / 8) {
+        case 1: PS_TILES(1);
+        case 2: PS_TILES(2);
+        case 3: PS_TILES(3);
+        case 4: PS_TILES(4);
+        case 5: PS_TILES(5);
+        case 6: PS_TILES(6);
+        case 7: PS_TILES(7);
+        default: PS_TILES(8);
+    }
+#undef PS_TILES
 }
 
 
@@ -359,13 +390,13 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             int k = (s0 + u * WARPS) << 5;
-            bool ok = (s0 + u * WARPS) < steps && (k + 8 * t) < K;
-            if (!ok) continue;
+            if ((s0 + u * WARPS) >= steps) continue;       // the same for the whole warp: the MMAs stay converged
+            const bool in_k = (k + 8 * t) < K;             // a lane past the end of K feeds zeros
             uint32_t a1[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
             uint32_t a2[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                uint4 x = aok[mt] ? *reinterpret_cast<const uint4*>(arow[mt] + k) : make_uint4(0, 0, 0, 0);
+                uint4 x = (in_k && aok[mt]) ? *reinterpret_cast<const uint4*>(arow[mt] + k) : make_uint4(0, 0, 0, 0);
                 uint32_t b1[2] = {x.x, x.y}, b2[2] = {x.z, x.w};
                 mma_bf16_16816(acc[mt], a1, b1);
                 mma_bf16_16816(acc[mt], a2, b2);
@@ -447,22 +478,31 @@ int pick_tiles_fused(const NormInput& in, const void* W, int ldw, const float* b
     return pick_warps_fused<4, TOut>(in, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
 }
 
+
 }  // namespace ps
 
+// An optional cache write of the key and value columns rides on the epilogue (kv_* arguments as for
+// ps_gemm_skinny_fused; k_pool null = none).
 PS_EXPORT int ps_gemm_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* out,
                              int ldo, int M, int N, int K, int out_dtype, int act, int accumulate,
-                             void* stream) {
+                             void* k_pool, void* v_pool, long long page_stride, const int* token_item,
+                             const int* positions, const int* block_table, int bt_stride, int q_width,
+                             int kv_width, int head_dim, int page_size, void* stream) {
     if (M <= 0 || N <= 0) return PS_OK;
     if (M > 64) return PS_ERR_UNSUPPORTED;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K || ldo < N)
         return PS_ERR_UNSUPPORTED;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return PS_ERR_UNSUPPORTED;
     if (accumulate && out_dtype != PS_F32) return PS_ERR_BAD_ARGUMENT;
+    if (k_pool && (q_width + 2 * kv_width != N || head_dim <= 0 || kv_width % head_dim != 0 || page_size <= 0))
+        return PS_ERR_BAD_ARGUMENT;
+    ps::KvScatter kv{(__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride, token_item, positions, block_table,
+                     bt_stride, q_width, kv_width, head_dim, page_size};
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == PS_F32)
-        return ps::pick_tiles<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
+        return ps::pick_tiles<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
     if (out_dtype == PS_BF16)
-        return ps::pick_tiles<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, s);
+        return ps::pick_tiles<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
     return PS_ERR_UNSUPPORTED;
 }
 

@@ -97,7 +97,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
 // move every request one position on, and append the tokens to the history of the run.
 __global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids,
                                int* __restrict__ positions, int* __restrict__ kv_len,
-                               int* __restrict__ history, int* __restrict__ step_counter, int B, int max_steps) {
+                               int* __restrict__ history, int* __restrict__ step_counter, int B, int max_steps,
+                               const int* status, int* status_copy) {
     pdl_prologue();
     sampled = pdl_fresh(sampled);
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -110,7 +111,11 @@ __global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict_
         if (step < max_steps) history[(size_t)step * B + i] = token;
     }
     __syncthreads();
-    if (i == 0) *step_counter = step + 1;
+    if (i == 0) {
+        *step_counter = step + 1;
+        // every kernel of the step has ended: what they flagged travels with the tokens
+        if (status && status_copy) *status_copy = *(volatile const int*)status;
+    }
 }
 
 }  // namespace ps
@@ -129,10 +134,12 @@ PS_EXPORT int ps_sample(const float* logits, int ld, int R, int V, const float* 
 }
 
 // One block: B <= 1024.
+// status_copy (may be null): where the step's status flag is copied to, e.g. host memory mapped for the device.
 PS_EXPORT int ps_advance(const int* sampled, int* token_ids, int* positions, int* kv_len, int* history,
-                         int* step_counter, int B, int max_steps, void* stream) {
+                         int* step_counter, int B, int max_steps, const int* status, int* status_copy,
+                         void* stream) {
     if (B <= 0) return PS_OK;
     if (B > 1024) return PS_ERR_UNSUPPORTED;
     return ps::launch_pdl(ps::advance_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, (cudaStream_t)stream, sampled,
-                          token_ids, positions, kv_len, history, step_counter, B, max_steps);
+                          token_ids, positions, kv_len, history, step_counter, B, max_steps, status, status_copy);
 }

@@ -125,6 +125,10 @@ class Engine:
     def finish(self, request: Hashable) -> None:
         self.runner.finish(request)
 
+    def check_status(self) -> None:
+        """Raise if a kernel of an earlier step flagged bad input or gave up a wait (synchronises)."""
+        self.runner.check_status()
+
     def sample(self, logits, temperatures, seeds, positions) -> List[int]:
         return self.sampler.sample(logits, temperatures, seeds, positions)
 

@@ -264,6 +264,9 @@ class Scheduler:
         """reference: src/scheduler/orca_scheduler.py:297-303 (token ids instead of decoded text)"""
         while self.waiting or self.active:
             self.step()
+        check = getattr(self.engine, "check_status", None)
+        if check is not None:
+            check()                   # a kernel that flagged something in a step without device sampling
         return {request_id: list(request.generated_token_ids) for request_id, request in self.finished.items()}
 
     run = run_until_complete

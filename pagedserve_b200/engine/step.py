@@ -75,7 +75,8 @@ class ModelRunner:
         self._staging = []
         self._staging_events = []
         self._turn = 0
-        self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.ops = model.env.ops
+        self._status = self.ops.status_flag(self.device)      # one flag for every kernel of the model's steps
         self._grow(BatchLayout(max_step_tokens, min(max_step_tokens, cache.max_slots),
                                min(max_step_tokens, 4 * cache.max_slots), self.table_widths).total)
         self.steps = 0
@@ -84,14 +85,16 @@ class ModelRunner:
         # padding needs the scratch slot's pages and positions 0 .. PAD_LONG - 1 to exist in the model
         self._pad_mixed = (self.enable_cuda_graphs and cache.scratch_tokens >= self.PAD_LONG
                            and self.max_model_len >= 2 * self.PAD_LONG)
-        self.ops = model.env.ops
         self._graphs = {}                 # (batch size, kind) or step shape -> _DecodeGraph
         self._shape_seen = {}             # step shape -> times seen (a shape is captured when it comes back)
         self.graph_replays = 0
         self._sampled = torch.zeros(cache.max_slots, dtype=torch.int32, device=self.device)
         # the sampled tokens of a run of decode steps: page-locked host memory that the token feedback kernel
         # writes directly (no device-to-host copy after the step)
-        self._history = self.ops.mapped_host_buffer(self.MAX_DEVICE_STEPS * cache.max_slots)
+        # (its last word is the copy of the status flag that the same kernel leaves there)
+        self._status_index = self.MAX_DEVICE_STEPS * cache.max_slots
+        self._history = self.ops.mapped_host_buffer(self._status_index + 1)
+        self._history.array[self._status_index] = 0
         self._shapes = {}                 # (T, I, R) -> (BatchLayout, DeviceViews)
         self._staged = None               # a decode step staged ahead of its tokens
         self._capture_stream = None       # made at the first capture
@@ -397,6 +400,8 @@ class ModelRunner:
         if stage_next and steps == 1:
             self._staged = self._stage_ahead(requests, temperatures, seeds)
         torch.cuda.current_stream().synchronize()          # the tokens are in host memory now
+        if self._history.array[self._status_index]:
+            self.check_status()
         return self._history.array[:steps * B].reshape(steps, B).copy()
 
     def _forward_and_sample(self, ctx: StepContext) -> torch.Tensor:
@@ -406,7 +411,7 @@ class ModelRunner:
         # the token drawn now will sit at position (input position + 1)
         self.ops.sample(logits, ctx.temperature, ctx.seed, ctx.positions, sampled, pos_offset=1)
         self.ops.advance(sampled, ctx.token_ids, ctx.positions, ctx.kv_len, self._history, ctx.step_counter,
-                         self.MAX_DEVICE_STEPS)
+                         self.MAX_DEVICE_STEPS, status=self._status, status_index=self._status_index)
         return logits
 
     def _run_mixed_step(self, ctx: StepContext) -> torch.Tensor:
@@ -489,8 +494,11 @@ class ModelRunner:
         self.cache.free(request)
 
     def check_status(self) -> None:
-        """Raise if a kernel flagged bad input (reads one int from the device)."""
+        """Raise if a kernel flagged bad input or a wait that ran out (reads one int from the device).
+        Decode steps that sample on the device bring the flag along with their tokens and check it
+        themselves; after other steps the caller decides when the read is worth a synchronisation."""
         flag = int(self._status.item())
         if flag:
             self._status.zero_()
-            raise StepError(f"a kernel reported bad input (status {flag})")
+            self._history.array[self._status_index] = 0
+            raise StepError(f"a kernel reported bad input or gave up waiting (status {flag})")

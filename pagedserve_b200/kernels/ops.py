@@ -77,13 +77,14 @@ _SIGNATURES = {
         "ps_kv_append": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P],
         "ps_paged_attention_simt": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
-        "ps_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+        "ps_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P],
         "ps_host_alloc_mapped": [_L, _P, _P],
         "ps_host_free": [_P],
         "ps_copy_h2d": [_P, _P, _L, _P],
     },
     "bf16": {
-        "ps_gemm_skinny": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ps_gemm_skinny": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                           _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_gemm_skinny_fused": [_P, _I, _P, _P, _P, _F, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                  _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_paged_attention_decode_checked": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
@@ -148,7 +149,7 @@ class Ops:
         self.core = _declare(_load_library("core"), "core")
         self.fast = _declare(_load_library("bf16"), "bf16") if dtype == torch.bfloat16 else None
         self._tc = None              # tcgen05 library, loaded when a product first needs it
-        self._tc_status = None
+        self.status = None
         self._counters = None        # zeroed int32 scratch of the split attention kernel
         self.launches = 0            # count of kernel launches issued through this object
 
@@ -222,8 +223,10 @@ class Ops:
                "gemm_simt")
         return out
 
-    def linear_skinny(self, a, w, bias, out, act=None, accumulate=False):
-        """Weight-streaming product for at most 64 rows of ``a`` (bfloat16 operands)."""
+    def linear_skinny(self, a, w, bias, out, act=None, accumulate=False, kv=None):
+        """Weight-streaming product for at most 64 rows of ``a`` (bfloat16 operands).  ``kv`` =
+        (ctx, layer, q_width, kv_width, head_dim) sends the key and value columns of a packed q|k|v
+        projection into the pages instead of ``out``."""
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
@@ -239,7 +242,7 @@ class Ops:
         _check(self.fast.ps_gemm_skinny(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias),
                                         _ptr(out), out.stride(0), M, N, K,
                                         dtype_code(out.dtype), _ACT_CODE[act],
-                                        1 if accumulate else 0, _stream()), "gemm_skinny")
+                                        1 if accumulate else 0, *self._kv_arguments(kv, N), _stream()), "gemm_skinny")
         return out
 
     def linear_tc(self, a, w, bias, out, act=None, accumulate=False, status=None, bn=0):
@@ -258,9 +261,7 @@ class Ops:
         if self._tc is None:
             self._tc = _declare(_load_library("tc"), "tc")
         if status is None:
-            if self._tc_status is None:
-                self._tc_status = torch.zeros(1, dtype=torch.int32, device=a.device)
-            status = self._tc_status
+            status = self.status_flag(a.device)
         self.launches += 1
         _check(self._tc.ps_gemm_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
                                    out.stride(0), M, N, K,
@@ -301,6 +302,23 @@ class Ops:
                 and norm.weight.data_ptr() % 16 == 0
                 and (norm.bias is None or norm.bias.data_ptr() % 16 == 0))
 
+    @staticmethod
+    def _kv_arguments(kv, N):
+        """The cache-write arguments of a product's epilogue; ``kv`` None = no cache write."""
+        if kv is None:
+            return (None, None, 0, None, None, None, 0, N, 0, 1, 1)
+        ctx, layer, q_width, kv_width, head_dim = kv
+        return (_ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride, _ptr(ctx.token_item),
+                _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
+                q_width, kv_width, head_dim, layer.page_size)
+
+    def status_flag(self, device) -> torch.Tensor:
+        """The device int32 that kernels of this object set non-zero when a bounded wait ran out or an input
+        was bad, unless the caller hands them a flag of its own."""
+        if self.status is None:
+            self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        return self.status
+
     def linear_skinny_fused(self, a, w, bias, out, act=None, accumulate=False, kv=None):
         """out = act(norm(x)[rows] @ w.T + bias) with the norm computed inside the product's kernel
         (``a`` is a DeferredNorm); ``kv`` = (ctx, layer, q_width, kv_width, head_dim) also sends the key
@@ -311,14 +329,7 @@ class Ops:
         if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
             raise KernelError("linear_skinny_fused: shapes do not match")
         _require(out, "out")
-        if kv is not None:
-            ctx, layer, q_width, kv_width, head_dim = kv
-            kv_args = (_ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride, _ptr(ctx.token_item),
-                       _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
-                       q_width, kv_width, head_dim, layer.page_size)
-        else:
-            kv_args = (None, None, 0, None, None, None, 0,
-                       N, 0, 1, 1)
+        kv_args = self._kv_arguments(kv, N)
         self.launches += 1
         _check(self.fast.ps_gemm_skinny_fused(
             _ptr(a.x), a.x.stride(0), _ptr(a.rows), _ptr(norm.weight), _ptr(norm.bias),
@@ -337,10 +348,16 @@ class Ops:
                 return True
             if hasattr(a, "materialize"):
                 a = a.materialize()
+            from pagedserve_b200.kernels import tensorcore
+
             # many rows: the tcgen05 product, whose TMA-store epilogue sends the key and value columns to the pages
-            if (not self.skinny_ok(a, w) and self.tc_ok(a, w) and q_width % 64 == 0 and head_dim % 8 == 0
-                    and out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 and out.dtype == torch.bfloat16):
-                self.linear_tc_qkv(a, w, bias, out, ctx, layer, q_width, kv_width, head_dim)
+            if tensorcore.prefers_tc(self, a, w):
+                if (q_width % 64 == 0 and head_dim % 8 == 0 and out.data_ptr() % 16 == 0
+                        and out.stride(0) % 8 == 0 and out.dtype == torch.bfloat16):
+                    self.linear_tc_qkv(a, w, bias, out, ctx, layer, q_width, kv_width, head_dim)
+                    return True
+            elif self.skinny_ok(a, w):
+                self.linear_skinny(a, w, bias, out, kv=(ctx, layer, q_width, kv_width, head_dim))
                 return True
         self.linear(a, w, bias, out)
         return False
@@ -356,12 +373,10 @@ class Ops:
         _require(out, "out", torch.bfloat16)
         if self._tc is None:
             self._tc = _declare(_load_library("tc"), "tc")
-        if self._tc_status is None:
-            self._tc_status = torch.zeros(1, dtype=torch.int32, device=a.device)
         self.launches += 1
         _check(self._tc.ps_gemm_tc_qkv(
             _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
-            _ptr(self._tc_status), _ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride,
+            _ptr(self.status_flag(a.device)), _ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride,
             _ptr(ctx.token_item), _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
             q_width, kv_width, head_dim, layer.page_size, _stream()), "gemm_tc_qkv")
         return out
@@ -522,9 +537,7 @@ class Ops:
         if self._tc is None:
             self._tc = _declare(_load_library("tc"), "tc")
         if status is None:
-            if self._tc_status is None:
-                self._tc_status = torch.zeros(1, dtype=torch.int32, device=q.device)
-            status = self._tc_status
+            status = self.status_flag(q.device)
         pages, layers, two, kv_heads, ps, hd = pool.shape
         rows_per_tensor = kv_heads * ps                      # rows of one (layer, k or v) inside a page
         page_rows = layers * 2 * rows_per_tensor
@@ -578,10 +591,13 @@ class Ops:
         stream (the plain runtime call: a fraction of the host time of a tensor ``copy_``)."""
         _check(self.core.ps_copy_h2d(dst.data_ptr(), src_host_ptr, nbytes, _stream()), "copy_h2d")
 
-    def advance(self, sampled, token_ids, positions, kv_len, history, step_counter, max_steps):
-        """Feed sampled tokens back as the next inputs of a decode-only batch and move it one position on."""
+    def advance(self, sampled, token_ids, positions, kv_len, history, step_counter, max_steps, status=None,
+                status_index=None):
+        """Feed sampled tokens back as the next inputs of a decode-only batch and move it one position on.
+        ``status`` (device int32) is copied to ``history[status_index]`` for the host to read with the tokens."""
         B = sampled.numel()
         self.launches += 1
+        copy_to = None if status is None else _ptr(history) + 4 * status_index
         _check(self.core.ps_advance(_ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(kv_len), _ptr(history),
-                                    _ptr(step_counter), B, max_steps, _stream()),
+                                    _ptr(step_counter), B, max_steps, _ptr(status), copy_to, _stream()),
                "advance")

@@ -11,17 +11,22 @@
 from __future__ import annotations
 
 
+def prefers_tc(ops, a, w) -> bool:
+    """Whether the tcgen05 kernel takes this product.  The weight-streaming kernel brings the rows of ``a`` to
+    every CTA (16 output columns): from 17 rows on and 4,096 columns up (a vocabulary, the wide projections of
+    large models) that traffic costs more than the half-empty 128-row tiles of the tcgen05 kernel (64 rows x
+    50,257 x 768: 46 vs 85 us; 64 x 4,800 x 1,600: 12 vs 37 us; 16 rows: the streaming kernel wins at every
+    shape)."""
+    if not ops.tc_ok(a, w):
+        return False
+    return (a.shape[0] > 16 and w.shape[0] >= 4096) or not ops.skinny_ok(a, w)
+
+
 def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
-    # The weight-streaming kernel re-reads the rows of ``a`` for every 16 output columns: from 17 rows on and
-    # 4,096 columns up (a vocabulary, the wide projections of large models) that traffic costs more than the
-    # half-empty 128-row tiles of the tcgen05 kernel (64 rows x 50,257 x 768: 46 vs 85 us; 64 x 4,800 x 1,600:
-    # 12 vs 37 us; 16 rows: the streaming kernel wins at every shape).
-    if a.shape[0] > 16 and w.shape[0] >= 4096 and ops.tc_ok(a, w):
+    if prefers_tc(ops, a, w):
         return ops.linear_tc(a, w, bias, out, act, accumulate, status=status)
     if ops.skinny_ok(a, w):
         return ops.linear_skinny(a, w, bias, out, act, accumulate)
-    if ops.tc_ok(a, w):
-        return ops.linear_tc(a, w, bias, out, act, accumulate, status=status)
     return ops.linear_simt(a, w, bias, out, act, accumulate)
 
 

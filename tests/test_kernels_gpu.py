@@ -193,7 +193,7 @@ def test_gemm_tcgen05_96_wide(M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 8, 9, 16, 25, 32])
-@pytest.mark.parametrize("N,K", [(288, 96), (2304, 768), (1000, 320), (768, 3072)])
+@pytest.mark.parametrize("N,K", [(288, 96), (2304, 768), (1000, 320), (768, 3072), (312, 104), (96, 328)])
 def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
     """norm -> product in one kernel against norm kernel + product, with gathered rows, the RMS form, and
     the key/value columns of a packed projection landing in the right page slots."""
@@ -279,6 +279,77 @@ def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
             assert rel_err(slot[0], want[i, width:2 * width]) < 8e-3
             assert rel_err(slot[1], want[i, 2 * width:]) < 8e-3
         assert int((pool != 0).sum()) <= 2 * M * width             # nothing else was touched
+
+
+@pytest.mark.parametrize("M", [17, 24, 25, 33, 41, 47, 49, 57])
+@pytest.mark.parametrize("N,K", [(48, 8), (300, 328), (1003, 104), (2304, 768), (770, 3080), (160, 6400)])
+def test_gemm_skinny_every_count_of_row_tiles(M, N, K):
+    """Row counts that fall into each instance of the few-rows product (3 to 8 tiles of 8 rows), with widths
+    that are no multiple of 32: against float64 and against the CUDA-core product on the same inputs."""
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(3 * M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    for act, out_dtype, tol in ((None, torch.float32, 2e-5), ("gelu_tanh", torch.bfloat16, 6e-3)):
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        ops.linear_skinny(a, w, bias, out, act=act)
+        assert rel_err(out, gemm_reference(a.cpu(), w.cpu(), bias.cpu(), act, None)) < tol, (act, out_dtype)
+    base = torch.randn(M, N, generator=g)
+    stream = base.clone().to(DEV)
+    ops.linear_skinny(a, w, bias, stream, accumulate=True)
+    assert rel_err(stream, gemm_reference(a.cpu(), w.cpu(), bias.cpu(), None, base)) < 2e-5
+    simt = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    fast = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_simt(a, w, None, simt)
+    ops.linear_skinny(a, w, None, fast)
+    assert rel_err(fast, simt) < 1e-5
+
+
+@pytest.mark.parametrize("M", [17, 40, 64])
+@pytest.mark.parametrize("width,head_dim,K", [(96, 48, 96), (768, 64, 768), (160, 16, 264)])
+def test_gemm_skinny_writes_the_cache(M, width, head_dim, K):
+    """The packed q|k|v projection of 17 to 64 rows, too many for the norm to be folded in: queries to the
+    buffer, keys and values into the pages."""
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(M + width + K)
+    N = 3 * width
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    kv_heads = width // head_dim
+    page = 8
+    lengths = [3 + 2 * i for i in range(M)]                 # every token is the last of its own request
+    pages = [-(-n // page) for n in lengths]
+    table = torch.full((M, max(pages)), -1, dtype=torch.int32)
+    order = torch.randperm(sum(pages), generator=g)
+    cursor = 0
+    for i, count in enumerate(pages):
+        table[i, :count] = order[cursor:cursor + count].to(torch.int32)
+        cursor += count
+    pool = torch.zeros(sum(pages), 1, 2, kv_heads, page, head_dim, dtype=torch.bfloat16, device=DEV)
+
+    class Ctx:
+        token_item = torch.arange(M, dtype=torch.int32, device=DEV)
+        positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+
+    class Layer:
+        k_pool, v_pool = pool[:, 0, 0], pool[:, 0, 1]
+        page_stride = 2 * kv_heads * page * head_dim
+        page_size = page
+        block_table = table.to(DEV)
+
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    assert ops.linear_qkv(a, w, bias, out, Ctx, Layer, width, width, head_dim, scatter=True)
+    want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear_skinny(a, w, bias, want)
+    assert torch.equal(out[:, :width], want[:, :width])       # the same kernel: the same sums in the same order
+    assert float(out[:, width:].abs().max()) == 0.0           # keys and values did not go to the buffer
+    for i, n in enumerate(lengths):
+        slot = pool[int(table[i, (n - 1) // page]), 0, :, :, (n - 1) % page, :].reshape(2, width)
+        assert torch.equal(slot[0], want[i, width:2 * width])
+        assert torch.equal(slot[1], want[i, 2 * width:])
+    assert int((pool != 0).sum()) <= 2 * M * width             # nothing else was touched
 
 
 def test_gemm_skinny_refuses_what_it_cannot_take():
