@@ -234,3 +234,30 @@ def test_a_step_staged_ahead_is_used_or_undone():
     engine.finish(1)
     assert engine.cache.free_pages() == engine.cache.total_pages() >= free_before
     engine.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_flag_raised_by_a_kernel_reaches_the_caller(dtype):
+    """Kernels report bad input and waits that ran out through one device flag.  A decode step brings the flag
+    back with its tokens and raises; after steps that only return logits, ``check_status`` does.  The flag is
+    set by hand here (no kernel is made to fail)."""
+    from pagedserve_b200.engine.batch import StepEntry
+    from pagedserve_b200.engine.step import StepError
+
+    engine = make_engine("a", dtype)
+    vocab = helpers.TINY["a"][0]["vocab_size"]
+    prompt = helpers.random_tokens(vocab, 9, seed=3)
+    logits = engine.step([StepEntry(0, prompt, [len(prompt) - 1])])
+    engine.check_status()                                              # nothing flagged
+    token = int(logits.argmax(-1).item())
+    out = engine.decode_tokens([0], [token], [0.0], [0], 1)
+    assert engine.runner._status is engine.ops.status_flag(engine.device)      # one flag for ops and runner
+    engine.runner._status.fill_(7)
+    with pytest.raises(StepError, match="status 7"):
+        engine.decode_tokens([0], [int(out[0, 0])], [0.0], [0], 1)
+    assert int(engine.runner._status.item()) == 0                      # raised once, then cleared
+    engine.runner._status.fill_(5)
+    with pytest.raises(StepError, match="status 5"):
+        engine.check_status()
+    engine.check_status()
+    engine.finish(0)
