@@ -103,6 +103,8 @@ __global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict_
     sampled = pdl_fresh(sampled);
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     int step = *step_counter;
+    // every kernel of the step has ended: what they flagged travels with the tokens
+    const int flagged = (i == 0 && status && status_copy) ? *(volatile const int*)status : 0;
     if (i < B) {
         int token = sampled[i];
         token_ids[i] = token;
@@ -113,8 +115,7 @@ __global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict_
     __syncthreads();
     if (i == 0) {
         *step_counter = step + 1;
-        // every kernel of the step has ended: what they flagged travels with the tokens
-        if (status && status_copy) *status_copy = *(volatile const int*)status;
+        if (flagged) *status_copy = flagged;                  // the host zeroed the copy and zeroes it after a read
     }
 }
 
