@@ -23,6 +23,8 @@ class EngineConfig:
     block_size: int = 16                        # tokens per KV page (reference: main.py:215)
     num_blocks: Optional[int] = None            # pages in the pool; None => from kv_cache_memory_mb
     kv_cache_memory_mb: Optional[int] = None    # reference: main.py:283-287
+    kv_cache_memory_utilization: float = 0.90   # reference: main.py:288-293; used when neither is given
+    kv_cache_safety_mb: int = 3072              # reference: main.py:294-298
     max_num_seqs: int = 32                      # live requests (reference --max-batch-size, main.py:151)
     max_num_batched_tokens: int = 2048          # token budget of one step
     strategy: str = ORCA_STRATEGY               # reference: main.py:265-270
@@ -39,6 +41,10 @@ class EngineConfig:
             raise ConfigError("num_blocks must be positive")
         if self.kv_cache_memory_mb is not None and self.kv_cache_memory_mb <= 0:
             raise ConfigError("kv_cache_memory_mb must be positive")   # reference: main.py:209-210
+        if not 0 < self.kv_cache_memory_utilization <= 1:
+            raise ConfigError("kv_cache_memory_utilization must be in (0, 1]")   # reference: main.py:55-56
+        if self.kv_cache_safety_mb < 0:
+            raise ConfigError("kv_cache_safety_mb cannot be negative")           # reference: main.py:57-58
         if self.max_num_seqs <= 0:
             raise ConfigError("max_num_seqs must be positive")         # reference: main.py:183-184
         if self.max_num_batched_tokens <= 0:

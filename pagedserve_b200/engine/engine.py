@@ -11,6 +11,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
+from pagedserve_b200.cache.budget import MIB, kv_cache_budget, pages_for_budget
 from pagedserve_b200.cache.manager import CacheManager
 from pagedserve_b200.config.engine_config import EngineConfig
 from pagedserve_b200.config.registry import ModelConfig, load_config_dict, resolve_architecture
@@ -21,7 +22,6 @@ from pagedserve_b200.parts.base import PartEnv
 from pagedserve_b200.sampling.sampler import Sampler
 
 _TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
-MIB = 1024 * 1024
 
 
 class Engine:
@@ -90,10 +90,11 @@ class Engine:
             if num_pages == 0:
                 raise ValueError(f"Memory budget is too small; one block requires {bytes_per_page} bytes")
         else:
-            wanted = cfg.max_num_seqs * (-(-self.spec.max_model_len // cfg.block_size))
-            free, _ = torch.cuda.mem_get_info(self.device)
-            affordable = int(free * 0.5) // max(bytes_per_page, 1)
-            num_pages = max(1, min(wanted, affordable))
+            # reference: main.py:186-200 (budget from the device's free and total memory)
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = kv_cache_budget(free, total, cfg.kv_cache_memory_utilization, cfg.kv_cache_safety_mb * MIB)
+            num_pages = pages_for_budget(budget, bytes_per_page, cfg.max_num_seqs, self.spec.max_model_len,
+                                         cfg.block_size)
         return CacheManager(kv_needs, state_needs, cfg.block_size, int(num_pages), cfg.max_num_seqs,
                             self.spec.max_model_len, dtype=self.dtype, device=self.device,
                             scratch_tokens=ModelRunner.PAD_LONG)

@@ -3,11 +3,12 @@
 reference: main.py:136-254 (``build_scheduler``) and :257-342 (``main``).  Options
 keep the reference's names and meanings where it has them (``--model``,
 ``--strategy``, ``--prefill-chunk-size``, ``--max-batch-size``,
-``--kv-cache-memory-mb``, ``--dtype``, ``--disable-cuda-graphs``).  ``--model`` is a
+``--kv-cache-memory-mb``, ``--kv-cache-memory-utilization``, ``--kv-cache-safety-mb``,
+``--dtype``, ``--disable-cuda-graphs``).  ``--model`` is a
 folder with ``config.json`` and ``model.safetensors``, or the name of a size
 (``tiny-a``, ``tiny-b``, ``gpt2-124m``, ``gpt2-345m``, ``gpt2-1.5b``) to be filled with
-seeded random weights.  Dropped: the decode-attention backend switch, the INT8
-cache and the utilisation heuristics (one backend, no quantisation).  Prompts are
+seeded random weights.  Dropped: the decode-attention backend switch and the INT8
+cache (one backend, no quantisation).  Prompts are
 token ids: there is no tokenizer in the engine.
 """
 
@@ -18,6 +19,7 @@ import os
 import sys
 from typing import Optional
 
+from pagedserve_b200.cache.budget import DEFAULT_KV_MEMORY_UTILIZATION, DEFAULT_KV_SAFETY_MB
 from pagedserve_b200.config.engine_config import (
     EngineConfig,
     ORCA_STRATEGY,
@@ -40,6 +42,8 @@ def build_engine(model: str, seed: int = 0, **engine_options):
 
 def build_scheduler(model: str = "tiny-a", scheduling_strategy: str = ORCA_STRATEGY, prefill_chunk_size: int = 16,
                     max_batch_size: Optional[int] = None, kv_cache_memory_mb: Optional[int] = None,
+                    kv_cache_memory_utilization: float = DEFAULT_KV_MEMORY_UTILIZATION,
+                    kv_cache_safety_mb: int = DEFAULT_KV_SAFETY_MB,
                     execution_dtype: str = "float32", enable_cuda_graphs: bool = True, block_size: int = 16,
                     num_blocks: Optional[int] = None, max_num_batched_tokens: int = 2048, seed: int = 0,
                     eos_token_id: Optional[int] = None):
@@ -49,7 +53,9 @@ def build_scheduler(model: str = "tiny-a", scheduling_strategy: str = ORCA_STRAT
     if max_batch_size <= 0:
         raise ValueError("max_batch_size must be positive")
     engine = build_engine(model, seed=seed, dtype=execution_dtype, block_size=block_size, num_blocks=num_blocks,
-                          kv_cache_memory_mb=kv_cache_memory_mb, max_num_seqs=max_batch_size,
+                          kv_cache_memory_mb=kv_cache_memory_mb,
+                          kv_cache_memory_utilization=kv_cache_memory_utilization,
+                          kv_cache_safety_mb=kv_cache_safety_mb, max_num_seqs=max_batch_size,
                           max_num_batched_tokens=max_num_batched_tokens, strategy=scheduling_strategy,
                           prefill_chunk_size=prefill_chunk_size, enable_cuda_graphs=enable_cuda_graphs)
     return engine.make_scheduler(eos_token_id=eos_token_id)
@@ -69,6 +75,10 @@ def main(argv=None) -> int:
     parser.add_argument("--max-batch-size", type=int, help="maximum requests per iteration (default: 32)")
     parser.add_argument("--max-num-batched-tokens", type=int, default=2048, help="token budget of one step")
     parser.add_argument("--kv-cache-memory-mb", type=int, help="explicit KV-cache budget in MiB")
+    parser.add_argument("--kv-cache-memory-utilization", type=float, default=DEFAULT_KV_MEMORY_UTILIZATION,
+                        help="target total GPU memory utilization for automatic KV sizing")
+    parser.add_argument("--kv-cache-safety-mb", type=int, default=DEFAULT_KV_SAFETY_MB,
+                        help="device memory left free for activations and temporary buffers")
     parser.add_argument("--num-blocks", type=int, help="explicit number of KV pages")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per KV page")
     parser.add_argument("--dtype", choices=SUPPORTED_DTYPES, default="float32", help="execution dtype")
@@ -85,6 +95,7 @@ def main(argv=None) -> int:
     scheduler = build_scheduler(
         args.model, scheduling_strategy=args.strategy, prefill_chunk_size=args.prefill_chunk_size,
         max_batch_size=args.max_batch_size, kv_cache_memory_mb=args.kv_cache_memory_mb,
+        kv_cache_memory_utilization=args.kv_cache_memory_utilization, kv_cache_safety_mb=args.kv_cache_safety_mb,
         execution_dtype=args.dtype, enable_cuda_graphs=not args.disable_cuda_graphs,
         block_size=args.block_size, num_blocks=args.num_blocks,
         max_num_batched_tokens=args.max_num_batched_tokens, seed=args.seed)

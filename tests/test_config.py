@@ -78,3 +78,35 @@ def test_engine_config_checks():
                 dict(strategy="fifo"), dict(prefill_chunk_size=0), dict(num_blocks=0), dict(kv_cache_memory_mb=0)):
         with pytest.raises(ConfigError):
             EngineConfig(**bad)
+
+
+def test_kv_cache_budget_takes_the_smaller_of_target_and_margin():
+    """reference: main.py:48-73 (same arithmetic, same refusals)."""
+    from pagedserve_b200.cache.budget import MIB, kv_cache_budget, pages_for_budget
+
+    total, free = 1000 * MIB, 800 * MIB
+    # utilisation target: 900 - 200 in use = 700; safety margin: 800 - 50 = 750
+    assert kv_cache_budget(free, total, 0.90, 50 * MIB) == int(total * 0.90) - 200 * MIB
+    # a large margin decides instead
+    assert kv_cache_budget(free, total, 0.90, 300 * MIB) == 500 * MIB
+    with pytest.raises(RuntimeError, match="no device memory remains"):
+        kv_cache_budget(free, total, 0.90, 800 * MIB)
+    with pytest.raises(RuntimeError):
+        kv_cache_budget(100 * MIB, total, 0.5, 0)          # already above the target
+    for bad in (dict(memory_utilization=0.0), dict(memory_utilization=1.5), dict(safety_memory=-1)):
+        with pytest.raises(ValueError):
+            kv_cache_budget(free, total, **bad)
+    with pytest.raises(ValueError):
+        kv_cache_budget(total + 1, total)
+    # pages: what the budget affords, but never more than the live requests can hold
+    assert pages_for_budget(10 * MIB, 4096, max_num_seqs=4, max_model_len=100, block_size=16) == 4 * 7
+    assert pages_for_budget(5 * 4096 + 17, 4096, max_num_seqs=4, max_model_len=100, block_size=16) == 5
+    with pytest.raises(ValueError, match="too small"):
+        pages_for_budget(4095, 4096, 4, 100, 16)
+
+
+def test_engine_config_refuses_bad_budget_options():
+    for bad in (dict(kv_cache_memory_utilization=0.0), dict(kv_cache_memory_utilization=1.01),
+                dict(kv_cache_safety_mb=-1)):
+        with pytest.raises(ConfigError):
+            EngineConfig(**bad)
