@@ -260,6 +260,27 @@ class Scheduler:
         self.steps += 1
         return emitted
 
+    def abort(self, request_id: int) -> List[int]:
+        """Take a request out before it is done: what it holds (pages, slot, reservation) is given back
+        and it counts as finished with the tokens it has so far, which are returned.  Between steps only."""
+        request = self.active.pop(request_id, None)
+        if request is None:
+            for candidate in self.waiting:
+                if candidate.request_id == request_id:
+                    request = candidate
+                    break
+            if request is None:
+                raise KeyError(f"request {request_id} is not waiting or running")
+            self.waiting.remove(request)
+        if request.reserved_blocks:
+            # admitted: it has run at least one step, so the cache knows it
+            self.engine.finish(request.request_id)
+            self.reserved_blocks -= request.reserved_blocks
+            request.reserved_blocks = 0
+        request.pending_token_id = None
+        self.finished[request.request_id] = request
+        return list(request.generated_token_ids)
+
     def run_until_complete(self) -> Dict[int, List[int]]:
         """reference: src/scheduler/orca_scheduler.py:297-303 (token ids instead of decoded text)"""
         while self.waiting or self.active:

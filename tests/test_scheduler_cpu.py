@@ -137,3 +137,27 @@ def test_max_num_seqs_limits_a_step():
     assert [entry[0] for entry in engine.steps[0]] == ids[:2]
     sched.run_until_complete()
     assert set(sched.finished) == set(ids)
+
+
+def test_abort_gives_back_pages_and_reservation_in_every_state():
+    engine = FakeEngine(pages=8, page=4)
+    sched = Scheduler(engine, max_num_seqs=4, max_num_batched_tokens=64, strategy="sarathi", prefill_chunk_size=4)
+    a = sched.add_token_request(list(range(1, 11)), max_new_tokens=4)     # 14 tokens: 4 pages
+    b = sched.add_token_request([1, 2, 3], max_new_tokens=5)              # 2 pages
+    c = sched.add_token_request(list(range(1, 14)), max_new_tokens=3)     # 4 pages: waits for room
+    sched.step()                                                          # a: first portion
+    assert sched.reserved_blocks == 4 and engine.cache.free_pages() == 7
+    assert sched.abort(a) == []                                           # in the middle of its prompt
+    assert sched.reserved_blocks == 0 and engine.cache.free_pages() == 8 and engine.cache.live_requests == 0
+    sched.step()                                                          # b: whole prompt, first token
+    sched.step()                                                          # b decodes, c's first portion
+    assert b in sched.active and sched.reserved_blocks == 6
+    assert sched.abort(b) == sched.finished[b].generated_token_ids and len(sched.finished[b].generated_token_ids) == 2
+    assert sched.reserved_blocks == 4
+    assert sched.abort(sched.add_token_request([4, 5], max_new_tokens=2)) == []   # never ran: holds nothing
+    with pytest.raises(KeyError):
+        sched.abort(a)                                                    # already finished
+    results = sched.run_until_complete()
+    assert len(results[c]) == 3 and results[a] == []
+    assert sched.reserved_blocks == 0 and engine.cache.free_pages() == 8 and engine.cache.live_requests == 0
+    engine.cache.check_invariants()
