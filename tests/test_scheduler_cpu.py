@@ -161,3 +161,50 @@ def test_abort_gives_back_pages_and_reservation_in_every_state():
     assert len(results[c]) == 3 and results[a] == []
     assert sched.reserved_blocks == 0 and engine.cache.free_pages() == 8 and engine.cache.live_requests == 0
     engine.cache.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("strategy", ["orca", "sarathi"])
+def test_random_workloads_finish_without_leaks_whatever_the_limits(strategy, seed):
+    """Requests arrive while others run, under random limits: every one finishes with the tokens
+    that depend on its own positions only, reservations never exceed the pool, nothing leaks."""
+    import random
+
+    rng = random.Random(seed)
+    engine = FakeEngine(pages=rng.randint(21, 40), page=rng.choice([2, 4, 8]), slots=rng.randint(2, 8))
+    sched = Scheduler(engine, max_num_seqs=rng.randint(1, 8), max_num_batched_tokens=rng.randint(3, 40),
+                      strategy=strategy, prefill_chunk_size=rng.randint(2, 12),
+                      max_prefills_per_step=rng.randint(1, 3))
+    expected = {}
+    to_add = rng.randint(5, 14)
+    aborted = set()
+    guard = 0
+    while to_add or sched.waiting or sched.active:
+        guard += 1
+        assert guard < 5000
+        if to_add and (rng.random() < 0.4 or not (sched.waiting or sched.active)):
+            prompt_len, new = rng.randint(1, 30), rng.randint(1, 12)
+            rid = sched.add_token_request([rng.randrange(50) for _ in range(prompt_len)], max_new_tokens=new)
+            expected[rid] = [(prompt_len + i) % 50 for i in range(new)]
+            to_add -= 1
+            continue
+        if rng.random() < 0.05 and (sched.waiting or sched.active):
+            victim = rng.choice([r.request_id for r in sched.waiting] + list(sched.active))
+            expected[victim] = expected[victim][:len(sched.abort(victim))]
+            aborted.add(victim)
+            continue
+        before = {r.request_id: len(r.generated_token_ids) for r in list(sched.waiting) + list(sched.active.values())}
+        emitted = sched.step()
+        assert sched.reserved_blocks <= sched.total_blocks
+        assert len(engine.steps[-1]) <= sched.max_num_seqs
+        assert sum(count for _, count, _ in engine.steps[-1]) <= sched.max_num_batched_tokens
+        assert all(rid in before for rid in emitted)
+        # a request that decodes is never left out of a step while it holds pages (no preemption, no starvation)
+        if strategy == "sarathi":
+            ran = {rid for rid, _, _ in engine.steps[-1]}
+            decoding = [rid for rid, n in before.items() if n > 0]
+            assert set(decoding[:sched.max_num_seqs]) <= ran or len(ran) == sched.max_num_seqs
+    assert {rid: r.generated_token_ids for rid, r in sched.finished.items()} == expected
+    assert sched.reserved_blocks == 0 and engine.cache.live_requests == 0
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+    engine.cache.check_invariants()
