@@ -501,4 +501,5 @@ class ModelRunner:
         if flag:
             self._status.zero_()
             self._history.array[self._status_index] = 0
+            self.ops.reset_after_fault()
             raise StepError(f"a kernel reported bad input or gave up waiting (status {flag})")

@@ -319,6 +319,12 @@ class Ops:
             self.status = torch.zeros(1, dtype=torch.int32, device=device)
         return self.status
 
+    def reset_after_fault(self) -> None:
+        """After a kernel gave up a wait: the split attention kernel's arrival counters may not be back at
+        zero (the CTA that would have reset them stopped), and later steps would merge too early."""
+        if self._counters is not None:
+            self._counters.zero_()
+
     def linear_skinny_fused(self, a, w, bias, out, act=None, accumulate=False, kv=None):
         """out = act(norm(x)[rows] @ w.T + bias) with the norm computed inside the product's kernel
         (``a`` is a DeferredNorm); ``kv`` = (ctx, layer, q_width, kv_width, head_dim) also sends the key
