@@ -10,6 +10,8 @@ value     decoded tokens per second over K steps timed on the device (CUDA event
           decode step replayed K times, sampling and token feedback on the device.
 e2e       the same through the Python entry point (``Scheduler.step``): every step the host builds
           the batch, copies it from pinned memory to the device and reads the sampled tokens back.
+          (The scheduler launches the next step of an unchanged batch behind the running one: that
+          step's token ids are the ones the device fed back, every other input is uploaded.)
 prefill   one step of 2,048 prompt tokens (2 prompts of 1,024).
 roofline  bytes the decode step has to read (every weight once + the cache of the live requests)
           divided by its time, against the measured copy bandwidth.

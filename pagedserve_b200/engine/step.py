@@ -37,7 +37,10 @@ class _DecodeGraph:
 
 
 class _StagedStep:
-    """A decode step prepared ahead of its tokens: its pages are taken, its buffer is filled."""
+    """A decode step prepared ahead of its tokens: its pages are taken, its buffer is filled.  ``launched``:
+    it is already in the stream behind the step before it, whose kernel feeds the tokens back on the device;
+    ``half`` is the half of the token history it writes, ``event`` marks its end and ``fed_tokens`` are the
+    tokens it was given (what the step before it sampled)."""
 
     def __init__(self, requests, temperatures, seeds, ctx, turn):
         self.requests = requests
@@ -45,6 +48,10 @@ class _StagedStep:
         self.seeds = seeds
         self.ctx = ctx
         self.turn = turn
+        self.launched = False
+        self.half = 0
+        self.event = None
+        self.fed_tokens = None
 
 
 class ModelRunner:
@@ -96,7 +103,8 @@ class ModelRunner:
         self._history = self.ops.mapped_host_buffer(self._status_index + 1)
         self._history.array[self._status_index] = 0
         self._shapes = {}                 # (T, I, R) -> (BatchLayout, DeviceViews)
-        self._staged = None               # a decode step staged ahead of its tokens
+        self._staged = None               # a decode step staged (and perhaps launched) ahead of its tokens
+        self._step_events = [torch.cuda.Event(), torch.cuda.Event()]    # ends of the steps of the two halves
         self._capture_stream = None       # made at the first capture
         self._graph_pool = None
         self._ramp = np.arange(cache.max_slots + 2, dtype=np.int32)
@@ -206,13 +214,16 @@ class ModelRunner:
         self._staging_turn = turn
         return layout, views, self._staging[turn], self._staging_numpy[turn]
 
-    def _upload(self, layout: BatchLayout, staging: torch.Tensor, record: bool = True) -> None:
+    def _upload(self, layout: BatchLayout, staging: torch.Tensor, record: bool = True, first: int = 0) -> None:
         """The step's one host-to-device copy.  ``record=False``: the caller synchronises the stream before
-        it returns, so the staging buffer needs no event of its own."""
-        self.ops.copy_h2d(self._device_buffer, self._staging_ptr[self._staging_turn], layout.total * 4)
+        it returns, so the staging buffer needs no event of its own.  ``first``: the element the copy starts
+        at (a step launched ahead leaves out its token ids, which the device has fed back itself)."""
+        nbytes = (layout.total - first) * 4
+        self.ops.copy_h2d(self._device_buffer[first:] if first else self._device_buffer,
+                          self._staging_ptr[self._staging_turn] + first * 4, nbytes)
         if record:
             self._staging_events[self._staging_turn].record()
-        self.h2d_bytes = layout.total * 4
+        self.h2d_bytes = nbytes
 
     def _prepare_single_tokens(self, requests, tokens, extra_tokens: int, sampling) -> StepContext:
         """``prepare`` for a step in which every request brings one token and wants its logits: the same
@@ -290,14 +301,32 @@ class ModelRunner:
 
     # A decode step is followed, most of the time, by a decode step of the same requests.  While the device
     # runs step n the host therefore stages step n+1 (pages, positions, tables: everything but the token ids,
-    # which step n has yet to produce).  If the next call brings the same requests, only its tokens are
-    # written and the buffer goes up; if anything else is called first, the staged step is undone.
-    def _stage_ahead(self, requests, temperatures, seeds):
+    # which step n has yet to produce).  Step n's last kernel feeds its tokens back on the device, so where the
+    # step is a captured graph, step n+1 is also launched right behind it: its buffer goes up without the token
+    # section and the graph is replayed before the host has seen step n's tokens.  The device then never waits
+    # for the host between the two.  If the next call brings the same requests (and, for a launched step, the
+    # tokens that step n sampled), the step is used: only its tokens are written and the buffer goes up, or it
+    # is simply waited for.  If anything else is called first, the step is undone: its pages go back, and what
+    # a launched step computes is ignored (everything later is ordered behind it in the stream).
+    def _stage_ahead(self, requests, temperatures, seeds, launch_half=None):
         try:
             ctx = self._prepare_single_tokens(requests, None, 0, (temperatures, seeds))
         except (StepError, CacheFull):
             return None                       # no room or no length left: the real call will say so
-        return _StagedStep(list(requests), list(temperatures), list(seeds), ctx, self._staging_turn)
+        staged = _StagedStep(list(requests), list(temperatures), list(seeds), ctx, self._staging_turn)
+        graph = self._graphs.get((ctx.num_items, "sample")) if launch_half is not None else None
+        if graph is not None:
+            layout = ctx.layout
+            # the step's tokens go to the half of the history that the step before it does not use
+            self._staging_numpy[staged.turn][layout.counter] = launch_half
+            self._upload(layout, self._staging[staged.turn], record=True, first=layout.positions)
+            graph.replay()
+            self.graph_replays += 1
+            staged.event = self._step_events[launch_half]
+            staged.event.record()
+            staged.half = launch_half
+            staged.launched = True
+        return staged
 
     def _drop_staged(self) -> None:
         staged, self._staged = self._staged, None
@@ -365,32 +394,44 @@ class ModelRunner:
         if not (1 <= steps <= self.MAX_DEVICE_STEPS):
             raise StepError(f"steps must be between 1 and {self.MAX_DEVICE_STEPS}")
         staged, self._staged = self._staged, None
+        ahead = None                                        # this very step, if it was launched ahead
         if (staged is not None and steps == 1 and staged.requests == list(requests)
-                and staged.temperatures == list(temperatures) and staged.seeds == list(seeds)):
-            self._check_vocabulary(tokens)
+                and staged.temperatures == list(temperatures) and staged.seeds == list(seeds)
+                and (not staged.launched or np.array_equal(staged.fed_tokens, tokens))):
             ctx = staged.ctx
-            ctx.host.token_ids[:] = tokens
-            self._staging_turn = staged.turn
-            self._upload(ctx.layout, self._staging[staged.turn], record=False)
+            if staged.launched:
+                ahead = staged
+            else:
+                self._check_vocabulary(tokens)
+                ctx.host.token_ids[:] = tokens
+                self._staging_turn = staged.turn
+                self._upload(ctx.layout, self._staging[staged.turn], record=False)
         else:
             if staged is not None:
                 self._staged = staged
                 self._drop_staged()
             ctx = self._prepare_single_tokens(requests, tokens, steps - 1, (temperatures, seeds))
         B = ctx.num_items
-        try:
-            if self.enable_cuda_graphs:
-                graph = self._run_decode_graph(ctx, "sample")
-                for _ in range(steps - 1):
-                    graph.replay()
-                    self.graph_replays += 1
-            else:
-                for _ in range(steps):
-                    self._forward_and_sample(ctx)
-        except Exception:
-            for request in requests:
-                self.cache.rollback(request)
-            raise
+        half, done = 0, None
+        if ahead is not None:
+            half, done = ahead.half, ahead.event
+        else:
+            try:
+                if self.enable_cuda_graphs:
+                    graph = self._run_decode_graph(ctx, "sample")
+                    for _ in range(steps - 1):
+                        graph.replay()
+                        self.graph_replays += 1
+                else:
+                    for _ in range(steps):
+                        self._forward_and_sample(ctx)
+            except Exception:
+                for request in requests:
+                    self.cache.rollback(request)
+                raise
+            if stage_next and steps == 1 and self.enable_cuda_graphs:
+                done = self._step_events[0]
+                done.record()
         # the step is on its way: what follows runs on the host while the device works
         commit = self.cache.commit
         for request in requests:
@@ -398,11 +439,18 @@ class ModelRunner:
         self.steps += steps
         self.tokens_run += steps * B
         if stage_next and steps == 1:
-            self._staged = self._stage_ahead(requests, temperatures, seeds)
-        torch.cuda.current_stream().synchronize()          # the tokens are in host memory now
+            self._staged = self._stage_ahead(requests, temperatures, seeds,
+                                             launch_half=None if done is None else 1 - half)
+        if done is not None:
+            done.synchronize()                             # this step's tokens are in host memory now
+        else:
+            torch.cuda.current_stream().synchronize()
         if self._history.array[self._status_index]:
             self.check_status()
-        return self._history.array[:steps * B].reshape(steps, B).copy()
+        result = self._history.array[half * B:(half + steps) * B].reshape(steps, B).copy()
+        if self._staged is not None and self._staged.launched:
+            self._staged.fed_tokens = result[0]
+        return result
 
     def _forward_and_sample(self, ctx: StepContext) -> torch.Tensor:
         logits = self.model.forward(ctx)

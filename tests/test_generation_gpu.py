@@ -188,9 +188,10 @@ def test_graph_replay_equals_eager_and_device_loop_equals_stepwise(dtype):
 
 
 def test_a_step_staged_ahead_is_used_or_undone():
-    """While a decode step runs, the host stages the next one of the same requests.  The staged step must be
-    used when the batch comes back, and undone (its pages returned) when a request ends on an end-of-sequence
-    token, when another request joins, and when something else is called in between."""
+    """While a decode step runs, the host stages the next one of the same requests and, once the step is a
+    captured graph, launches it right behind (the tokens are fed back on the device).  The step must be used
+    when the batch comes back, and undone (its pages returned, its results ignored) when a request ends on an
+    end-of-sequence token, when another request joins, and when something else is called in between."""
     from pagedserve_b200.engine.batch import StepEntry
 
     config, weights = helpers.plain_model("a")
@@ -205,7 +206,7 @@ def test_a_step_staged_ahead_is_used_or_undone():
     engine = make_engine("a", "float32")
     scheduler = engine.make_scheduler(strategy="orca", max_num_seqs=4, eos_token_id=eos)
     ids = [scheduler.add_token_request(prompt, max_new_tokens=12) for prompt in prompts[:3]]
-    staged_seen = 0
+    staged_seen = launched_seen = 0
     for step in range(64):
         if step == 3:
             ids.append(scheduler.add_token_request(prompts[3], max_new_tokens=12))
@@ -213,8 +214,9 @@ def test_a_step_staged_ahead_is_used_or_undone():
             break
         scheduler.step()
         staged_seen += engine.runner._staged is not None
+        launched_seen += engine.runner._staged is not None and engine.runner._staged.launched
         engine.cache.check_invariants()
-    assert staged_seen > 0                                   # the path under test was taken
+    assert staged_seen > 0 and launched_seen > 0             # the paths under test were taken
     got = [scheduler.finished[i].generated_token_ids for i in ids]
     assert got == want
     assert engine.runner._staged is None
@@ -226,7 +228,7 @@ def test_a_step_staged_ahead_is_used_or_undone():
     tokens = [int(t) for t in first.argmax(-1).tolist()]
     free_before = engine.cache.free_pages()
     out = engine.decode_tokens([0, 1], tokens, [0.0, 0.0], [0, 0], 1, stage_next=True)
-    assert engine.runner._staged is not None
+    assert engine.runner._staged is not None and engine.runner._staged.launched
     logits = engine.step([StepEntry(0, [int(out[0, 0])], [0])])          # not the staged batch
     assert engine.runner._staged is None
     assert int(logits.argmax(-1).item()) == want[0][2] or eos in want[0][:2]
