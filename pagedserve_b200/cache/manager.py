@@ -311,6 +311,64 @@ class CacheManager:
             raise
         self.pending[slot] = new_tokens
 
+    def extend_many(self, requests: Sequence[Hashable], counts: Sequence[int]) -> None:
+        """``extend`` for several requests at once (each at most once), all or nothing.
+
+        Most entries of a step are single decoded tokens that stay inside their last page: those are settled
+        with whole-array operations, and only the requests that need a new page go through ``extend``."""
+        try:
+            slots = np.fromiter((self.slot_of[request] for request in requests), dtype=np.int64,
+                                count=len(requests))
+        except KeyError as missing:
+            raise CacheError(f"unknown request {missing.args[0]!r}") from None
+        counts = np.asarray(counts, dtype=np.int64)
+        if counts.shape != slots.shape:
+            raise CacheError("extend_many needs one count per request")
+        if slots.size == 0:
+            return
+        if (counts <= 0).any():
+            raise CacheError("extend needs a positive token count")
+        if len(set(requests)) != len(requests):
+            raise CacheError("a request can be extended only once at a time")
+        if self.pending[slots].any():
+            raise CacheError("the previous extension was not committed")
+        starts = self.lengths[slots].astype(np.int64)
+        ends = starts + counts
+        if (ends > self.max_model_len).any():
+            worst = requests[int(np.argmax(ends))]
+            raise CacheError(f"request {worst!r} would exceed the model's maximum length {self.max_model_len}")
+        # a table has a page for every committed position (released ones keep their place as -1)
+        crossing = np.flatnonzero(-(-ends // self.page_size) > -(-starts // self.page_size))
+        done: List[Hashable] = []
+        try:
+            for index in crossing.tolist():
+                self.extend(requests[index], int(counts[index]))
+                done.append(requests[index])
+        except CacheFull:
+            for request in reversed(done):          # last taken, first returned: the free list is as before
+                self.rollback(request)
+            raise
+        self.pending[slots] = counts
+
+    def commit_many(self, requests: Sequence[Hashable]) -> None:
+        """``commit`` for several requests at once."""
+        if any(group.need.window is not None for group in self.groups):
+            for request in requests:                # pages that a window has passed are released one by one
+                self.commit(request)
+            return
+        try:
+            slots = np.fromiter((self.slot_of[request] for request in requests), dtype=np.int64,
+                                count=len(requests))
+        except KeyError as missing:
+            raise CacheError(f"unknown request {missing.args[0]!r}") from None
+        if slots.size == 0:
+            return
+        pending = self.pending[slots]
+        if not pending.all():
+            raise CacheError("nothing to commit")
+        self.lengths[slots] += pending
+        self.pending[slots] = 0
+
     def rollback(self, request: Hashable) -> None:
         """Undo an ``extend`` that was not committed (the step failed)."""
         slot = self._slot(request)

@@ -143,29 +143,25 @@ class ModelRunner:
         self._check_vocabulary(tokens)
 
         admitted: List[Hashable] = []
-        extended: List[Hashable] = []
+        slot_of = cache.slot_of
         try:
-            for entry, count in zip(entries, counts.tolist()):
-                if entry.request not in cache:
-                    cache.admit(entry.request)
-                    admitted.append(entry.request)
-                if cache.length(entry.request) + count > self.max_model_len:
-                    # reference: src/model/paged_decoder.py:521-522
-                    raise StepError(f"request {entry.request!r} would pass the model's maximum length "
-                                    f"{self.max_model_len}")
-                cache.extend(entry.request, count)
-                extended.append(entry.request)
+            for request in requests:
+                if request not in slot_of:
+                    cache.admit(request)
+                    admitted.append(request)
+            slots = np.fromiter((slot_of[requests[source]] for source in order), dtype=np.int64, count=I)
+            starts = cache.lengths[slots].astype(np.int64)             # cached length of each laid-out item
+            beyond = np.flatnonzero(starts + counts[order] > self.max_model_len)
+            if beyond.size:
+                # reference: src/model/paged_decoder.py:521-522
+                raise StepError(f"request {requests[int(order[beyond[0]])]!r} would pass the model's maximum "
+                                f"length {self.max_model_len}")
+            cache.extend_many(requests, counts)                        # all or nothing
         except Exception:
-            for request in extended:
-                cache.rollback(request)
             for request in admitted:
                 cache.free(request)
             raise
         self._admitted_in_step = admitted
-
-        slot_of = cache.slot_of
-        slots = np.fromiter((slot_of[requests[source]] for source in order), dtype=np.int64, count=I)
-        starts = cache.lengths[slots].astype(np.int64)                 # cached length of each laid-out item
         batch = arrange_step(order, num_short_items, counts, tokens, slots, starts,
                              [entry.want for entry in entries], pad=pad, pad_short=self.PAD_SHORT,
                              pad_long=self.PAD_LONG, scratch_slot=cache.scratch_slot)
@@ -247,15 +243,7 @@ class ModelRunner:
         starts = cache.lengths[slots]
         if int(starts.max()) + 1 + extra_tokens > self.max_model_len:
             raise StepError(f"a request would pass the model's maximum length {self.max_model_len}")
-        extended: List[Hashable] = []
-        try:
-            for request in requests:
-                cache.extend(request, 1 + extra_tokens)
-                extended.append(request)
-        except Exception:
-            for request in extended:
-                cache.rollback(request)
-            raise
+        cache.extend_many(requests, np.full(I, 1 + extra_tokens, dtype=np.int64))      # all or nothing
         self._admitted_in_step = []
 
         layout, views, staging, host = self._stage(I, I, I)
@@ -355,8 +343,7 @@ class ModelRunner:
         except Exception:
             self._abandon(entries)
             raise
-        for entry in entries:
-            self.cache.commit(entry.request)
+        self.cache.commit_many([entry.request for entry in entries])
         self.steps += 1
         self.tokens_run += ctx.num_tokens
         expected = sum(len(entry.want) for entry in entries)
@@ -433,9 +420,7 @@ class ModelRunner:
                 done = self._step_events[0]
                 done.record()
         # the step is on its way: what follows runs on the host while the device works
-        commit = self.cache.commit
-        for request in requests:
-            commit(request)
+        self.cache.commit_many(requests)
         self.steps += steps
         self.tokens_run += steps * B
         if stage_next and steps == 1:

@@ -153,3 +153,76 @@ def test_state_slots_are_declared_per_layer():
     assert cache.state_needs[0].shape == (3, 4) and cache.group_of_layer == {1: 0}
     with pytest.raises(CacheError):
         CacheManager([KVNeed(1, 16)], [None], 12, 4, 2, 32)
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("window", [None, 7])
+def test_batched_extend_and_commit_equal_one_by_one(seed, window):
+    """``extend_many`` / ``commit_many`` leave the manager exactly as the same calls one by one do: same
+    pages in the same order, same tables, same lengths; and a batch that does not fit takes nothing."""
+    rng = random.Random(100 + seed)
+    batched = manager(pages=20, page=4, window=window, slots=6, max_len=48, mixed=window is not None)
+    single = manager(pages=20, page=4, window=window, slots=6, max_len=48, mixed=window is not None)
+    live = []
+    counter = 0
+    refused = 0
+    for _ in range(300):
+        action = rng.random()
+        if action < 0.2 and batched.free_slots:
+            name = f"r{counter}"; counter += 1
+            batched.admit(name); single.admit(name); live.append(name)
+        elif action < 0.9 and live:
+            chosen = rng.sample(live, rng.randint(1, len(live)))
+            counts = [1 if rng.random() < 0.6 else rng.randint(2, 9) for _ in chosen]
+            if any(single.length(name) + count > 48 for name, count in zip(chosen, counts)):
+                continue
+            free_before = [g.allocator.free_pages for g in batched.groups]
+            try:
+                batched.extend_many(chosen, counts)
+            except CacheFull:
+                refused += 1
+                assert [g.allocator.free_pages for g in batched.groups] == free_before    # all or nothing
+                assert not batched.pending.any()
+                batched.check_invariants()
+                continue
+            for name, count in zip(chosen, counts):
+                single.extend(name, count)
+            if rng.random() < 0.1:
+                for name in chosen:
+                    batched.rollback(name); single.rollback(name)
+            else:
+                batched.commit_many(chosen)
+                for name in chosen:
+                    single.commit(name)
+        elif live:
+            name = live.pop(rng.randrange(len(live)))
+            batched.free(name); single.free(name)
+        batched.check_invariants()
+        assert (batched.lengths == single.lengths).all() and (batched.pending == single.pending).all()
+        for g_batched, g_single in zip(batched.groups, single.groups):
+            assert g_batched.tables == g_single.tables
+            assert (g_batched.rows == g_single.rows).all()
+            assert g_batched.allocator._free == g_single.allocator._free
+    assert refused > 0                                   # the pool was small enough to run out
+
+
+def test_batched_extend_refuses_what_extend_refuses():
+    cache = manager(pages=8, page=4, slots=3, max_len=16)
+    cache.admit("a"); cache.admit("b")
+    with pytest.raises(CacheError, match="only once"):
+        cache.extend_many(["a", "a"], [1, 1])
+    with pytest.raises(CacheError, match="positive"):
+        cache.extend_many(["a", "b"], [1, 0])
+    with pytest.raises(CacheError, match="unknown request"):
+        cache.extend_many(["a", "zz"], [1, 1])
+    with pytest.raises(CacheError, match="maximum length"):
+        cache.extend_many(["a", "b"], [3, 17])
+    cache.extend_many(["a", "b"], [3, 5])
+    with pytest.raises(CacheError, match="not committed"):
+        cache.extend_many(["b"], [1])
+    cache.commit_many([])
+    cache.commit_many(["a", "b"])
+    assert cache.length("a") == 3 and cache.length("b") == 5
+    with pytest.raises(CacheError, match="nothing to commit"):
+        cache.commit_many(["a"])
+    cache.check_invariants()
