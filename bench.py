@@ -214,11 +214,15 @@ def main():
         import gc
 
         runs = []
+        # requests whose prompts ran in an earlier step are that many tokens ahead: where the context has room,
+        # everybody gets as many tokens more, so that nobody finishes inside the timed steps
+        head_start = -(-batch * args.prompt_len // 2048) + 1
+        spare = max(0, min(head_start, context_len - args.prompt_len - (warmup + k_steps + 2)))
         for _ in range(repeats):
             scheduler = engine.make_scheduler(strategy="orca", max_num_seqs=batch, max_num_batched_tokens=2048)
             for _ in range(batch):
                 scheduler.add_token_request(rng.integers(0, config.vocab_size, args.prompt_len).tolist(),
-                                            max_new_tokens=warmup + k_steps + 2)
+                                            max_new_tokens=warmup + k_steps + 2 + spare)
             while scheduler.waiting:
                 scheduler.step()                       # prefill (untimed)
             for _ in range(warmup):
