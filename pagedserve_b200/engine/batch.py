@@ -26,16 +26,21 @@ class StepEntry:
 
     def __post_init__(self):
         tokens = np.asarray(self.tokens)
-        if tokens.size and not np.issubdtype(tokens.dtype, np.integer):
+        if tokens.size and tokens.dtype.kind not in "iu":                  # signed or unsigned integers only
             raise ValueError("token ids must be integers")
-        self.tokens = tokens.astype(np.int64, copy=False).reshape(-1)      # kept as an array: prompts are long
-        self.want = [int(w) for w in self.want]
-        if self.tokens.size == 0:
+        if tokens.dtype != np.int64 or tokens.ndim != 1:
+            tokens = tokens.astype(np.int64, copy=False).reshape(-1)
+        self.tokens = tokens                                               # kept as an array: prompts are long
+        count = tokens.size
+        if count == 0:
             # reference: src/model/iteration.py:23-24
             raise ValueError("a step entry must contain at least one token")
-        for place in self.want:
-            if not (0 <= place < len(self.tokens)):
-                raise ValueError(f"wanted place {place} is outside the entry's {len(self.tokens)} tokens")
+        want = self.want
+        if type(want) is not list or any(type(place) is not int for place in want):
+            want = self.want = [int(w) for w in want]
+        for place in want:
+            if not (0 <= place < count):
+                raise ValueError(f"wanted place {place} is outside the entry's {count} tokens")
 
 
 def layout_order(counts: np.ndarray, long_entry: int):

@@ -139,3 +139,21 @@ def test_packed_sections_do_not_overlap_and_are_aligned():
         assert end <= next_start
     assert all(start % 4 == 0 for start, _ in spans)             # 16-byte sections: vector loads are legal
     assert spans[-1][1] <= layout.total
+
+
+def test_step_entry_checks_and_normalises():
+    entry = StepEntry("r", [5, 17, 3], (0, np.int32(2)))
+    assert entry.tokens.dtype == np.int64 and entry.tokens.tolist() == [5, 17, 3]
+    assert entry.want == [0, 2] and all(type(place) is int for place in entry.want)
+    assert StepEntry("r", np.asarray([[1, 2], [3, 4]], dtype=np.uint16)).tokens.tolist() == [1, 2, 3, 4]
+    assert StepEntry("r", np.int32(7)).tokens.tolist() == [7] and StepEntry("r", [7]).want == []
+    kept = np.arange(4, dtype=np.int64)
+    assert StepEntry("r", kept).tokens is kept                         # already in the kept form: no copy
+    with pytest.raises(ValueError, match="at least one token"):
+        StepEntry("r", [])
+    for bad in ([1.0, 2.0], [True, False], ["a"]):
+        with pytest.raises(ValueError, match="must be integers"):
+            StepEntry("r", bad)
+    for want in ([3], [-1], [0, 5]):
+        with pytest.raises(ValueError, match="outside the entry"):
+            StepEntry("r", [1, 2, 3], want)
