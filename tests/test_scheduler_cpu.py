@@ -208,3 +208,46 @@ def test_random_workloads_finish_without_leaks_whatever_the_limits(strategy, see
     assert sched.reserved_blocks == 0 and engine.cache.live_requests == 0
     assert engine.cache.free_pages() == engine.cache.total_pages()
     engine.cache.check_invariants()
+
+
+def _recorded_workloads():
+    import json
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scheduler_steps.json")
+    with open(path) as handle:
+        return json.load(handle)
+
+
+@pytest.mark.parametrize("name", sorted(_recorded_workloads()))
+def test_steps_equal_the_reference_schedulers(name):
+    """Every step holds the same requests, in the same order, with the same token counts and the same
+    entries producing logits as the reference's own scheduler made for this workload (recorded by
+    tests/golden/make_scheduler_golden.py): worst-case reservation against a pool that runs out,
+    head-of-line waiting, whole prompts (orca) or one portion beside the decodes (sarathi), release at the
+    end.  The token budget is left out of play here (the reference has none)."""
+    record = _recorded_workloads()[name]
+
+    class Engine(FakeEngine):
+        vocab_size = 1000
+        max_model_len = record["context"]
+
+    engine = Engine(pages=record["total_blocks"], page=record["block_size"], slots=record["max_batch_size"])
+    sched = Scheduler(engine, max_num_seqs=record["max_batch_size"], max_num_batched_tokens=10 ** 9,
+                      strategy=record["strategy"], prefill_chunk_size=record["prefill_chunk_size"],
+                      max_prefills_per_step=1)
+    assert sched.block_size == record["block_size"] and sched.total_blocks == record["total_blocks"]
+    for index, (prompt_len, new_tokens) in enumerate(record["requests"]):
+        assert sched.add_token_request([(index + place) % 1000 for place in range(prompt_len)],
+                                       max_new_tokens=new_tokens) == index
+    finished_after = {}
+    while sched.waiting or sched.active:
+        sched.step()
+        for request_id in sched.finished:
+            finished_after.setdefault(request_id, len(engine.steps))
+    ours = [[[request, count, bool(want)] for request, count, want in step] for step in engine.steps]
+    for number, (mine, theirs) in enumerate(zip(ours, record["steps"])):
+        assert mine == theirs, f"step {number} differs"
+    assert len(ours) == len(record["steps"])
+    assert [finished_after[index] for index in range(len(record["requests"]))] == record["finished_after_step"]
+    assert sched.reserved_blocks == 0 and engine.cache.free_pages() == record["total_blocks"]
