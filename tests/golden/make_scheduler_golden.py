@@ -8,7 +8,9 @@ It builds the reference's ``ContinuousBatchScheduler`` with its small random mod
 (reference: main.py:136-254, ``model_name="reference"``), submits token requests
 (reference: src/scheduler/orca_scheduler.py:85-117), and runs it to the end while noting for
 every step the batch that ``build_iteration_batch`` made (:171-219): request, number of
-tokens, and whether the entry produces a logits row.  The end-of-sequence rule is switched
+tokens, and whether the entry produces a logits row; and, from the reference's ``KVCacheManager``
+(src/model/kv_manager.py:115-127, 425-442), the ids of the pages each request was handed in that
+step.  The end-of-sequence rule is switched
 off on the scheduler object (as the reference's benchmarks do), so a request ends by its
 token limit alone and the record does not depend on the model's weights.  Workloads are
 chosen so that the page pool, not the batch size, is what makes requests wait: that is the
@@ -62,15 +64,22 @@ def record(reference_root, strategy, chunk, max_batch, pool_mib, requests):
         scheduler.add_token_request([(7 * index + 3 * place + 1) % vocabulary for place in range(prompt_len)],
                                     max_new_tokens=new_tokens)
     finished_after = {}
+    held = {}                  # request -> number of pages it held after the step before
+    pages = []                 # per step: [request, the page ids it was handed in this step], by request
     while scheduler.waiting or scheduler.active:
         scheduler.step()
         for request_id in scheduler.finished:
             finished_after.setdefault(request_id, len(steps))
+        tables = {request_id: list(info.block_ids) for request_id, info in scheduler.kv_manager.requests.items()}
+        pages.append([[request_id, table[held.get(request_id, 0):]] for request_id, table in sorted(tables.items())
+                      if len(table) > held.get(request_id, 0)])
+        held = {request_id: len(table) for request_id, table in tables.items()}
     return {
         "strategy": strategy, "prefill_chunk_size": chunk, "max_batch_size": max_batch,
         "block_size": scheduler.kv_manager.block_size, "total_blocks": scheduler.kv_manager.total_available_blocks,
         "context": context, "requests": [list(request) for request in requests], "steps": steps,
         "finished_after_step": [finished_after[index] for index in range(len(requests))],
+        "pages_handed_out": pages,
     }
 
 

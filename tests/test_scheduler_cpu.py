@@ -225,7 +225,8 @@ def test_steps_equal_the_reference_schedulers(name):
     entries producing logits as the reference's own scheduler made for this workload (recorded by
     tests/golden/make_scheduler_golden.py): worst-case reservation against a pool that runs out,
     head-of-line waiting, whole prompts (orca) or one portion beside the decodes (sarathi), release at the
-    end.  The token budget is left out of play here (the reference has none)."""
+    end; and every request is handed the same page ids as by the reference's cache manager.  The token budget
+    is left out of play here (the reference has none)."""
     record = _recorded_workloads()[name]
 
     class Engine(FakeEngine):
@@ -241,13 +242,21 @@ def test_steps_equal_the_reference_schedulers(name):
         assert sched.add_token_request([(index + place) % 1000 for place in range(prompt_len)],
                                        max_new_tokens=new_tokens) == index
     finished_after = {}
+    held, handed_out = {}, []
     while sched.waiting or sched.active:
         sched.step()
         for request_id in sched.finished:
             finished_after.setdefault(request_id, len(engine.steps))
+        tables = engine.cache.groups[0].tables
+        handed_out.append([[request_id, list(table[held.get(request_id, 0):])]
+                           for request_id, table in sorted(tables.items()) if len(table) > held.get(request_id, 0)])
+        held = {request_id: len(table) for request_id, table in tables.items()}
     ours = [[[request, count, bool(want)] for request, count, want in step] for step in engine.steps]
     for number, (mine, theirs) in enumerate(zip(ours, record["steps"])):
         assert mine == theirs, f"step {number} differs"
     assert len(ours) == len(record["steps"])
+    # and the cache manager hands out the very pages the reference's does (last freed, first reused)
+    for number, (mine, theirs) in enumerate(zip(handed_out, record["pages_handed_out"])):
+        assert mine == theirs, f"pages of step {number} differ"
     assert [finished_after[index] for index in range(len(record["requests"]))] == record["finished_after_step"]
     assert sched.reserved_blocks == 0 and engine.cache.free_pages() == record["total_blocks"]
