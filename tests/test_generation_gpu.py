@@ -46,6 +46,30 @@ def test_greedy_generation_equals_plain(which, strategy, chunk):
     engine.cache.check_invariants()
 
 
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_generation_equals_what_the_reference_generated(which):
+    """The workloads the two tiny configurations are quoted with, run by the reference's own scheduler, cache
+    and model on the CPU (recorded by tests/golden/make_golden.py): the float32 engine generates the very same
+    tokens under the same strategy, portion size and page size."""
+    import json
+    import os
+
+    from pagedserve_b200.engine.engine import generate
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"tiny_{which}_generated.json")
+    with open(path) as handle:
+        record = json.load(handle)
+    vocab = helpers.TINY[which][0]["vocab_size"]
+    assert record["block_size"] == helpers.TINY[which][2]
+    prompts = [helpers.random_tokens(vocab, length, seed=record["prompt_seed_offset"] + length)
+               for length in record["prompt_lengths"]]
+    engine = make_engine(which, "float32")
+    got = generate(engine, prompts, max_new_tokens=record["max_new_tokens"], strategy=record["strategy"],
+                   prefill_chunk_size=record["prefill_chunk_size"], max_num_seqs=4)
+    assert got == record["generated"]
+    assert engine.cache.live_requests == 0 and engine.cache.free_pages() == engine.cache.total_pages()
+
+
 def test_temperature_sampling_follows_the_keyed_noise():
     """Tiny B, mixed batch with 24-token portions beside decodes, 12 tokens at T = 0.8:
     every sampled token must (nearly) maximise logit/T + gumbel(seed, position, i) under the

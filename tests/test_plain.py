@@ -24,6 +24,19 @@ def test_plain_matches_reference_outputs(which):
     assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_plain_generates_what_the_reference_generated(which):
+    """Greedy tokens of each configuration's serving workload as the reference's own scheduler, paged cache
+    and chunked forward pass produced them on the CPU (tests/golden/make_golden.py)."""
+    with open(os.path.join(GOLDEN, f"tiny_{which}_generated.json")) as handle:
+        record = json.load(handle)
+    config, weights = helpers.plain_model(which)
+    vocab = helpers.TINY[which][0]["vocab_size"]
+    for length, want in zip(record["prompt_lengths"], record["generated"]):
+        prompt = helpers.random_tokens(vocab, length, seed=record["prompt_seed_offset"] + length)
+        assert plain_gpt2.generate(config, weights, prompt, record["max_new_tokens"]) == want
+
+
 def test_causality_and_prefix_property():
     """Logits at a position depend only on the tokens up to it."""
     config, weights = helpers.plain_model("a")
