@@ -101,15 +101,203 @@ class ClockSampler:
                 "sm_max_mhz": max(maxes) if maxes else None, "reasons": reasons, "samples": len(clocks)}
 
 
-def reference_arm(args):
-    """The unmodified reference from baseline/_ref, if it could be installed offline."""
+def _reference_tree():
+    """The folder that holds the unmodified reference (its ``main.py`` and ``src/``), or (None, why).
+
+    jainalphin/pagedserve is a script tree without setup.py or pyproject.toml, so ``pip install --target
+    baseline/_ref`` refuses it; a plain copy of the checkout stands in its place.  Where the copy is missing
+    and ``PAGEDSERVE_REFERENCE_SRC`` names a checkout, the copy is made now."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    reason = None
-    if not os.path.isdir(ref) or not os.listdir(ref):
-        reason = ("jainalphin/pagedserve has no setup.py/pyproject.toml: pip install --no-index --target "
-                  "baseline/_ref fails, and its GPT-2 loader needs a checkpoint download (no network)")
-    print(json.dumps({"impl": "reference", "unavailable": reason or "reference install is empty"}))
+    if not os.path.isfile(os.path.join(ref, "src", "model", "paged_decoder.py")):
+        source = os.environ.get("PAGEDSERVE_REFERENCE_SRC", "")
+        if not os.path.isfile(os.path.join(source, "src", "model", "paged_decoder.py")):
+            return None, ("baseline/_ref holds no copy of jainalphin/pagedserve (pip refuses the tree: neither "
+                          "setup.py nor pyproject.toml) and PAGEDSERVE_REFERENCE_SRC names no checkout")
+        import shutil
+
+        os.makedirs(ref, exist_ok=True)
+        shutil.copytree(os.path.join(source, "src"), os.path.join(ref, "src"), dirs_exist_ok=True)
+        shutil.copy(os.path.join(source, "main.py"), os.path.join(ref, "main.py"))
+    return ref, None
+
+
+def reference_arm(args):
+    """The same measurements on the unmodified reference: its own ``PagedDecoderLM`` with random weights at the
+    named layer sizes, its ``KVCacheManager``, ``PagedAttention`` and ``ContinuousBatchScheduler``
+    (reference: main.py:104-116, 215-254; benchmark.py:106-128; src/scheduler/orca_scheduler.py:85-117,
+    221-303), driven through ``add_token_request`` and ``step`` with the same seeded prompts, warm-up and step
+    count as this engine's arm.  Nothing of ``pagedserve_b200`` but the table of layer sizes is imported."""
+    ref, why = _reference_tree()
+    if ref is None:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    try:
+        result = _run_reference(args, ref)
+    except Exception as error:                                    # the arm must not take the driver down
+        message = " ".join(f"{type(error).__name__}: {error}".split())[:300]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference raised: {message}"}))
+        return 0
+    print(json.dumps(result))
     return 0
+
+
+def _run_reference(args, ref):
+    import importlib.util
+
+    import numpy as np
+    import torch
+
+    from pagedserve_b200.config.gpt2 import NAMED_CONFIGS          # layer sizes only: plain Python, no kernels
+
+    sys.path.insert(0, ref)
+    from src.model.kv_manager import KVCacheManager
+    from src.model.paged_attention import PagedAttention
+    from src.model.paged_decoder import PagedDecoderLM, TransformerConfig
+    from src.scheduler.orca_scheduler import ContinuousBatchScheduler
+
+    sizes = dict(NAMED_CONFIGS[args.model])
+    full_layers = sizes["n_layer"]
+    if args.layers:
+        sizes["n_layer"] = args.layers
+    hidden, heads, inner = sizes["n_embd"], sizes["n_head"], sizes["n_inner"] or 4 * sizes["n_embd"]
+    context_len, vocab = sizes["n_positions"], sizes["vocab_size"]
+    steps, warmup = args.steps, max(args.warmup, 3)
+    if args.prompt_len + warmup + steps + 2 > context_len:
+        steps = context_len - args.prompt_len - warmup - 2
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    on_gpu = torch.cuda.is_available()               # without a GPU the arm still runs (a dry run of its host side)
+    device = torch.device("cuda" if on_gpu else "cpu")
+    backend = "triton" if on_gpu and importlib.util.find_spec("triton") is not None else "torch"
+
+    class DeviceTimer:
+        """Milliseconds between ``start`` and ``stop`` on the device (CUDA events); wall clock without a GPU."""
+
+        def start(self):
+            if on_gpu:
+                self.events = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                self.events[0].record()
+            self.began = time.perf_counter()
+
+        def stop(self):
+            if on_gpu:
+                self.events[1].record()
+                torch.cuda.synchronize()
+            self.seconds = time.perf_counter() - self.began
+            return self.events[0].elapsed_time(self.events[1]) if on_gpu else self.seconds * 1e3
+    peaks = load_peaks()
+
+    torch.manual_seed(0)                                           # reference: benchmark.py:106-107
+    model = PagedDecoderLM(TransformerConfig(
+        vocab_size=vocab, hidden_size=hidden, num_layers=sizes["n_layer"], num_heads=heads,
+        head_dim=hidden // heads, mlp_hidden_size=inner, max_sequence_length=context_len,
+        activation_function="gelu_tanh", layer_norm_epsilon=sizes["layer_norm_epsilon"],
+        tie_word_embeddings=True, lm_head_bias=False))
+    model = model.to(device=device, dtype=dtype).eval()            # reference: main.py:133
+    model.enable_cuda_graphs = True                                # reference: main.py:193
+    max_batch = max(64, args.batch)
+    width = 2 if dtype == torch.bfloat16 else 4
+    block_bytes = 2 * sizes["n_layer"] * hidden * 16 * width
+    cache = KVCacheManager(block_size=16, total_memory=(max_batch * (context_len // 16) + 64) * block_bytes,
+                           tensor_dtype=dtype, device=device, num_layers=sizes["n_layer"], num_kv_heads=heads,
+                           head_dim=hidden // heads, cache_dtype=dtype)          # reference: main.py:214-223
+    attention = PagedAttention(kv_manager=cache, decode_attention_backend=backend)
+    rng = np.random.default_rng(0)
+    weight_bytes = sum(p.numel() * p.element_size() for name, p in model.named_parameters()
+                       if not name.startswith("position_embeddings"))
+    kv_bytes_per_token = 2 * sizes["n_layer"] * hidden * width
+
+    def make_scheduler(batch):
+        return ContinuousBatchScheduler(model_engine=model, max_batch_size=batch, tokenizer=None, kv_manager=cache,
+                                        paged_attn_manager=attention, eos_token_id=None,
+                                        scheduling_strategy="orca")
+
+    def measure_decode(batch, k_steps):
+        scheduler = make_scheduler(batch)
+        for _ in range(batch):
+            scheduler.add_token_request(rng.integers(0, vocab, args.prompt_len).tolist(),
+                                        max_new_tokens=warmup + k_steps + 2)
+        while scheduler.waiting:
+            scheduler.step()                                       # the prompts (untimed)
+        for _ in range(warmup):
+            scheduler.step()
+        timer, produced = DeviceTimer(), 0
+        with ClockSampler() as clocks:
+            timer.start()
+            for _ in range(k_steps):
+                produced += len(scheduler.step())
+            ms = timer.stop()
+        seconds = timer.seconds
+        _drain(scheduler)
+        mean_context = args.prompt_len + warmup + (k_steps + 1) / 2.0
+        return {"ms": ms, "tok_s": produced / (ms / 1e3), "e2e_tok_s": produced / seconds,
+                "e2e_ms_per_step": seconds * 1e3 / k_steps,
+                "bytes_per_step": weight_bytes + batch * mean_context * kv_bytes_per_token,
+                "clocks": clocks.summary()}
+
+    def _drain(scheduler):
+        while scheduler.waiting or scheduler.active:
+            scheduler.step()
+
+    def measure_prefill(tokens_total=2048, repeats=5):
+        prompt_len = min(1024, context_len - 1)
+        count = max(1, tokens_total // prompt_len)
+        times = []
+        for repeat in range(repeats + 3):
+            scheduler = make_scheduler(count)
+            for _ in range(count):
+                scheduler.add_token_request(rng.integers(0, vocab, prompt_len).tolist(), max_new_tokens=1)
+            timer = DeviceTimer()
+            timer.start()
+            scheduler.step()                                       # whole prompts in one iteration (Orca)
+            elapsed = timer.stop()
+            if repeat >= 3:
+                times.append(elapsed)
+            _drain(scheduler)
+        ms = statistics.median(times)
+        T = count * prompt_len
+        L = sizes["n_layer"]
+        gemm = 2.0 * T * L * (4 * hidden * hidden + 2 * hidden * inner) + 2.0 * count * hidden * vocab
+        flops = gemm + L * count * 4.0 * hidden * (prompt_len * (prompt_len + 1) / 2.0)
+        peak = peaks["bf16_tflops"] * 1e12 if dtype == torch.bfloat16 else 75e12
+        return {"value": T / (ms / 1e3), "tokens": T, "ms": ms, "frac": flops / (ms / 1e3) / peak,
+                "gflop": flops / 1e9}
+
+    with torch.inference_mode():
+        main_run = measure_decode(args.batch, steps)
+        result = {
+            "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (GPT-2 124M)",
+            "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": main_run["ms"] / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "fp32", "data": "synthetic",
+            "impl": "reference", "decode_attention_backend": backend,
+            "config": {
+                "model": args.model, "weights": "random(torch.manual_seed(0))", "n_layer": sizes["n_layer"],
+                "n_layer_full": full_layers, "n_embd": hidden, "n_head": heads, "n_inner": inner,
+                "vocab_size": vocab, "n_positions": context_len, "global_batch": args.batch,
+                "seq_len": context_len, "prompt_len": args.prompt_len, "generated": steps, "block_size": 16,
+                "parallelism": "single-gpu", "tokens": "uniform-random ids",
+                "l2": "working set per step exceeds L2 (no flush)", "peaks": peaks["source"],
+            },
+            "clocks": {k: main_run["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+            # every step of the reference builds its ids and positions on the host (int64), copies them and
+            # its decode metadata to the device, and reads the argmax back (reference:
+            # src/scheduler/orca_scheduler.py:214-219, 250)
+            "e2e": {"value": main_run["e2e_tok_s"], "unit": "tokens/s", "ms_per_step": main_run["e2e_ms_per_step"],
+                    "h2d_bytes_per_step": 2 * args.batch * 8, "d2h_bytes_per_step": args.batch * 8},
+            "gpu_launches": None,                                  # none of this repository's kernels run in this arm
+            "roofline": {"bound": "hbm", "achieved": main_run["bytes_per_step"] / (main_run["ms"] / steps / 1e3) / 1e9,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s"},
+        }
+        result["cuda_graphs"] = {key: value for key, value in model.cuda_graph_summary().items()
+                                 if key in ("captured_graphs", "graph_replays", "capture_failures")}
+        result["roofline"]["frac"] = result["roofline"]["achieved"] / result["roofline"]["peak"]
+        if not args.small and not args.skip_prefill:
+            result["prefill"] = measure_prefill()
+        if not args.small and not args.skip_points:
+            result["points"] = {"decode_b1": measure_decode(1, steps)["tok_s"],
+                                "decode_b64": measure_decode(64, steps)["tok_s"]}
+    return result
 
 
 def main():

@@ -72,7 +72,8 @@ def build_gpt2_spec(config: GPT2Config) -> ModelSpec:
         schedule=[],
         final_norm=PartSpec("layernorm", dict(norm, name="ln_f")),
         head=PartSpec("lm_head", dict(vocab_size=config.vocab_size, hidden_size=hidden,
-                                      tied=config.tie_word_embeddings, name="lm_head", init_std=std)),
+                                      tied=config.tie_word_embeddings, tied_to="wte.weight", name="lm_head",
+                                      init_std=std)),
         normalise_name=_normalise_name,
         checkpoint_name=_checkpoint_name,
     )

@@ -39,14 +39,16 @@ class TokenEmbedding(Embedding):
 class LMHead(Head):
     """logits = x table^T in float32, no bias; ``tied`` uses the token embedding's table
     (reference: src/model/paged_decoder.py:295-301; src/model/gpt2.py:42-43, 77-78).
-    params: vocab_size, hidden_size, tied, name, init_std."""
+    A tied model may still store the head: the copy must then equal the table it is tied to
+    (``tied_to``, the canonical name of that tensor), else loading fails.
+    params: vocab_size, hidden_size, tied, tied_to, name, init_std."""
 
     graph_safe = True
 
     def param_specs(self):
         p = self.params
         spec = ParamSpec(self._n(p["name"] + ".weight"), (p["vocab_size"], p["hidden_size"]), "table",
-                         optional=bool(p["tied"]))
+                         optional=bool(p["tied"]), same_as=p.get("tied_to") if p["tied"] else None)
         if p["tied"]:
             return [(spec, ("skip", 0.0))]
         return [(spec, ("normal", p.get("init_std", 0.02)))]

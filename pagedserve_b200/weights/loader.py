@@ -34,12 +34,13 @@ ROLES = ("matmul", "table", "vector", "keep32", "index")
 class WeightError(ValueError):
     """Missing, unexpected or wrongly shaped tensors; lists all of them."""
 
-    def __init__(self, message, missing=(), unexpected=(), wrong_shape=(), wrong_dtype=()):
+    def __init__(self, message, missing=(), unexpected=(), wrong_shape=(), wrong_dtype=(), not_tied=()):
         super().__init__(message)
         self.missing = list(missing)
         self.unexpected = list(unexpected)
         self.wrong_shape = list(wrong_shape)
         self.wrong_dtype = list(wrong_dtype)
+        self.not_tied = list(not_tied)        # (name, name it is tied to): stored copies that differ
 
 
 @dataclass(frozen=True)
@@ -49,6 +50,8 @@ class ParamSpec:
     role: str = "matmul"
     transpose: bool = False           # store [in,out] -> keep [out,in]
     optional: bool = False            # may be absent (e.g. a tied head)
+    same_as: Optional[str] = None     # canonical name of the tensor this one is tied to: a stored copy must
+                                      # equal it (reference: src/model/gpt2.py:42, 77-78 ties or copies the head)
 
     def __post_init__(self):
         if self.role not in ROLES:
@@ -105,7 +108,14 @@ def place_tensors(
                 wrong_dtype.append((origin[name], "integer", str(tensor.dtype)))
         elif not tensor.dtype.is_floating_point:
             wrong_dtype.append((origin[name], "floating point", str(tensor.dtype)))
-    if missing or unexpected or wrong_shape or wrong_dtype:
+    not_tied = []
+    for name, spec in wanted.items():
+        tensor, twin = canonical.get(name), canonical.get(spec.same_as) if spec.same_as else None
+        if tensor is None or twin is None or tensor.shape != twin.shape:
+            continue                          # absent, or already reported above
+        if not torch.equal(tensor.to(torch.float32), twin.to(torch.float32)):
+            not_tied.append((origin[name], origin[spec.same_as]))
+    if missing or unexpected or wrong_shape or wrong_dtype or not_tied:
         lines = [f"{source}: the tensors do not match the model"]
         if missing:
             lines.append(f"  missing ({len(missing)}): " + ", ".join(missing))
@@ -115,13 +125,15 @@ def place_tensors(
             lines.append(f"  wrong shape: {name}: expected {list(expected)}, got {list(got)}")
         for name, expected, got in wrong_dtype:
             lines.append(f"  wrong dtype: {name}: expected {expected}, got {got}")
-        raise WeightError("\n".join(lines), missing, unexpected, wrong_shape, wrong_dtype)
+        for name, twin in not_tied:
+            lines.append(f"  not tied: {name} differs from {twin}, to which the configuration ties it")
+        raise WeightError("\n".join(lines), missing, unexpected, wrong_shape, wrong_dtype, not_tied)
 
     placed: Dict[str, torch.Tensor] = {}
     for name, spec in wanted.items():
         tensor = canonical.get(name)
-        if tensor is None:
-            continue
+        if tensor is None or (spec.same_as and spec.same_as in canonical):
+            continue                          # absent, or an equal copy of a tensor that is placed anyway
         if spec.transpose:
             tensor = tensor.transpose(0, 1)
         target = _target_dtype(spec.role, tensor.dtype, compute_dtype)

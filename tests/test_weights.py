@@ -105,6 +105,28 @@ def test_untied_head_needs_its_tensor():
         model.load_tensors(tensors)
 
 
+def test_tied_head_stored_in_the_file_must_equal_the_table(tmp_path):
+    """reference: src/model/gpt2.py:42, 77-78 ties the head to the token table when tie_word_embeddings is set and
+    copies lm_head.weight otherwise; a file that stores a tied head with other numbers contradicts its configuration."""
+    config, model = cpu_model(helpers.TINY_A)
+    tensors = random_tensors(config, 0)
+    tensors["lm_head.weight"] = tensors["transformer.wte.weight"].clone()
+    model.load_tensors(tensors)                                        # an equal copy is accepted and not kept
+    assert "lm_head.weight" not in model.tensors and model.head.table is None
+    tensors["lm_head.weight"][3, 5] += 0.25
+    del tensors["transformer.ln_f.bias"]
+    with pytest.raises(WeightError) as caught:
+        model.load_tensors(tensors)
+    assert caught.value.not_tied == [("lm_head.weight", "transformer.wte.weight")]
+    assert caught.value.missing == ["ln_f.bias"]                       # still one error that lists everything
+    assert "not tied: lm_head.weight differs from transformer.wte.weight" in str(caught.value)
+    # the same file loads into the untied configuration, which then uses the stored head
+    untied_config, untied = cpu_model(dict(helpers.TINY_A, tie_word_embeddings=False))
+    tensors["transformer.ln_f.bias"] = torch.zeros(64)
+    untied.load_tensors(tensors)
+    assert not torch.equal(untied.head.table, untied.embedding.table)
+
+
 def test_random_weights_are_seeded_and_bf16_exact(tmp_path):
     config = GPT2Config(**helpers.TINY_A)
     a, b, c = random_tensors(config, 5), random_tensors(config, 5), random_tensors(config, 6)
