@@ -146,6 +146,13 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int first_chunk = lo >> chunk_log2, last_chunk = p >> chunk_log2;
     const int first_split = first_chunk / split_chunks, last_split = last_chunk / split_chunks;
     const int n_active = last_split - first_split + 1;
+    if (last_split >= n_splits) {
+        // The grid is too shallow for this token's newest keys (the caller's bound on the context was too
+        // low). Every CTA of the (token, head) sees the same: none computes, merges or touches a counter,
+        // the output stays unwritten and the status word says why.
+        if (status && tid == 0 && split == 0) atomicExch(status, 3);
+        return;
+    }
     const bool active = split >= first_split && split <= last_split;
     const bool by_cluster = cluster > 1 && n_active > 1;
     if (!active && !by_cluster) return;                                // no keys here and nobody waits for us
@@ -496,12 +503,8 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
 #define PS_DECODE_LAUNCH(KS)                                                                                          \
     {                                                                                                                \
         auto kernel = ps::paged_attention_decode_kernel<KS>;                                                         \
-        static size_t raised = 48 * 1024;                                                                            \
-        if (smem > raised) {                                                                                         \
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
-                return PS_ERR_LAUNCH;                                                                                \
-            raised = smem;                                                                                           \
-        }                                                                                                            \
+        static size_t raised[ps::MAX_DEVICES] = {0};                                                                 \
+        if (!ps::ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;                       \
         return ps::launch_pdl_cluster(kernel, grid, dim3(ps::DEC_THREADS), smem, s, cluster,                         \
                                       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,             \
                                       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride,        \
@@ -631,13 +634,28 @@ PS_EXPORT int ps_paged_attention_decode_noalloc(const void* q, int q_stride, voi
     int* counters = reinterpret_cast<int*>(base);
     float* part_ml = reinterpret_cast<float*>(static_cast<unsigned char*>(base) + PS_NOALLOC_MAX_ROWS * 4);
     float* part_acc = part_ml + PS_NOALLOC_MAX_PARTIALS * 2;
+    int* status = reinterpret_cast<int*>(static_cast<unsigned char*>(base) + PS_NOALLOC_STATUS_OFFSET);
     // the counters must start at zero whatever an earlier call left behind
     if (cudaMemsetAsync(counters, 0, (size_t)rows * sizeof(int), (cudaStream_t)stream) != cudaSuccess)
         return refuse(message, message_capacity, PS_ERR_LAUNCH, "clearing the counters failed (%lld rows, %lld)", rows, 0);
-    rc = ps_paged_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
-                                   block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window,
-                                   scale, split_tiles, n_splits, part_acc, part_ml, counters, stream);
+    rc = ps_paged_attention_decode_checked(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item,
+                                           positions, block_table, bt_stride, T, n_heads, n_kv_heads, head_dim,
+                                           page_size, window, scale, split_tiles, n_splits, part_acc, part_ml,
+                                           counters, status, stream);
     if (rc != PS_OK)
         return refuse(message, message_capacity, rc, "the attention kernel refused its arguments (status %lld, %lld)", rc, 0);
+    return PS_OK;
+}
+
+PS_EXPORT int ps_paged_attention_decode_noalloc_status(int* value, int clear, void* stream) {
+    if (!value) return PS_ERR_BAD_ARGUMENT;
+    void* base = nullptr;
+    int rc = noalloc_scratch(&base, nullptr, 0);
+    if (rc != PS_OK) return rc;
+    int* status = reinterpret_cast<int*>(static_cast<unsigned char*>(base) + PS_NOALLOC_STATUS_OFFSET);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(value, status, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return PS_ERR_LAUNCH;
+    if (clear && cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess) return PS_ERR_LAUNCH;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return PS_ERR_LAUNCH;
     return PS_OK;
 }

@@ -10,7 +10,7 @@
 // allocator of ours to ask; a latency-critical loop that is not allowed to touch the allocator at
 // all. For them this variant keeps the scratch in a fixed array that is part of the library image.
 //
-// What it costs. The array is PS_NOALLOC_SCRATCH_BYTES (about 4.3 MB) of device memory on every
+// What it costs. The array is PS_NOALLOC_SCRATCH_BYTES (4,243,712 bytes) of device memory on every
 // GPU that loads the library, held until the process exits, whether or not the entry point is used.
 //
 // Limits (beyond them the call is refused with PS_ERR_SCRATCH_LIMIT and a message, nothing runs):
@@ -28,6 +28,15 @@
 //     them yourself.
 //   * No cudaMalloc, cudaFree or allocating library routine is called, by this entry point or by
 //     anything it uses.
+//   * The split rule is the caller's: a split is split_tiles * 32 keys (a whole number of the
+//     kernel's chunks: 128 keys up to head size 64, 64 up to 128, 32 above, never fewer than a
+//     page), and n_splits must reach every token's newest key: n_splits >= floor(longest position
+//     / (split_tiles * 32)) + 1. A token that the grid does not reach gets no output.
+//   * The kernel reports what it cannot report through the return code (the grid did not reach a
+//     token: 3; a bounded wait inside the kernel ran out: 2) in one status word at the end of the
+//     fixed array. ps_paged_attention_decode_noalloc_status copies it to the host (and clears it
+//     if asked) on the given stream and waits for that stream; 0 means every call since the last
+//     clear was fine. It allocates nothing either.
 //
 // Arguments are those of ps_paged_attention_decode without the three scratch pointers, plus an
 // optional buffer that receives a readable message when the call is refused.
@@ -36,8 +45,10 @@
 #define PS_NOALLOC_MAX_ROWS 4096
 #define PS_NOALLOC_MAX_PARTIALS 4096
 #define PS_NOALLOC_MAX_HEAD_DIM 256
-#define PS_NOALLOC_SCRATCH_BYTES \
+// counters | (max, sum) pairs | partial accumulators | status word (padded to 256 bytes)
+#define PS_NOALLOC_STATUS_OFFSET \
     (PS_NOALLOC_MAX_ROWS * 4 + PS_NOALLOC_MAX_PARTIALS * 2 * 4 + PS_NOALLOC_MAX_PARTIALS * PS_NOALLOC_MAX_HEAD_DIM * 4)
+#define PS_NOALLOC_SCRATCH_BYTES (PS_NOALLOC_STATUS_OFFSET + 256)
 #define PS_ERR_SCRATCH_LIMIT 4
 #define PS_ERR_SETUP 5
 
@@ -51,6 +62,9 @@ int ps_paged_attention_decode_noalloc(const void* q, int q_stride, void* out, in
                                       int bt_stride, int T, int n_heads, int n_kv_heads, int head_dim,
                                       int page_size, int window, float scale, int split_tiles, int n_splits,
                                       void* stream, char* message, int message_capacity);
+
+// *value = the status word of the fixed array on the current device; clear != 0 also zeroes it.
+int ps_paged_attention_decode_noalloc_status(int* value, int clear, void* stream);
 
 #ifdef __cplusplus
 }

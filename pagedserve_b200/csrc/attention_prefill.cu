@@ -276,14 +276,8 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
     constexpr int RS = HD + 8;
     size_t smem = (size_t)(BQ + 8 * BKEY) * RS * 2;
     auto kernel = prefill_attention_kernel<HD>;
-    if (smem > 48 * 1024) {
-        static bool raised = false;
-        if (!raised) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                return PS_ERR_LAUNCH;
-            raised = true;
-        }
-    }
+    static size_t raised[MAX_DEVICES] = {0};
+    if (!ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
     return launch_pdl(kernel, dim3(max_blocks, n_heads), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride,
                       (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
                       page_stride, q_start, kv_len, block_table, bt_stride, first_item, n_items, n_heads, n_kv_heads,

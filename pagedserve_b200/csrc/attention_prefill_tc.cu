@@ -527,12 +527,8 @@ int launch(const void* q, int q_stride, int T, void* out, int out_stride, const 
     if (!make_map(&map_kv, pool, pool_rows, HD, HD, page_size)) return PS_ERR_LAUNCH;
     using L = Layout<HD, SPLIT>;
     auto kernel = prefill_attention_tc_kernel<HD, SPLIT>;
-    static bool raised = false;
-    if (!raised) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM) != cudaSuccess)
-            return PS_ERR_LAUNCH;
-        raised = true;
-    }
+    static size_t raised[MAX_DEVICES] = {0};
+    if (!ensure_dynamic_smem((const void*)kernel, (size_t)L::SMEM, raised)) return PS_ERR_LAUNCH;
     // heads vary fastest: the heaviest query blocks of all heads are scheduled first
     return launch_pdl(kernel, dim3(n_heads, max_blocks), dim3(L::THREADS), L::SMEM, stream, map_q, map_kv,
                       (__nv_bfloat16*)out, out_stride, q_start, kv_len, block_table, bt_stride, first_item, n_items,

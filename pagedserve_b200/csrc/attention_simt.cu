@@ -190,7 +190,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
 
 static int check_attention_sizes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return PS_ERR_BAD_ARGUMENT;
-    if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > ps::ATT_MAX_HD) return PS_ERR_UNSUPPORTED;
+    if (head_dim <= 0 || head_dim > ps::ATT_MAX_HD) return PS_ERR_UNSUPPORTED;      // any head size up to the limit
     if (page_size <= 0 || page_size > 64 || (page_size & (page_size - 1))) return PS_ERR_UNSUPPORTED;
     return PS_OK;
 }

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <cstring>
 #include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 #include <stdint.h>
 #include <stdlib.h>
 
@@ -118,10 +120,7 @@ __device__ __forceinline__ T* pdl_fresh(T* p) {
 // PAGEDSERVE_B200_PDL: unset or 1 = programmatic dependent launch for every kernel, 0 = for none; any other
 // value is a comma-separated list of pieces of kernel names that get it (for finding out which kernel gains
 // or misbehaves).
-inline bool pdl_enabled_for(const void* kernel) {
-    const char* env = getenv("PAGEDSERVE_B200_PDL");
-    if (!env || !*env || !strcmp(env, "1")) return true;
-    if (!strcmp(env, "0")) return false;
+inline bool pdl_name_listed(const void* kernel, const char* env) {
     const char* name = nullptr;
     if (cudaFuncGetName(&name, kernel) != cudaSuccess || !name) return false;
     const char* piece = env;
@@ -140,6 +139,36 @@ inline bool pdl_enabled_for(const void* kernel) {
     return false;
 }
 
+// The decision is per kernel (the launcher below is one template instance for all kernels of one signature,
+// so a static inside it would let the first kernel decide for the others).
+inline bool pdl_enabled_for(const void* kernel) {
+    static const char* const env = getenv("PAGEDSERVE_B200_PDL");
+    static const int mode = (!env || !*env || !strcmp(env, "1")) ? 1 : (!strcmp(env, "0") ? 0 : 2);
+    if (mode != 2) return mode == 1;
+    static std::mutex lock;
+    static std::unordered_map<const void*, bool> decided;
+    std::lock_guard<std::mutex> guard(lock);
+    auto found = decided.find(kernel);
+    if (found != decided.end()) return found->second;
+    const bool listed = pdl_name_listed(kernel, env);
+    decided.emplace(kernel, listed);
+    return listed;
+}
+
+// A kernel that needs more than 48 KB of dynamic shared memory has its limit raised once per device:
+// `raised` is the call site's own static table (one per kernel instantiation) of what each device allows.
+constexpr int MAX_DEVICES = 64;
+inline bool ensure_dynamic_smem(const void* kernel, size_t smem, size_t (&raised)[MAX_DEVICES]) {
+    if (smem <= 48 * 1024) return true;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return false;
+    if (smem <= raised[device]) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return false;
+    raised[device] = smem;
+    return true;
+}
+
 // Launch with the programmatic-stream-serialization attribute (kept when a stream is captured into a
 // CUDA graph, where it becomes a programmatic dependency edge).
 template <typename... KArgs, typename... Args>
@@ -153,7 +182,7 @@ inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     // Measured on B200 with the 64-kernel decode graph of GPT-2 124M at batch 8: 362 us per step with it,
     // 414 us without. (A first form, in which every kernel let its successor launch before its own wait, so
     // that many kernels sat resident at once, was slower than no early launch at all.)
-    static const bool enabled = pdl_enabled_for((const void*)kernel);
+    const bool enabled = pdl_enabled_for((const void*)kernel);
     cudaLaunchAttribute attribute[2];
     int count = 0;
     if (enabled) {

@@ -157,14 +157,8 @@ int launch_skinny(const void* A, int lda, const void* W, int ldw, const float* b
                   int M, int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
     size_t smem = (size_t)WARPS * 16 * 8 * MT * sizeof(float) + (size_t)8 * MT * sizeof(long long);
     auto kernel = gemm_skinny_kernel<MT, WARPS, UNROLL, TOut>;
-    if (smem > 48 * 1024) {
-        static bool raised = false;
-        if (!raised) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                return PS_ERR_LAUNCH;
-            raised = true;
-        }
-    }
+    static size_t raised[MAX_DEVICES] = {0};
+    if (!ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
     return launch_pdl(kernel, dim3((N + 15) / 16), dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)A, lda,
                       (const __nv_bfloat16*)W, ldw, bias, (TOut*)out, ldo, M, N, K, act, accumulate, kv);
 }
@@ -449,12 +443,8 @@ int launch_skinny_fused(const NormInput& in, const void* W, int ldw, const float
     size_t smem = skinny_fused_smem(MT, WARPS, K);
     auto kernel = gemm_skinny_fused_kernel<MT, WARPS, UNROLL, TOut>;
     if (smem > 200 * 1024) return PS_ERR_UNSUPPORTED;
-    static size_t raised = 48 * 1024;
-    if (smem > raised) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return PS_ERR_LAUNCH;
-        raised = smem;
-    }
+    static size_t raised[MAX_DEVICES] = {0};
+    if (!ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
     return launch_pdl(kernel, dim3((N + 15) / 16), dim3(WARPS * 32), smem, s, in, (const __nv_bfloat16*)W, ldw, bias,
                       (TOut*)out, ldo, M, N, K, act, accumulate, kv);
 }

@@ -498,13 +498,8 @@ int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUte
                   void* out, int ldo, int M, int N, int K, int act, int accumulate, int* status, const KvScatter& kv,
                   cudaStream_t stream) {
     auto kernel = gemm_tc_kernel<BN, TOut, TMA_OUT>;
-    static bool raised = false;
-    if (!raised) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Config<BN>::SMEM) !=
-            cudaSuccess)
-            return PS_ERR_LAUNCH;
-        raised = true;
-    }
+    static size_t raised[MAX_DEVICES] = {0};
+    if (!ensure_dynamic_smem((const void*)kernel, (size_t)Config<BN>::SMEM, raised)) return PS_ERR_LAUNCH;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     return launch_pdl(kernel, dim3(grid), dim3(THREADS), Config<BN>::SMEM, stream, map_a, map_w, map_out, bias,

@@ -26,6 +26,7 @@ nothing can be scheduled, ``step`` raises (reference: :223-225).
 from __future__ import annotations
 
 import math
+import numbers
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -93,8 +94,10 @@ class Scheduler:
         prompt = list(prompt_token_ids)
         if not prompt:
             raise ValueError("The prompt is empty")
-        if any(not isinstance(token, int) or isinstance(token, bool) for token in prompt):
+        # any integer type counts (a slice of a token array gives numpy integers), booleans do not
+        if any(not isinstance(token, numbers.Integral) or isinstance(token, bool) for token in prompt):
             raise ValueError("Prompt token IDs must be integers")
+        prompt = [int(token) for token in prompt]
         if min(prompt) < 0 or max(prompt) >= self.engine.vocab_size:
             raise ValueError("A prompt token is outside the model vocabulary")
         if len(prompt) + max_new_tokens > self.engine.max_model_len:
@@ -112,7 +115,9 @@ class Scheduler:
     add_request = add_token_request
 
     def _required_blocks(self, request: RequestState) -> int:
-        """Worst case pages of a request (reference: :119-122)."""
+        """Worst case pages of a request (reference: :119-122).  The last generated token is never run, so
+        only prompt + max_new_tokens - 1 positions are ever cached: at exact multiples of the page size this
+        reserves one page more than is used.  Kept, so that admission decisions equal the reference's."""
         return math.ceil((len(request.prompt_token_ids) + request.max_new_tokens) / self.block_size)
 
     # ------------------------------------------------------------------ decisions

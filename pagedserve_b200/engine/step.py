@@ -410,6 +410,9 @@ class ModelRunner:
                         graph.replay()
                         self.graph_replays += 1
                 else:
+                    # the positions move on the device: the bound that fixes the attention grid must cover
+                    # the last step's context, not only the first one's
+                    ctx.max_kv_len = min(self.max_model_len, ctx.max_kv_len + steps - 1)
                     for _ in range(steps):
                         self._forward_and_sample(ctx)
             except Exception:

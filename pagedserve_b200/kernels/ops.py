@@ -285,7 +285,9 @@ class Ops:
     FUSED_NORM_COLUMNS = 16 * 2 * 148   # and most output columns
 
     def _fused_norm_ok(self, a, w):
-        norm = a.norm
+        prologue = getattr(a.norm, "fused_prologue", lambda: None)()
+        if prologue is None:
+            return False                  # this norm cannot be written as the product's prologue
         # every CTA (16 output columns) recomputes the statistics: worth it only while the product is narrow
         rows = 8 if a.shape[0] <= 8 else 16 if a.shape[0] <= 16 else 32
         # the normed rows and the norm's scale and shift are staged in shared memory
@@ -295,12 +297,12 @@ class Ops:
         # than a norm kernel of its own
         return (self.dtype == torch.bfloat16 and a.shape[0] <= self.FUSED_NORM_ROWS
                 and w.shape[0] <= self.FUSED_NORM_COLUMNS
-                and type(norm).__name__ == "LayerNorm" and a.x.dtype == torch.float32
+                and a.x.dtype == torch.float32 and prologue.weight.dtype == torch.float32
                 and a.shape[1] % 8 == 0 and a.x.stride(0) % 4 == 0 and a.x.stride(1) == 1
                 and w.stride(0) % 8 == 0 and w.stride(1) == 1 and w.dtype == torch.bfloat16
                 and a.x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-                and norm.weight.data_ptr() % 16 == 0
-                and (norm.bias is None or norm.bias.data_ptr() % 16 == 0))
+                and prologue.weight.data_ptr() % 16 == 0
+                and (prologue.bias is None or prologue.bias.data_ptr() % 16 == 0))
 
     @staticmethod
     def _kv_arguments(kv, N):
@@ -329,7 +331,7 @@ class Ops:
         """out = act(norm(x)[rows] @ w.T + bias) with the norm computed inside the product's kernel
         (``a`` is a DeferredNorm); ``kv`` = (ctx, layer, q_width, kv_width, head_dim) also sends the key
         and value columns of the result straight into the pages."""
-        norm = a.norm
+        norm = a.norm.fused_prologue()
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
@@ -339,7 +341,7 @@ class Ops:
         self.launches += 1
         _check(self.fast.ps_gemm_skinny_fused(
             _ptr(a.x), a.x.stride(0), _ptr(a.rows), _ptr(norm.weight), _ptr(norm.bias),
-            float(norm.params["eps"]), 1 if norm.params.get("has_mean", True) else 0,
+            float(norm.eps), 1 if norm.has_mean else 0,
             _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N,
             K, dtype_code(out.dtype), _ACT_CODE[act], 1 if accumulate else 0,
             *kv_args, _stream()), "gemm_skinny_fused")
@@ -348,7 +350,7 @@ class Ops:
     def linear_qkv(self, a, w, bias, out, ctx, layer, q_width, kv_width, head_dim, scatter=True):
         """The packed q|k|v projection.  Returns True when the key and value columns were written into
         the pages by the product's own epilogue (then no separate cache write is needed)."""
-        if scatter and layer.k_pool is not None and self.dtype == torch.bfloat16:
+        if scatter and layer.k_pool is not None and self.dtype == torch.bfloat16 and head_dim % 16 == 0:
             if hasattr(a, "materialize") and self._fused_norm_ok(a, w):
                 self.linear_skinny_fused(a, w, bias, out, kv=(ctx, layer, q_width, kv_width, head_dim))
                 return True
@@ -562,7 +564,8 @@ class Ops:
         if write_cache:
             self.kv_append(k, v, ctx.token_item, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
                            layer.page_stride, n_kv_heads, head_dim, layer.page_size)
-        if self.dtype == torch.float32:
+        if self.dtype == torch.float32 or head_dim % 16 != 0:
+            # the CUDA-core kernel takes every head size; the tensor-core kernels want multiples of 16
             return self.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride,
                                              ctx.token_item, ctx.positions, layer.block_table, n_heads,
                                              n_kv_heads, head_dim, layer.page_size, window, scale)

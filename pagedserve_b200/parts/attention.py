@@ -37,8 +37,9 @@ class CausalSelfAttention(Mixer):
         p = self.params
         if p["n_heads"] % p["n_kv_heads"] != 0:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
-        if p["head_dim"] % 16 != 0 or p["head_dim"] > 256:
-            raise ValueError(f"head_dim {p['head_dim']} is not supported: multiples of 16 up to 256")
+        if not (0 < p["head_dim"] <= 256):
+            # multiples of 16 run on the tensor-core kernels in bfloat16; other sizes on the CUDA-core ones
+            raise ValueError(f"head_dim {p['head_dim']} is not supported: at most 256")
         self.q_width = p["n_heads"] * p["head_dim"]
         self.kv_width = p["n_kv_heads"] * p["head_dim"]
 

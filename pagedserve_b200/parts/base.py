@@ -108,12 +108,28 @@ class PositionEncoding(Part):
         return None
 
 
+@dataclass
+class NormPrologue:
+    """What a matrix product needs to compute a norm of the form ``(x - mean?) * rsqrt(var + eps) * weight
+    (+ bias)`` over the last axis inside its own kernel, in float32."""
+
+    weight: torch.Tensor                 # float32 [width]
+    bias: Optional[torch.Tensor]         # float32 [width] or None
+    eps: float
+    has_mean: bool                       # False: the RMS form
+
+
 class Norm(Part):
     category = "norm"
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
+
+    def fused_prologue(self) -> Optional[NormPrologue]:
+        """A norm that a consuming product may fold into its prologue says how here (any norm of the form
+        :class:`NormPrologue` describes, whatever its class); None: it has to run as its own kernel."""
+        return None
 
 
 class Mixer(Part):

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from pagedserve_b200.parts.base import Norm, register_part
+from pagedserve_b200.parts.base import Norm, NormPrologue, register_part
 from pagedserve_b200.weights.loader import ParamSpec
 
 
@@ -51,6 +51,9 @@ class LayerNorm(Norm):
 
     def defer(self, x, rows=None):
         return DeferredNorm(self, x, rows)
+
+    def fused_prologue(self):
+        return NormPrologue(self.weight, self.bias, float(self.params["eps"]), bool(self.params.get("has_mean", True)))
 
     def forward(self, x, out=None, rows=None, out_dtype=None):
         n_rows = rows.numel() if rows is not None else x.shape[0]

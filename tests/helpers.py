@@ -26,7 +26,20 @@ TINY_C = dict(n_layer=2, n_embd=192, n_head=3, n_inner=520, vocab_size=777, n_po
               layer_norm_epsilon=1e-5, activation_function="gelu_new")
 TINY_D = dict(n_layer=2, n_embd=256, n_head=2, n_inner=264, vocab_size=1031, n_positions=320,
               layer_norm_epsilon=1e-6, activation_function="gelu")
-TINY = {"a": (TINY_A, 0, 16), "b": (TINY_B, 1, 8), "c": (TINY_C, 2, 16), "d": (TINY_D, 3, 32)}     # config, seed, block size
+# A head size that is no multiple of 16 (GPT-2's config.json allows any n_embd / n_head): CUDA-core kernels.
+TINY_E = dict(n_layer=2, n_embd=100, n_head=5, n_inner=260, vocab_size=301, n_positions=96,
+              layer_norm_epsilon=1e-5, activation_function="gelu_new")
+# The layer sizes of the benchmarked models with two layers each, so that the kernels meet the widths they are
+# timed at: tails of 128-wide tiles at 1,600 and 4,800 columns, 25 heads, products too wide for the folded norm
+# (medium and XL, small vocabulary), and the 50,257-wide head at the 124M widths.
+REAL_MD2 = dict(n_layer=2, n_embd=1024, n_head=16, n_inner=4096, vocab_size=1003, n_positions=1024,
+                layer_norm_epsilon=1e-5, activation_function="gelu_new")
+REAL_XL2 = dict(n_layer=2, n_embd=1600, n_head=25, n_inner=6400, vocab_size=1003, n_positions=1024,
+                layer_norm_epsilon=1e-5, activation_function="gelu_new")
+REAL_SM2 = dict(n_layer=2, n_embd=768, n_head=12, n_inner=3072, vocab_size=50257, n_positions=1024,
+                layer_norm_epsilon=1e-5, activation_function="gelu_new")
+TINY = {"a": (TINY_A, 0, 16), "b": (TINY_B, 1, 8), "c": (TINY_C, 2, 16), "d": (TINY_D, 3, 32),     # config, seed, block size
+        "e": (TINY_E, 4, 8), "md2": (REAL_MD2, 5, 16), "xl2": (REAL_XL2, 6, 16), "sm2": (REAL_SM2, 7, 16)}
 
 _FOLDERS = {}
 
@@ -200,16 +213,40 @@ def collect(out, steps):
     return {name: np.stack(parts) for name, parts in rows.items()}
 
 
+_PLAIN_LOGITS = {}
+
+
 def plain_logits(which, sequences):
+    """The plain implementation's logits of whole sequences (kept: every replay mode asks for the same ones)."""
     config, weights = plain_model(which)
-    return {name: plain_gpt2.forward_logits(config, weights, tokens).numpy()
-            for name, tokens in sequences.items()}
+    out = {}
+    for name, tokens in sequences.items():
+        key = (which, tuple(tokens))
+        if key not in _PLAIN_LOGITS:
+            _PLAIN_LOGITS[key] = plain_gpt2.forward_logits(config, weights, tokens).numpy()
+        out[name] = _PLAIN_LOGITS[key]
+    return out
+
+
+def plain_rows(which, tokens, rows):
+    """The plain implementation's logits at ``rows`` of one whole sequence: the blocks run on every position,
+    the head only on the wanted ones (a vocabulary of 50,257 makes the head the larger part)."""
+    config, weights = plain_model(which)
+    ids = torch.as_tensor(list(tokens), dtype=torch.long)
+    hidden = plain_gpt2.embedding(weights, ids, torch.arange(ids.numel()))
+    for index in range(config["n_layer"]):
+        hidden = plain_gpt2.block(weights, index, hidden, config)
+    return plain_gpt2.lm_head(weights, config, hidden[torch.as_tensor(list(rows), dtype=torch.long)])
 
 
 # Tolerances, relative to the largest |logit| of the reference row set.
 #   float32 : every sum is float32; differences come from summation order only.
 #   bfloat16: activations are rounded to 8 bits of mantissa between the kernels.
 TOLERANCE = {"float32": 2e-5, "bfloat16": 3e-2}
+# Measured on the tiny and the real-width configurations: the worst element is off by up to 5e-3 x scale, the mean
+# element by up to 1e-3 x scale, and no top-1 differs where the plain model's lead exceeds 3.3e-3 x scale.
+BF16_MEAN_TOLERANCE = 3e-3
+TOP1_LEAD = {"float32": 2e-5, "bfloat16": 1e-2}
 
 
 def assert_close(got, want, dtype, what=""):
@@ -222,3 +259,15 @@ def assert_close(got, want, dtype, what=""):
         first = int(bad[:, 0].min())
         raise AssertionError(f"{what}: max error {error:.3e} exceeds {TOLERANCE[dtype]:.0e} x scale "
                              f"{scale:.3e}; first wrong position {first}")
+    # Where the plain model's best logit leads the second clearly, the engine must pick the same token (the
+    # elementwise bound alone only implies this for leads of twice the tolerance).
+    ordered = np.sort(want, axis=-1)
+    clear = (ordered[:, -1] - ordered[:, -2]) > TOP1_LEAD[dtype] * scale
+    wrong = np.flatnonzero(clear & (got.argmax(-1) != want.argmax(-1)))
+    assert wrong.size == 0, f"{what}: top-1 differs at position {int(wrong[0])} although the lead is clear"
+    if dtype == "bfloat16":
+        # one wrong key in one head moves a whole row by a little: the mean error over the rows is bounded
+        # far more tightly than the worst element
+        mean_error = float(np.abs(got.astype(np.float64) - want).mean())
+        assert mean_error <= BF16_MEAN_TOLERANCE * scale, \
+            f"{what}: mean error {mean_error:.3e} exceeds {BF16_MEAN_TOLERANCE:.0e} x scale {scale:.3e}"

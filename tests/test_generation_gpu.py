@@ -169,8 +169,7 @@ def test_command_line_runs():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graph_replay_equals_eager_and_device_loop_equals_stepwise(dtype):
-    """The captured decode step (a CUDA graph, or the persistent decode kernel where the model qualifies)
-    gives the logits of the eager step, and a run of several decode steps on the device gives the tokens
+    """The captured decode step (a CUDA graph) gives the logits of the eager step, and a run of several decode steps on the device gives the tokens
     of step-by-step generation."""
     from pagedserve_b200.engine.batch import StepEntry
 
@@ -209,6 +208,31 @@ def test_graph_replay_equals_eager_and_device_loop_equals_stepwise(dtype):
             scores = plain_gpt2.temperature_scores(logits, 0.9, 42, len(sequence))
             assert scores[drawn] >= scores.max() - 1e-4
             sequence.append(drawn)
+
+
+def test_eager_device_loop_crosses_a_key_chunk_boundary():
+    """Several decode steps in one call without CUDA graphs, bfloat16: the contexts pass 128 keys (the split
+    attention kernel's chunk at this head size) inside the call, so the bound that sizes the kernel's grid has
+    to cover the last step, not the first.  The tokens must be those of one call per step."""
+    from pagedserve_b200.engine.batch import StepEntry
+
+    vocab = helpers.TINY["b"][0]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=70 + n) for n in (121, 126, 60)]
+    runs = []
+    for steps_per_call in (1, 12):
+        engine = make_engine("b", "bfloat16", enable_cuda_graphs=False)
+        first = engine.step([StepEntry(i, p, [len(p) - 1]) for i, p in enumerate(prompts)])
+        tokens = [int(t) for t in first.argmax(-1).tolist()]
+        drawn = []
+        for _ in range(12 // steps_per_call):
+            out = engine.decode([StepEntry(i, [tokens[i]]) for i in range(3)], [0.0] * 3, [0] * 3,
+                                steps=steps_per_call)
+            drawn.append(out)
+            tokens = [int(t) for t in out[-1]]
+        engine.check_status()
+        runs.append(np.concatenate(drawn))
+        assert [engine.cache.length(i) for i in range(3)] == [len(p) + 12 for p in prompts]
+    assert np.array_equal(runs[0], runs[1])
 
 
 def test_a_step_staged_ahead_is_used_or_undone():

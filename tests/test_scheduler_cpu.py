@@ -1,6 +1,7 @@
 """The scheduler's decisions, with a fake engine (no GPU): admission, portions under a token
 budget, decode priority, finishing and freeing, and what happens when pages run out."""
 
+import numpy as np
 import pytest
 
 from pagedserve_b200.cache import CacheManager, KVNeed
@@ -115,9 +116,15 @@ def test_pages_run_out_requests_wait_and_nothing_is_preempted():
 def test_submit_checks_and_eos():
     engine = FakeEngine()
     sched = Scheduler(engine, eos_token_id=4)
-    for bad in ([], [1, 99], [1, -1], [1.5]):
+    for bad in ([], [1, 99], [1, -1], [1.5], [True, 2], [np.float32(1.0)]):
         with pytest.raises(ValueError):
             sched.add_token_request(bad, max_new_tokens=2)
+    # a slice of a token array is a list of numpy integers: accepted, and kept as plain ints
+    sliced = list(np.array([1, 2, 3], dtype=np.int64)[:2]) + [np.uint8(3)]
+    other = Scheduler(FakeEngine())
+    other.add_token_request(sliced, max_new_tokens=1)
+    assert other.waiting[0].prompt_token_ids == [1, 2, 3]
+    assert all(type(token) is int for token in other.waiting[0].prompt_token_ids)
     with pytest.raises(ValueError, match="context limit"):
         sched.add_token_request([1] * 60, max_new_tokens=10)
     with pytest.raises(ValueError):
