@@ -15,9 +15,12 @@ What is different here:
 * A page id addresses all cache layers of its group at once; the pool of a
   group is ``[pages, cache layers, 2 (k,v), kv heads, page size, head dim]``.
 * Every live request also holds a **slot**: an index into fixed-size
-  per-request state (its length, and one state tensor per layer that declares
-  a :class:`StateNeed`).  GPT-2 declares none; the slot mechanism is what a
-  mixer with a state of fixed size uses instead of pages.
+  per-request state: on the device its length, last token, sampling
+  parameters and block tables (:class:`pagedserve_b200.cache.slots.SlotStore`,
+  kept up to date by corrections that travel with each step), and one state
+  tensor per layer that declares a :class:`StateNeed`.  GPT-2 declares none;
+  the slot mechanism is what a mixer with a state of fixed size uses instead
+  of pages.
 * The protocol is host-side and has two phases per step: ``extend`` makes sure
   pages exist for the step's new positions (all or nothing), the kernels write
   them, ``commit`` advances the length and releases pages behind a window.
@@ -36,6 +39,8 @@ try:  # torch is only needed when pools live on a device
     import torch
 except ImportError:  # pragma: no cover
     torch = None
+
+from pagedserve_b200.cache.slots import SlotStore
 
 
 class CacheError(RuntimeError):
@@ -201,10 +206,15 @@ class CacheManager:
             CacheGroup(need, layers, page_size, num_pages, self.max_pages_per_request, dtype, device, scratch_pages)
             for need, layers in by_need.items()
         ]
-        for group in self.groups:
-            # the tables once more as one array by slot, so that a step gathers its rows in one operation
+        # the device copy of every slot's state: lengths, sampling parameters, block tables by slot
+        self.slots = SlotStore(max_slots, [self.max_pages_per_request] * len(self.groups))
+        for index, group in enumerate(self.groups):
+            # the tables once more as one array by slot: what the slot store's tables must equal
             group.rows = np.full((max_slots + 1, self.max_pages_per_request), -1, dtype=np.int32)
             group.rows[max_slots, :scratch_pages] = group.scratch_pages
+            self.slots.set_table(index, max_slots, 0, group.scratch_pages)
+        if device is not None:
+            self.slots.attach(device)
         self.group_of_layer: Dict[int, int] = {
             layer: index for index, group in enumerate(self.groups) for layer in group.cache_layers
         }
@@ -271,8 +281,7 @@ class CacheManager:
         for tensor in self.state.values():
             tensor[slot].zero_()
         for group in self.groups:
-            group.tables[request] = []
-            group.rows[slot] = -1
+            group.tables[request] = []          # the slot's row is all -1 since its last owner was freed
         return slot
 
     def extend(self, request: Hashable, new_tokens: int) -> None:
@@ -293,23 +302,29 @@ class CacheManager:
         needed = -(-end // self.page_size)
         taken: List[Tuple[CacheGroup, List[int], int]] = []
         try:
-            for group in self.groups:
+            for index, group in enumerate(self.groups):
                 table = group.tables[request]
                 old_len = len(table)
                 fresh: List[int] = []
-                taken.append((group, fresh, old_len))
+                taken.append((index, group, fresh, old_len))
                 if needed > old_len:
                     fresh.extend(group.allocator.allocate_many(needed - old_len))
-                    group.rows[slot, old_len:needed] = fresh
+                    self._set_rows(index, slot, old_len, fresh)
                     table.extend(fresh)
         except CacheFull:
-            for group, fresh, old_len in taken:
+            for index, group, fresh, old_len in taken:
                 del group.tables[request][old_len:]
-                group.rows[slot, old_len:] = -1
+                self._set_rows(index, slot, old_len, [-1] * len(fresh))
                 for page in reversed(fresh):
                     group.allocator.release(page)
             raise
         self.pending[slot] = new_tokens
+
+    def _set_rows(self, group_index: int, slot: int, first_column: int, pages) -> None:
+        """Write page ids into a slot's table row: the host array and, queued, the device's."""
+        if len(pages):
+            self.groups[group_index].rows[slot, first_column:first_column + len(pages)] = pages
+            self.slots.set_table(group_index, slot, first_column, pages)
 
     def extend_many(self, requests: Sequence[Hashable], counts: Sequence[int]) -> None:
         """``extend`` for several requests at once (each at most once), all or nothing.
@@ -375,13 +390,13 @@ class CacheManager:
         if not self.pending[slot]:
             return
         keep = -(-int(self.lengths[slot]) // self.page_size)
-        for group in self.groups:
+        for index, group in enumerate(self.groups):
             table = group.tables[request]
             for page in reversed(table[keep:]):
                 if page >= 0:
                     group.allocator.release(page)
+            self._set_rows(index, slot, keep, [-1] * (len(table) - keep))
             del table[keep:]
-            group.rows[slot, keep:] = -1
         self.pending[slot] = 0
 
     def commit(self, request: Hashable) -> int:
@@ -393,7 +408,7 @@ class CacheManager:
         self.lengths[slot] += self.pending[slot]
         self.pending[slot] = 0
         length = int(self.lengths[slot])
-        for group in self.groups:
+        for group_index, group in enumerate(self.groups):
             if group.need.window is None:
                 continue
             first = group.first_needed_position(length)
@@ -402,7 +417,7 @@ class CacheManager:
                 if table[index] >= 0:
                     group.allocator.release(table[index])
                     table[index] = -1
-                    group.rows[slot, index] = -1
+                    self._set_rows(group_index, slot, index, [-1])
         return length
 
     def free(self, request: Hashable) -> None:
@@ -410,14 +425,14 @@ class CacheManager:
         slot = self._slot(request)
         if self.pending[slot]:
             raise CacheError("cannot free a request with an uncommitted extension")
-        for group in self.groups:
+        for index, group in enumerate(self.groups):
             table = group.tables.pop(request)
             live = [page for page in table if page >= 0]
             if len(live) != len(set(live)):
                 raise CacheError("request holds a page twice")
             for page in live:
                 group.allocator.release(page)
-            group.rows[slot] = -1
+            self._set_rows(index, slot, 0, [-1] * len(table))
         del self.slot_of[request]
         self.lengths[slot] = 0
         self._free_slots.append(slot)
@@ -449,6 +464,14 @@ class CacheManager:
                 row = group.rows[self.slot_of[request]]
                 if row[:len(table)].tolist() != table or (row[len(table):] != -1).any():
                     raise CacheError(f"the table array of request {request!r} differs from its table")
+        for index, group in enumerate(self.groups):
+            base, width = self.slots.tables[index], self.slots.table_widths[index]
+            mirrored = self.slots.mirror[base:base + group.rows.size].reshape(group.rows.shape)
+            if not np.array_equal(mirrored, group.rows):
+                raise CacheError("the slot store's block tables differ from the host's")
+            free_rows = [slot for slot in self._free_slots]
+            if free_rows and (group.rows[free_rows] != -1).any():
+                raise CacheError("a free slot still has pages in its table row")
         slots = list(self.slot_of.values())
         if len(slots) != len(set(slots)) or len(slots) + len(self._free_slots) != self.max_slots:
             raise CacheError("slot bookkeeping is inconsistent")

@@ -116,7 +116,8 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               int window, float scale_log2, int chunk_keys, int split_chunks, int n_splits,
                               float* __restrict__ part_acc, float* __restrict__ part_ml,
                               int* __restrict__ counters, int* __restrict__ status,
-                              const int* __restrict__ q_start, const int* __restrict__ kv_len, int cluster) {
+                              const int* __restrict__ q_start, const int* __restrict__ kv_len, int cluster,
+                              const int* __restrict__ token_row) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // page_size, chunk_keys and the unit are powers of two: shifts and masks instead of divisions
     const int unit = min(page_size, chunk_keys >> 3);                                // keys per copy
@@ -160,7 +161,8 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int chunk_hi = active ? min(last_chunk, (split + 1) * split_chunks - 1) : 0;
 
     const int g = h / (n_heads / n_kv_heads);
-    const int* bt = block_table + (size_t)item * bt_stride;
+    // the token's block-table row: token_row[t] where the table is kept by request slot, else its item
+    const int* bt = block_table + (size_t)(token_row ? token_row[t] : item) * bt_stride;
     const uint32_t unit_bytes = (uint32_t)unit * head_dim * 2;
     if (tid == 0) {
         mbar_init(&bar, 1);
@@ -481,7 +483,7 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
                                    int n_kv_heads, int head_dim, int page_size, int window, float scale,
                                    int split_tiles, int n_splits, float* part_acc, float* part_ml, int* counters,
                                    int* status, void* stream, const int* q_start = nullptr,
-                                   const int* kv_len = nullptr, int cluster = 1) {
+                                   const int* kv_len = nullptr, int cluster = 1, const int* token_row = nullptr) {
     if (T <= 0) return PS_OK;
     if ((q_start == nullptr) != (kv_len == nullptr)) return PS_ERR_BAD_ARGUMENT;
     if (cluster > 1 && (cluster != n_splits || cluster > 8 || (cluster & (cluster - 1)))) return PS_ERR_BAD_ARGUMENT;
@@ -510,7 +512,8 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
                                       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride,        \
                                       token_item, positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim,   \
                                       page_size, window, scale * 1.4426950408889634f, chunk_keys, split_chunks,       \
-                                      n_splits, part_acc, part_ml, counters, status, q_start, kv_len, cluster);       \
+                                      n_splits, part_acc, part_ml, counters, status, q_start, kv_len, cluster,        \
+                                      token_row);                                                                     \
     }
     if (head_dim <= 64) PS_DECODE_LAUNCH(4)
     if (head_dim <= 128) PS_DECODE_LAUNCH(8)
@@ -546,10 +549,13 @@ PS_EXPORT int ps_paged_attention_decode_checked(const void* q, int q_stride, voi
 // thread-block cluster and merge through shared memory (no scratch needed); cluster <= 1: any n_splits, merged
 // through the scratch arrays. q_start / kv_len (per item, may both be null) tell which keys are older than
 // this step, so that a first chunk of such keys is fetched before the wait on the kernel before.
+// token_row (may be null): the block-table row of each token, where the table is kept by request slot
+// instead of by item.
 PS_EXPORT int ps_paged_attention_decode_ex(const void* q, int q_stride, void* out, int out_stride,
                                            const void* k_pool, const void* v_pool, long long page_stride,
-                                           const int* token_item, const int* positions, const int* block_table,
-                                           int bt_stride, const int* q_start, const int* kv_len, int T,
+                                           const int* token_item, const int* token_row, const int* positions,
+                                           const int* block_table, int bt_stride, const int* q_start,
+                                           const int* kv_len, int T,
                                            int n_heads, int n_kv_heads, int head_dim, int page_size, int window,
                                            float scale, int split_tiles, int n_splits, int cluster,
                                            float* part_acc, float* part_ml, int* counters, int* status,
@@ -557,7 +563,7 @@ PS_EXPORT int ps_paged_attention_decode_ex(const void* q, int q_stride, void* ou
     return launch_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
                                    block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window, scale,
                                    split_tiles, n_splits, part_acc, part_ml, counters, status, stream, q_start, kv_len,
-                                   cluster < 1 ? 1 : cluster);
+                                   cluster < 1 ? 1 : cluster, token_row);
 }
 
 // ------------------------------------------------------------------------------------------------

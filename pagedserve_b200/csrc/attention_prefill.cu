@@ -58,8 +58,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          int out_stride, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, long long page_stride,
                          const int* __restrict__ q_start, const int* __restrict__ kv_len,
-                         const int* __restrict__ block_table, int bt_stride, int first_item, int n_items,
-                         int n_heads, int n_kv_heads, int page_size, int window, float scale_log2) {
+                         const int* __restrict__ block_table, int bt_stride, const int* __restrict__ item_row,
+                         int first_item, int n_items, int n_heads, int n_kv_heads, int page_size, int window,
+                         float scale_log2) {
     constexpr int RS = HD + 8;                         // padded row, in elements
     constexpr int CH = HD / 8;                         // 16-byte pieces of a row
     constexpr int KS = HD / 16;                        // k steps over the head dim
@@ -90,7 +91,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int hi = pos0 + rows - 1;                                // last key any row may see
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
     const int kb_first = lo / BKEY, kb_last = hi / BKEY;
-    const int* bt = block_table + (size_t)item * bt_stride;
+    // the item's block-table row: item_row[item] where the table is kept by request slot, else the item itself
+    const int* bt = block_table + (size_t)(item_row ? item_row[item] : item) * bt_stride;
 
     // ---- Q tile
     for (int c = threadIdx.x; c < BQ * CH; c += THREADS) {
@@ -271,8 +273,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 template <int HD>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pool, const void* v_pool,
            long long page_stride, const int* q_start, const int* kv_len, const int* block_table, int bt_stride,
-           int first_item, int n_items, int max_blocks, int n_heads, int n_kv_heads, int page_size, int window,
-           float scale, cudaStream_t stream) {
+           const int* item_row, int first_item, int n_items, int max_blocks, int n_heads, int n_kv_heads,
+           int page_size, int window, float scale, cudaStream_t stream) {
     constexpr int RS = HD + 8;
     size_t smem = (size_t)(BQ + 8 * BKEY) * RS * 2;
     auto kernel = prefill_attention_kernel<HD>;
@@ -280,8 +282,8 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
     if (!ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
     return launch_pdl(kernel, dim3(max_blocks, n_heads), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride,
                       (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-                      page_stride, q_start, kv_len, block_table, bt_stride, first_item, n_items, n_heads, n_kv_heads,
-                      page_size, window, scale * 1.4426950408889634f);
+                      page_stride, q_start, kv_len, block_table, bt_stride, item_row, first_item, n_items, n_heads,
+                      n_kv_heads, page_size, window, scale * 1.4426950408889634f);
 }
 
 }  // namespace pf
@@ -290,9 +292,11 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
 // Attention for items [first_item, first_item + n_items) of the step. q_start[i] is the flat index of item
 // i's first token, kv_len[i] its length after the step. max_blocks >= sum over items of ceil(q_len / 64).
 // q and out point at row 0 of the step's flat token arrays. Head sizes: multiples of 16 up to 128.
+// item_row (may be null): the block-table row of each item, where the table is kept by request slot.
 PS_EXPORT int ps_prefill_attention(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                    const void* v_pool, long long page_stride, const int* q_start, const int* kv_len,
-                                   const int* block_table, int bt_stride, int first_item, int n_items,
+                                   const int* block_table, int bt_stride, const int* item_row, int first_item,
+                                   int n_items,
                                    int max_blocks, int n_heads, int n_kv_heads, int head_dim, int page_size,
                                    int window, float scale, void* stream) {
     if (n_items <= 0 || max_blocks <= 0) return PS_OK;
@@ -306,8 +310,8 @@ PS_EXPORT int ps_prefill_attention(const void* q, int q_stride, void* out, int o
 #define PS_PF_CASE(D)                                                                                              \
     case D:                                                                                                        \
         return ps::pf::launch<D>(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, q_start, kv_len,       \
-                                 block_table, bt_stride, first_item, n_items, max_blocks, n_heads, n_kv_heads,     \
-                                 page_size, window, scale, s);
+                                 block_table, bt_stride, item_row, first_item, n_items, max_blocks, n_heads,       \
+                                 n_kv_heads, page_size, window, scale, s);
     switch (head_dim) {
         PS_PF_CASE(16) PS_PF_CASE(32) PS_PF_CASE(48) PS_PF_CASE(64)
         PS_PF_CASE(80) PS_PF_CASE(96) PS_PF_CASE(112) PS_PF_CASE(128)

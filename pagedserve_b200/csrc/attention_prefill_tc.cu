@@ -190,7 +190,8 @@ __global__ void __launch_bounds__(64 + 128 * SPLIT, (HD == 64 && SPLIT == 1) ? 2
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ q_start,
                             const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride,
-                            int first_item, int n_items, int n_heads, int n_kv_heads, int page_size, int window,
+                            const int* __restrict__ item_row, int first_item, int n_items, int n_heads,
+                            int n_kv_heads, int page_size, int window,
                             float scale_log2, long long k_row_base, long long v_row_base, long long page_rows,
                             int* __restrict__ status) {
     using L = Layout<HD, SPLIT>;
@@ -229,7 +230,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int hi = pos0 + rows - 1;
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
     const int kb_first = lo / BKEY, kb_last = hi / BKEY;
-    const int* bt = block_table + (size_t)item * bt_stride;
+    // the item's block-table row: item_row[item] where the table is kept by request slot, else the item itself
+    const int* bt = block_table + (size_t)(item_row ? item_row[item] : item) * bt_stride;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -520,8 +522,8 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, int col
 template <int HD, int SPLIT>
 int launch(const void* q, int q_stride, int T, void* out, int out_stride, const void* pool, long long pool_rows,
            long long k_row_base, long long v_row_base, long long page_rows, const int* q_start, const int* kv_len,
-           const int* block_table, int bt_stride, int first_item, int n_items, int max_blocks, int n_heads,
-           int n_kv_heads, int page_size, int window, float scale, int* status, cudaStream_t stream) {
+           const int* block_table, int bt_stride, const int* item_row, int first_item, int n_items, int max_blocks,
+           int n_heads, int n_kv_heads, int page_size, int window, float scale, int* status, cudaStream_t stream) {
     CUtensorMap map_q, map_kv;
     if (!make_map(&map_q, q, T, n_heads * HD, q_stride, BQ)) return PS_ERR_LAUNCH;
     if (!make_map(&map_kv, pool, pool_rows, HD, HD, page_size)) return PS_ERR_LAUNCH;
@@ -531,9 +533,9 @@ int launch(const void* q, int q_stride, int T, void* out, int out_stride, const 
     if (!ensure_dynamic_smem((const void*)kernel, (size_t)L::SMEM, raised)) return PS_ERR_LAUNCH;
     // heads vary fastest: the heaviest query blocks of all heads are scheduled first
     return launch_pdl(kernel, dim3(n_heads, max_blocks), dim3(L::THREADS), L::SMEM, stream, map_q, map_kv,
-                      (__nv_bfloat16*)out, out_stride, q_start, kv_len, block_table, bt_stride, first_item, n_items,
-                      n_heads, n_kv_heads, page_size, window, scale * 1.4426950408889634f, k_row_base, v_row_base,
-                      page_rows, status);
+                      (__nv_bfloat16*)out, out_stride, q_start, kv_len, block_table, bt_stride, item_row, first_item,
+                      n_items, n_heads, n_kv_heads, page_size, window, scale * 1.4426950408889634f, k_row_base,
+                      v_row_base, page_rows, status);
 }
 
 }  // namespace pftc
@@ -544,10 +546,12 @@ int launch(const void* q, int q_stride, int T, void* out, int out_stride, const 
 // of this cache layer start at k_row_base and the V rows at v_row_base, kv head g at + g * page_size.
 // max_blocks >= sum over the items of ceil(q_len / 128). Head sizes 64 and 128, pages of 8..64 tokens.
 // row_threads: threads per query row, 1 or 2 (0: chosen here).
+// item_row (may be null): the block-table row of each item, where the table is kept by request slot.
 PS_EXPORT int ps_prefill_attention_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* pool,
                                       long long pool_rows, long long k_row_base, long long v_row_base,
                                       long long page_rows, const int* q_start, const int* kv_len,
-                                      const int* block_table, int bt_stride, int first_item, int n_items,
+                                      const int* block_table, int bt_stride, const int* item_row, int first_item,
+                                      int n_items,
                                       int max_blocks, int n_heads, int n_kv_heads, int head_dim, int page_size,
                                       int window, float scale, int row_threads, int* status, void* stream) {
     if (n_items <= 0 || max_blocks <= 0) return PS_OK;
@@ -567,8 +571,8 @@ PS_EXPORT int ps_prefill_attention_tc(const void* q, int q_stride, int T, void* 
     const bool two = row_threads ? row_threads == 2 : (long long)max_blocks * n_heads <= 148;
 #define PS_PFTC_LAUNCH(HD, SPLIT)                                                                                     \
     return ps::pftc::launch<HD, SPLIT>(q, q_stride, T, out, out_stride, pool, pool_rows, k_row_base, v_row_base,     \
-                                       page_rows, q_start, kv_len, block_table, bt_stride, first_item, n_items,       \
-                                       max_blocks, n_heads, n_kv_heads, page_size, window, scale, status, s)
+                                       page_rows, q_start, kv_len, block_table, bt_stride, item_row, first_item,      \
+                                       n_items, max_blocks, n_heads, n_kv_heads, page_size, window, scale, status, s)
     if (head_dim == 64) {
         if (two) PS_PFTC_LAUNCH(64, 2);
         PS_PFTC_LAUNCH(64, 1);

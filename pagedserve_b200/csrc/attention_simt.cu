@@ -9,6 +9,8 @@
 // keys max(0, p-window+1) .. p read from the request's pages through the block table;
 // it makes no difference whether the token is a decode token or part of a prompt
 // portion, so a position's result does not depend on how the prompt was cut.
+// token_item[t] is the row of block_table that holds the pages of token t's request: the
+// request's slot where the table is kept by slot, the token's item where it is built per step.
 //   s = (q.k) * scale, softmax in float32, o = p.v
 //   (reference: src/model/paged_attention.py:262-295; src/kernels/triton_paged_attention.py:219-331)
 // Keys are visited in tiles of 32 aligned to absolute positions; warp w takes tiles with

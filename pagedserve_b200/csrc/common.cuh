@@ -70,7 +70,7 @@ struct KvScatter {
     __nv_bfloat16* k_pool;
     __nv_bfloat16* v_pool;
     long long page_stride;
-    const int* token_item;
+    const int* token_row;     // per token: the row of block_table that holds its request's pages
     const int* positions;
     const int* block_table;
     int bt_stride;

@@ -70,7 +70,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
             // where a row's keys and values go: offset of (page, head 0, position in page, 0), or -1
             for (int m = threadIdx.x; m < M; m += WARPS * 32) {
                 const int p = kv.positions[m];
-                const int page = kv.block_table[(size_t)kv.token_item[m] * kv.bt_stride + p / kv.page_size];
+                const int page = kv.block_table[(size_t)kv.token_row[m] * kv.bt_stride + p / kv.page_size];
                 dst_s[m] = page >= 0 ? (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim : -1;
             }
         }
@@ -272,7 +272,7 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         // where this row's keys and values go: offset of (page, head 0, position in page, 0), or -1
         const int m = threadIdx.x;
         const int p = kv.positions[m];
-        const int page = kv.block_table[(size_t)kv.token_item[m] * kv.bt_stride + p / kv.page_size];
+        const int page = kv.block_table[(size_t)kv.token_row[m] * kv.bt_stride + p / kv.page_size];
         dst_s[m] = page >= 0 ? (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim : -1;
     }
     __syncthreads();

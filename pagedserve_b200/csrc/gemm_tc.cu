@@ -250,7 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int row = m0 + quarter * 32 + lane;
                 if (kv.k_pool && row < M && n0 + BN > kv.q_width) {
                     const int p = kv.positions[row];
-                    const int page = kv.block_table[(size_t)kv.token_item[row] * kv.bt_stride + p / kv.page_size];
+                    const int page = kv.block_table[(size_t)kv.token_row[row] * kv.bt_stride + p / kv.page_size];
                     if (page >= 0) kv_base = (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim;
                 }
             }

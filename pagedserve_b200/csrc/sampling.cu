@@ -93,32 +93,6 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     cluster_sync_all();                                  // the shares stay until they were read
 }
 
-// After a decode step that sampled on the device: feed the sampled token back as the next input,
-// move every request one position on, and append the tokens to the history of the run.
-__global__ void advance_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids,
-                               int* __restrict__ positions, int* __restrict__ kv_len,
-                               int* __restrict__ history, int* __restrict__ step_counter, int B, int max_steps,
-                               const int* status, int* status_copy) {
-    pdl_prologue();
-    sampled = pdl_fresh(sampled);
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    int step = *step_counter;
-    // every kernel of the step has ended: what they flagged travels with the tokens
-    const int flagged = (i == 0 && status && status_copy) ? *(volatile const int*)status : 0;
-    if (i < B) {
-        int token = sampled[i];
-        token_ids[i] = token;
-        positions[i] += 1;
-        kv_len[i] += 1;
-        if (step < max_steps) history[(size_t)step * B + i] = token;
-    }
-    __syncthreads();
-    if (i == 0) {
-        *step_counter = step + 1;
-        if (flagged) *status_copy = flagged;                  // the host zeroed the copy and zeroes it after a read
-    }
-}
-
 }  // namespace ps
 
 // position[r] + pos_offset keys the noise of row r (the index of the token being drawn).
@@ -132,15 +106,4 @@ PS_EXPORT int ps_sample(const float* logits, int ld, int R, int V, const float* 
     const int splits = V >= 8192 ? (R <= 256 ? 8 : (R <= 1024 ? 4 : 2)) : 1;
     return ps::launch_pdl_cluster(ps::sample_kernel<256>, dim3(R, 1, splits), dim3(256), 0, (cudaStream_t)stream,
                                   splits, logits, ld, V, temperature, seed, position, pos_offset, out);
-}
-
-// One block: B <= 1024.
-// status_copy (may be null): where the step's status flag is copied to, e.g. host memory mapped for the device.
-PS_EXPORT int ps_advance(const int* sampled, int* token_ids, int* positions, int* kv_len, int* history,
-                         int* step_counter, int B, int max_steps, const int* status, int* status_copy,
-                         void* stream) {
-    if (B <= 0) return PS_OK;
-    if (B > 1024) return PS_ERR_UNSUPPORTED;
-    return ps::launch_pdl(ps::advance_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, (cudaStream_t)stream, sampled,
-                          token_ids, positions, kv_len, history, step_counter, B, max_steps, status, status_copy);
 }

@@ -6,7 +6,8 @@ ids, position ids, flattened offsets and ``produces_output``.  Here an entry
 carries only the request, its next tokens and the places whose logits are
 wanted; positions follow from the request's cached length, and a "decode" is
 simply an entry of one token.  The device side is one packed int32 buffer
-(one host-to-device copy per step).
+(one host-to-device copy per step) of which the host fills only the part the
+device cannot derive from the per-request state it keeps by slot.
 """
 
 from __future__ import annotations
@@ -159,46 +160,65 @@ def _pad4(n: int) -> int:
 
 @dataclass
 class BatchLayout:
-    """Offsets (in int32 elements) of the sections of the packed metadata buffer."""
+    """Offsets (in int32 elements) of the sections of a step's packed metadata buffer.
+
+    The first part is what the host uploads: a header (``[0]`` steps the device has run since the upload,
+    which selects the row of the token history; ``[1]`` 1 if the step's token ids are the ones the device
+    sampled last; ``[2]`` number of corrections), the slot of each item, the first token of each item, the
+    wanted rows, the corrections of the slot store as (offset, value) pairs, and the token ids.  The rest is
+    written on the device by the step's first kernel from the slots' state: positions, the item and the
+    block-table row of each token, each item's length after the step and its sampling parameters."""
 
     num_tokens: int
     num_items: int
     num_rows: int
-    table_widths: Sequence[int]
-    token_ids: int = 0
-    positions: int = 0
-    token_item: int = 0
+    update_capacity: int = 0      # most corrections a step of this shape can carry
+    header: int = 0
     item_slot: int = 0
     q_start: int = 0
-    kv_len: int = 0
     logit_rows: int = 0
+    updates: int = 0              # (offset, value) pairs
+    token_ids: int = 0
+    uploaded: int = 0             # end of the part the host uploads
+    positions: int = 0
+    token_item: int = 0
+    token_slot: int = 0
+    kv_len: int = 0
     temperature: int = 0          # float32 bits, one per item
     seed: int = 0                 # 64-bit, two words per item
-    counter: int = 0              # one word, uploaded as 0: decode steps the device has run since the upload
-    tables: List[int] = field(default_factory=list)
     total: int = 0
+
+    HEADER_WORDS = 4
+    COUNTER, FED, NUM_UPDATES = 0, 1, 2
 
     def __post_init__(self):
         cursor = 0
-        for name, count in (("token_ids", self.num_tokens), ("positions", self.num_tokens),
-                            ("token_item", self.num_tokens), ("item_slot", self.num_items),
-                            ("q_start", self.num_items + 1), ("kv_len", self.num_items),
-                            ("logit_rows", max(self.num_rows, 1)), ("temperature", self.num_items),
-                            ("seed", 2 * self.num_items), ("counter", 1)):
+        for name, count in (("header", self.HEADER_WORDS), ("item_slot", self.num_items),
+                            ("q_start", self.num_items + 1), ("logit_rows", max(self.num_rows, 1)),
+                            ("updates", 2 * self.update_capacity), ("token_ids", self.num_tokens)):
             setattr(self, name, cursor)
             cursor += _pad4(count)
-        self.tables = []
-        for width in self.table_widths:
-            self.tables.append(cursor)
-            cursor += _pad4(self.num_items * width)
+        self.uploaded = cursor
+        for name, count in (("positions", self.num_tokens), ("token_item", self.num_tokens),
+                            ("token_slot", self.num_tokens), ("kv_len", self.num_items),
+                            ("temperature", self.num_items), ("seed", 2 * self.num_items)):
+            setattr(self, name, cursor)
+            cursor += _pad4(count)
         self.total = cursor
+        # what the kernels that open and close a step are told of the layout
+        self.words = np.asarray([self.num_tokens, self.num_items, self.header, self.item_slot, self.q_start,
+                                 self.updates, self.update_capacity, self.token_ids, self.positions,
+                                 self.token_item, self.token_slot, self.kv_len, self.temperature, self.seed],
+                                dtype=np.int32)
+
+    @property
+    def counter(self) -> int:
+        return self.header + self.COUNTER
 
 
 class HostBatch:
-    """Host-side (numpy) view of a step, for parts that need host logic and for tests.
-
-    The arrays are views of the step's pinned staging buffer: they hold while the step runs and are
-    overwritten a few steps later."""
+    """Host-side (numpy) view of a step, for parts that need host logic and for tests: the same numbers that
+    the step's first kernel derives on the device."""
 
     def __init__(self, token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows, requests):
         self.token_ids = token_ids
@@ -215,9 +235,12 @@ class StepContext:
     """Everything a part may read during one step.
 
     Device tensors (int32): ``token_ids[T]``, ``positions[T]``, ``token_item[T]`` (index of the
-    entry a token belongs to), ``item_slot[I]``, ``q_start[I+1]`` (first token of each entry),
-    ``kv_len[I]`` (the request's length after this step), ``logit_rows[R]`` (flat token index of
-    each wanted place), ``block_tables[g]`` (``[I, max pages]`` per cache group; -1 = no page).
+    entry a token belongs to), ``token_slot[T]`` (slot of the token's request: the row of its block tables),
+    ``item_slot[I]``, ``q_start[I+1]`` (first token of each entry), ``kv_len[I]`` (the request's length
+    after this step), ``logit_rows[R]`` (flat token index of each wanted place), ``block_tables[g]``
+    (``[slots + 1, max pages]`` per cache group, indexed by SLOT; -1 = no page).  Everything but
+    ``token_ids`` (unless fed back), ``item_slot``, ``q_start`` and ``logit_rows`` is written by the step's
+    first kernel (``ModelRunner.begin``), so it holds once that kernel has run.
     Items are laid out short entries first (``num_short_items`` items, ``num_short_tokens`` tokens), then
     the prompt portions of ``LONG_ENTRY`` or more tokens; ``logit_rows`` keeps the caller's order.
     ``status`` is a device int32 that kernels set non-zero on bad input (checked after the step).
@@ -242,9 +265,11 @@ class StepContext:
         self.num_short_tokens = layout.num_tokens if num_short_tokens is None else num_short_tokens
         self.num_long_blocks = num_long_blocks      # 64-query blocks of the long entries
         views = views if views is not None else DeviceViews(layout, device_buffer)
+        self.views = views
         self.token_ids = views.token_ids
         self.positions = views.positions
         self.token_item = views.token_item
+        self.token_slot = views.token_slot
         self.item_slot = views.item_slot
         self.q_start = views.q_start
         self.kv_len = views.kv_len
@@ -252,7 +277,7 @@ class StepContext:
         self.temperature = views.temperature
         self.seed = views.seed
         self.step_counter = views.step_counter
-        self.block_tables = views.block_tables
+        self.block_tables = cache.slots.table_views
         self.decode_only = (layout.num_tokens == layout.num_items)
 
 
@@ -263,9 +288,11 @@ class DeviceViews:
     def __init__(self, layout: BatchLayout, device_buffer: torch.Tensor):
         T, I, R = layout.num_tokens, layout.num_items, layout.num_rows
         buf = device_buffer
+        self.meta = buf
         self.token_ids = buf[layout.token_ids:layout.token_ids + T]
         self.positions = buf[layout.positions:layout.positions + T]
         self.token_item = buf[layout.token_item:layout.token_item + T]
+        self.token_slot = buf[layout.token_slot:layout.token_slot + T]
         self.item_slot = buf[layout.item_slot:layout.item_slot + I]
         self.q_start = buf[layout.q_start:layout.q_start + I + 1]
         self.kv_len = buf[layout.kv_len:layout.kv_len + I]
@@ -273,7 +300,3 @@ class DeviceViews:
         self.temperature = buf[layout.temperature:layout.temperature + I].view(torch.float32)
         self.seed = buf[layout.seed:layout.seed + 2 * I].view(torch.int64)
         self.step_counter = buf[layout.counter:layout.counter + 1]
-        self.block_tables = [
-            buf[offset:offset + I * width].view(I, width)
-            for offset, width in zip(layout.tables, layout.table_widths)
-        ]

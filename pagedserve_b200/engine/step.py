@@ -76,7 +76,7 @@ class ModelRunner:
         self.device = torch.device(device)
         self.vocab_size = model.spec.vocab_size
         self.max_model_len = model.spec.max_model_len
-        self.table_widths = [group.max_pages_per_request for group in cache.groups]
+        self.slots = cache.slots              # per-request state on the device, corrected by each step's upload
         self._capacity = 0
         self._device_buffer = None
         self._staging = []
@@ -84,8 +84,10 @@ class ModelRunner:
         self._turn = 0
         self.ops = model.env.ops
         self._status = self.ops.status_flag(self.device)      # one flag for every kernel of the model's steps
-        self._grow(BatchLayout(max_step_tokens, min(max_step_tokens, cache.max_slots),
-                               min(max_step_tokens, 4 * cache.max_slots), self.table_widths).total)
+        self._resync_pinned = None           # staging of a whole-store copy, made when one is first needed
+        self._needs_resync = False
+        self._grow(self._layout(max_step_tokens, min(max_step_tokens, cache.max_slots),
+                                min(max_step_tokens, 4 * cache.max_slots)).total)
         self.steps = 0
         self.tokens_run = 0
         self.enable_cuda_graphs = enable_cuda_graphs and model.graph_safe
@@ -108,6 +110,14 @@ class ModelRunner:
         self._capture_stream = None       # made at the first capture
         self._graph_pool = None
         self._ramp = np.arange(cache.max_slots + 2, dtype=np.int32)
+
+    def _layout(self, T: int, I: int, R: int) -> BatchLayout:
+        """The layout of a step shape.  Room for corrections: a page id per page the step's tokens can start,
+        in every group, and per item a length and the sampling parameters; a step with more (many requests
+        freed at once) copies the whole store instead."""
+        page = self.cache.page_size
+        capacity = len(self.cache.groups) * (-(-T // page) + I) + 4 * I + 8
+        return BatchLayout(T, I, R, capacity)
 
     def _grow(self, needed: int) -> None:
         if needed <= self._capacity:
@@ -167,26 +177,15 @@ class ModelRunner:
                              pad_long=self.PAD_LONG, scratch_slot=cache.scratch_slot)
         T, I, R = batch.num_tokens, batch.num_items, batch.num_rows
         layout, views, staging, host = self._stage(T, I, R)
-
-        def section(offset, values):
-            view = host[offset:offset + len(values)]
-            view[:] = values
-            return view
-
-        token_ids = section(layout.token_ids, batch.token_ids)
-        positions = section(layout.positions, batch.positions)
-        token_item = section(layout.token_item, batch.token_item)
-        item_slot = section(layout.item_slot, batch.item_slot)
-        q_start = section(layout.q_start, batch.q_start)
-        kv_len = section(layout.kv_len, batch.kv_len)
-        logit_rows = section(layout.logit_rows, batch.logit_rows)
-        for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
-            cache.table_rows(group_index, batch.item_slot, host[offset:offset + I * width].reshape(I, width))
-
-        host[layout.counter] = 0
+        # where the device's idea of a request's length differs from the host's, a correction goes up
+        self.slots.set_lengths(slots, starts)
+        self._fill(layout, host, batch.item_slot, batch.q_start, batch.logit_rows, batch.token_ids, fed=0)
         self._upload(layout, staging)
-        host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
-                               [requests[source] for source in order])
+        self.slots.device_advanced(slots, counts[order])
+        as32 = lambda values: np.asarray(values, dtype=np.int32)
+        host_batch = HostBatch(as32(batch.token_ids), as32(batch.positions), as32(batch.token_item),
+                               as32(batch.item_slot), as32(batch.q_start), as32(batch.kv_len),
+                               as32(batch.logit_rows), [requests[source] for source in order])
         laid_counts = np.diff(batch.q_start)
         ctx = StepContext(layout, self._device_buffer, host_batch, cache, self._status, int(laid_counts.max()),
                           int(batch.kv_len.max()), batch.num_short_items, batch.num_short_tokens,
@@ -194,11 +193,49 @@ class ModelRunner:
         ctx.real_logit_rows = batch.real_rows
         return ctx
 
+    def _fill(self, layout: BatchLayout, host: np.ndarray, item_slot, q_start, logit_rows, token_ids, fed: int):
+        """Write the uploaded part of a step into its staging buffer; the queued corrections of the slot store
+        go along (or, if there are more than the shape has room for, the whole store is copied first)."""
+        I = layout.num_items
+        host[layout.item_slot:layout.item_slot + I] = item_slot
+        host[layout.q_start:layout.q_start + I + 1] = q_start
+        host[layout.logit_rows:layout.logit_rows + len(logit_rows)] = logit_rows
+        if token_ids is not None:
+            host[layout.token_ids:layout.token_ids + layout.num_tokens] = token_ids
+        if self._needs_resync or self.slots.pending > layout.update_capacity:
+            self._resync()
+        offsets, values = self.slots.drain()
+        count = len(offsets)
+        if count > layout.update_capacity:                # cannot happen: pending bounds the drained count
+            raise StepError("more slot corrections than the step has room for")
+        pairs = host[layout.updates:layout.updates + 2 * count].reshape(count, 2)
+        pairs[:, 0] = offsets
+        pairs[:, 1] = values
+        header = host[layout.header:layout.header + layout.HEADER_WORDS]
+        header[layout.COUNTER] = 0
+        header[layout.FED] = fed
+        header[layout.NUM_UPDATES] = count
+        header[3] = 0
+        self._drained = offsets
+
+    def _resync(self) -> None:
+        """Copy the whole slot store to the device: after a failed step (what the device applied is unknown),
+        or when more corrections wait than a step carries. The lengths are the host's."""
+        cache, slots = self.cache, self.slots
+        slots.mirror[slots.len:slots.len + cache.max_slots] = cache.lengths
+        words = slots.take_all()
+        if self._resync_pinned is None:
+            self._resync_pinned = torch.empty(slots.size, dtype=torch.int32).pin_memory()
+        self._resync_pinned.numpy()[:] = words
+        self.ops.copy_h2d(slots.store, self._resync_pinned.data_ptr(), slots.size * 4)
+        torch.cuda.current_stream().synchronize()         # the pinned copy may be overwritten by the next one
+        self._needs_resync = False
+
     def _stage(self, T: int, I: int, R: int):
         """The layout of a step shape, its device views, and the pinned staging buffer of this turn."""
         shape = self._shapes.get((T, I, R))
         if shape is None:
-            layout = BatchLayout(T, I, R, self.table_widths)
+            layout = self._layout(T, I, R)
             self._grow(layout.total)
             if len(self._shapes) >= 1024:
                 self._shapes.clear()
@@ -210,16 +247,21 @@ class ModelRunner:
         self._staging_turn = turn
         return layout, views, self._staging[turn], self._staging_numpy[turn]
 
-    def _upload(self, layout: BatchLayout, staging: torch.Tensor, record: bool = True, first: int = 0) -> None:
-        """The step's one host-to-device copy.  ``record=False``: the caller synchronises the stream before
-        it returns, so the staging buffer needs no event of its own.  ``first``: the element the copy starts
-        at (a step launched ahead leaves out its token ids, which the device has fed back itself)."""
-        nbytes = (layout.total - first) * 4
-        self.ops.copy_h2d(self._device_buffer[first:] if first else self._device_buffer,
-                          self._staging_ptr[self._staging_turn] + first * 4, nbytes)
+    def _upload(self, layout: BatchLayout, staging: torch.Tensor, record: bool = True,
+                with_tokens: bool = True) -> None:
+        """The step's one host-to-device copy: header, slots, item starts, wanted rows and corrections, and
+        the token ids unless the device has fed them back itself (``with_tokens=False``).  ``record=False``:
+        the caller synchronises the stream before it returns, so the staging buffer needs no event."""
+        if with_tokens:
+            words = layout.token_ids + layout.num_tokens
+        else:
+            count = int(self._staging_numpy[self._staging_turn][layout.header + layout.NUM_UPDATES])
+            words = layout.updates + 2 * count
+        self.ops.copy_h2d(self._device_buffer, self._staging_ptr[self._staging_turn], words * 4)
         if record:
             self._staging_events[self._staging_turn].record()
-        self.h2d_bytes = nbytes
+        self.h2d_bytes = words * 4
+        self._drained = None                               # the corrections are on their way
 
     def _prepare_single_tokens(self, requests, tokens, extra_tokens: int, sampling) -> StepContext:
         """``prepare`` for a step in which every request brings one token and wants its logits: the same
@@ -247,39 +289,24 @@ class ModelRunner:
         self._admitted_in_step = []
 
         layout, views, staging, host = self._stage(I, I, I)
-        token_ids = host[layout.token_ids:layout.token_ids + I]
-        positions = host[layout.positions:layout.positions + I]
-        token_item = host[layout.token_item:layout.token_item + I]
-        item_slot = host[layout.item_slot:layout.item_slot + I]
-        q_start = host[layout.q_start:layout.q_start + I + 1]
-        kv_len = host[layout.kv_len:layout.kv_len + I]
-        logit_rows = host[layout.logit_rows:layout.logit_rows + I]
-        ramp = self._ramp[:I + 1]
-        if tokens is not None:
-            token_ids[:] = tokens
-        positions[:] = starts
-        token_item[:] = ramp[:I]
-        item_slot[:] = slots
-        q_start[:] = ramp
-        np.add(starts, 1, out=kv_len)
-        logit_rows[:] = ramp[:I]
+        slots_store = self.slots
+        slots_store.set_lengths(slots, starts)
         if sampling is not None:
-            temperatures, seeds = sampling
-            host[layout.temperature:layout.temperature + I].view(np.float32)[:] = temperatures
-            try:
-                seed_words = np.asarray(seeds, dtype=np.int64).view(np.uint64)
-            except OverflowError:
-                seed_words = np.array([int(seed) & 0xFFFFFFFFFFFFFFFF for seed in seeds], dtype=np.uint64)
-            host[layout.seed:layout.seed + 2 * I].view(np.uint64)[:] = seed_words
-        host[layout.counter] = 0
-        for group_index, (offset, width) in enumerate(zip(layout.tables, layout.table_widths)):
-            cache.table_rows(group_index, slots, host[offset:offset + I * width].reshape(I, width))
+            slots_store.set_sampling(slots, sampling[0], sampling[1])
+        ramp = self._ramp[:I + 1]
+        self._fill(layout, host, slots, ramp, ramp[:I], tokens, fed=0 if tokens is not None else 1)
         if tokens is not None:
             self._upload(layout, staging, record=False)
-        host_batch = HostBatch(token_ids, positions, token_item, item_slot, q_start, kv_len, logit_rows,
-                               list(requests))
-        return StepContext(layout, self._device_buffer, host_batch, cache, self._status, 1,
-                           int(kv_len.max()), I, I, 0, views=views)
+            slots_store.device_advanced(slots, 1 + extra_tokens)
+        kv_len = starts + 1
+        token_ids = np.asarray(tokens, dtype=np.int32) if tokens is not None else np.zeros(I, dtype=np.int32)
+        host_batch = HostBatch(token_ids, starts.astype(np.int32), ramp[:I], slots.astype(np.int32), ramp,
+                               kv_len.astype(np.int32), ramp[:I], list(requests))
+        ctx = StepContext(layout, self._device_buffer, host_batch, cache, self._status, 1,
+                          int(kv_len.max()), I, I, 0, views=views)
+        ctx.slots = slots
+        ctx.drained = self._drained                        # corrections staged but not yet uploaded
+        return ctx
 
     def _check_vocabulary(self, tokens: np.ndarray) -> None:
         low, high = int(tokens.min()), int(tokens.max())
@@ -303,11 +330,15 @@ class ModelRunner:
             return None                       # no room or no length left: the real call will say so
         staged = _StagedStep(list(requests), list(temperatures), list(seeds), ctx, self._staging_turn)
         graph = self._graphs.get((ctx.num_items, "sample")) if launch_half is not None else None
-        if graph is not None:
+        if graph is not None and not self.cache.state:
+            # (a step that is launched and then dropped leaves its pages unread, but state of fixed size in
+            # the slots would have been moved on by it: models with such state are never launched ahead)
             layout = ctx.layout
             # the step's tokens go to the half of the history that the step before it does not use
             self._staging_numpy[staged.turn][layout.counter] = launch_half
-            self._upload(layout, self._staging[staged.turn], record=True, first=layout.positions)
+            self._upload(layout, self._staging[staged.turn], record=True, with_tokens=False)
+            self.slots.device_advanced(ctx.slots, 1)
+            ctx.drained = None
             graph.replay()
             self.graph_replays += 1
             staged.event = self._step_events[launch_half]
@@ -319,6 +350,8 @@ class ModelRunner:
     def _drop_staged(self) -> None:
         staged, self._staged = self._staged, None
         if staged is not None:
+            if staged.ctx.drained is not None:             # its corrections never went up: queue them again
+                self.slots.requeue(staged.ctx.drained)
             for request in staged.requests:
                 self.cache.rollback(request)
 
@@ -327,6 +360,7 @@ class ModelRunner:
             self.cache.rollback(entry.request)
         for request in self._admitted_in_step:
             self.cache.free(request)
+        self._needs_resync = True                           # how far the device got with the step is unknown
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one step; returns float32 logits ``[R, V]`` (R may be 0)."""
@@ -339,7 +373,7 @@ class ModelRunner:
             elif self.enable_cuda_graphs:
                 logits = self._run_mixed_step(ctx)
             else:
-                logits = self.model.forward(ctx)
+                logits = self._forward(ctx)
         except Exception:
             self._abandon(entries)
             raise
@@ -390,9 +424,15 @@ class ModelRunner:
                 ahead = staged
             else:
                 self._check_vocabulary(tokens)
+                layout = ctx.layout
+                host = self._staging_numpy[staged.turn]
+                host[layout.token_ids:layout.token_ids + layout.num_tokens] = tokens
+                host[layout.header + layout.FED] = 0
                 ctx.host.token_ids[:] = tokens
                 self._staging_turn = staged.turn
-                self._upload(ctx.layout, self._staging[staged.turn], record=False)
+                self._upload(layout, self._staging[staged.turn], record=False)
+                self.slots.device_advanced(ctx.slots, 1)
+                ctx.drained = None
         else:
             if staged is not None:
                 self._staged = staged
@@ -418,6 +458,7 @@ class ModelRunner:
             except Exception:
                 for request in requests:
                     self.cache.rollback(request)
+                self._needs_resync = True
                 raise
             if stage_next and steps == 1 and self.enable_cuda_graphs:
                 done = self._step_events[0]
@@ -440,14 +481,23 @@ class ModelRunner:
             self._staged.fed_tokens = result[0]
         return result
 
+    def begin(self, ctx: StepContext) -> None:
+        """The step's first kernel: apply the uploaded corrections to the slot store and derive the per-step
+        arrays (positions, token -> item and slot, lengths after the step, sampling parameters) from it."""
+        self.ops.step_begin(self.slots, ctx.layout, ctx.views.meta, self._status)
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        self.begin(ctx)
+        return self.model.forward(ctx)
+
     def _forward_and_sample(self, ctx: StepContext) -> torch.Tensor:
-        logits = self.model.forward(ctx)
+        logits = self._forward(ctx)
         B = ctx.num_items
         sampled = self._sampled[:B]
         # the token drawn now will sit at position (input position + 1)
         self.ops.sample(logits, ctx.temperature, ctx.seed, ctx.positions, sampled, pos_offset=1)
-        self.ops.advance(sampled, ctx.token_ids, ctx.positions, ctx.kv_len, self._history, ctx.step_counter,
-                         self.MAX_DEVICE_STEPS, status=self._status, status_index=self._status_index)
+        self.ops.step_end(self.slots, ctx.layout, ctx.views.meta, sampled, self._history, self.MAX_DEVICE_STEPS,
+                          status=self._status, status_index=self._status_index)
         return logits
 
     def _run_mixed_step(self, ctx: StepContext) -> torch.Tensor:
@@ -467,7 +517,7 @@ class ModelRunner:
             return graph.logits[:rows].clone()
         seen = self._shape_seen.get(key, 0) + 1
         self._shape_seen[key] = seen
-        logits = self.model.forward(ctx)[:rows]
+        logits = self._forward(ctx)[:rows]
         if seen < self.MIXED_SHAPE_SIGHTINGS:
             if len(self._shape_seen) > 4096:
                 self._shape_seen.clear()
@@ -475,7 +525,7 @@ class ModelRunner:
         if len(self._graphs) >= self.MAX_GRAPHS:
             self._graphs.pop(next(iter(self._graphs)))
         launches_before = self.ops.launches
-        captured, static_logits = self._capture(lambda: self.model.forward(ctx))
+        captured, static_logits = self._capture(lambda: self._forward(ctx))
         self._graphs[key] = _DecodeGraph(captured, static_logits, self.ops.launches - launches_before)
         return logits
 
@@ -514,10 +564,10 @@ class ModelRunner:
         if kind == "sample":
             self._forward_and_sample(ctx)
         else:
-            warm = self.model.forward(ctx)
+            warm = self._forward(ctx)
         launches_before = self.ops.launches
         captured, logits = self._capture(
-            lambda: self._forward_and_sample(ctx) if kind == "sample" else self.model.forward(ctx))
+            lambda: self._forward_and_sample(ctx) if kind == "sample" else self._forward(ctx))
         graph = _DecodeGraph(captured, logits, self.ops.launches - launches_before)
         self._graphs[key] = graph
         if kind == "logits":
@@ -538,4 +588,5 @@ class ModelRunner:
             self._status.zero_()
             self._history.array[self._status_index] = 0
             self.ops.reset_after_fault()
+            self._needs_resync = True
             raise StepError(f"a kernel reported bad input or gave up waiting (status {flag})")

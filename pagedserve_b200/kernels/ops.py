@@ -77,7 +77,8 @@ _SIGNATURES = {
         "ps_kv_append": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P],
         "ps_paged_attention_simt": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
-        "ps_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P],
+        "ps_step_begin": [_P, _P, _P, _P, _P, _P],
+        "ps_step_end": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P],
         "ps_host_alloc_mapped": [_L, _P, _P],
         "ps_host_free": [_P],
         "ps_copy_h2d": [_P, _P, _L, _P],
@@ -89,15 +90,16 @@ _SIGNATURES = {
                                  _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_paged_attention_decode_checked": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                               _F, _I, _I, _P, _P, _P, _P, _P],
-        "ps_paged_attention_decode_ex": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
+        "ps_paged_attention_decode_ex": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                          _I, _I, _F, _I, _I, _I, _P, _P, _P, _P, _P],
-        "ps_prefill_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+        "ps_prefill_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F,
+                                 _P],
     },
     "tc": {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
         "ps_gemm_tc_qkv": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
-        "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
-                                    _I, _F, _I, _P, _P],
+        "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
+                                    _I, _I, _F, _I, _P, _P],
     },
 }
 
@@ -310,7 +312,7 @@ class Ops:
         if kv is None:
             return (None, None, 0, None, None, None, 0, N, 0, 1, 1)
         ctx, layer, q_width, kv_width, head_dim = kv
-        return (_ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride, _ptr(ctx.token_item),
+        return (_ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride, _ptr(ctx.token_slot),
                 _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
                 q_width, kv_width, head_dim, layer.page_size)
 
@@ -385,7 +387,7 @@ class Ops:
         _check(self._tc.ps_gemm_tc_qkv(
             _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
             _ptr(self.status_flag(a.device)), _ptr(layer.k_pool), _ptr(layer.v_pool), layer.page_stride,
-            _ptr(ctx.token_item), _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
+            _ptr(ctx.token_slot), _ptr(ctx.positions), _ptr(layer.block_table), layer.block_table.stride(0),
             q_width, kv_width, head_dim, layer.page_size, _stream()), "gemm_tc_qkv")
         return out
 
@@ -473,13 +475,15 @@ class Ops:
     def paged_attention_decode(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
                                n_heads, n_kv_heads, head_dim, page_size, window, scale, max_kv_len,
                                target_ctas=1184, status=None, q_start=None, kv_len=None, merge="global",
-                               largest_cluster=8):
+                               largest_cluster=8, token_row=None):
         """Split-key attention for few query tokens (bfloat16).  ``max_kv_len`` bounds the context of
         every token in the call; it fixes the grid, so a CUDA graph passes the model's maximum.
         ``q_start`` / ``kv_len`` (the step's per-item arrays) let the kernel fetch keys older than this step
         before the kernel that precedes it has finished.  ``merge``: "global" (the splits of a token and head
         merge through scratch in global memory) or "cluster" (they are a thread-block cluster and merge
-        through shared memory; falls back to "global" where more than ``largest_cluster`` splits pay)."""
+        through shared memory; falls back to "global" where more than ``largest_cluster`` splits pay).
+        ``block_table`` rows are indexed by ``token_row[t]`` (a table kept by request slot) or, without it, by
+        ``token_item[t]``."""
         T = q.shape[0]
         _require(q, "q", torch.bfloat16)
         _require(out, "out", torch.bfloat16)
@@ -504,17 +508,19 @@ class Ops:
         self.launches += 1
         _check(self.fast.ps_paged_attention_decode_ex(
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
-            page_stride, _ptr(token_item), _ptr(positions), _ptr(block_table),
+            page_stride, _ptr(token_item), _ptr(token_row), _ptr(positions), _ptr(block_table),
             block_table.stride(0), _ptr(q_start), _ptr(kv_len), T, n_heads, n_kv_heads, head_dim,
             page_size, window or 0, scale, split_tiles, n_splits, cluster,
             _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(status), _stream()), "paged_attention_decode")
         return out
 
     def prefill_attention(self, q, out, k_pool, v_pool, page_stride, q_start, kv_len, block_table, first_item,
-                          n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale):
+                          n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale,
+                          item_row=None):
         """Tensor-core causal attention of prompt portions (bfloat16): items ``first_item ..`` of the step,
         ``max_blocks`` >= the number of 64-query blocks they make up.  ``q`` / ``out`` are the step's flat
-        token arrays (row 0 = token 0)."""
+        token arrays (row 0 = token 0).  ``item_row``: the block-table row of each item (a table kept by request
+        slot); without it item i uses row i."""
         _require(q, "q", torch.bfloat16)
         _require(out, "out", torch.bfloat16)
         if head_dim > 128:
@@ -522,7 +528,7 @@ class Ops:
         self.launches += 1
         _check(self.fast.ps_prefill_attention(
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
-            page_stride, _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0),
+            page_stride, _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), _ptr(item_row),
             first_item, n_items, max_blocks, n_heads, n_kv_heads,
             head_dim, page_size, window or 0, scale, _stream()),
             "prefill_attention")
@@ -535,7 +541,7 @@ class Ops:
 
     def prefill_attention_tc(self, q, out, pool, cache_layer_local, q_start, kv_len, block_table, first_item,
                              n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                             status=None, row_threads=0):
+                             status=None, row_threads=0, item_row=None):
         """tcgen05 causal attention of prompt portions (bfloat16, head size 64 or 128).  ``pool`` is the cache
         group's whole pool ``[pages, layers, 2, kv heads, page size, head dim]``; ``cache_layer_local`` the
         layer's index inside it; ``max_blocks`` >= the number of 128-query blocks of the items.
@@ -553,8 +559,9 @@ class Ops:
         _check(self._tc.ps_prefill_attention_tc(
             _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(pool), pages * page_rows,
             (cache_layer_local * 2) * rows_per_tensor, (cache_layer_local * 2 + 1) * rows_per_tensor, page_rows,
-            _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), first_item, n_items, max_blocks,
-            n_heads, n_kv_heads, head_dim, page_size, window or 0, scale, row_threads, _ptr(status), _stream()),
+            _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), _ptr(item_row), first_item,
+            n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window or 0, scale, row_threads,
+            _ptr(status), _stream()),
             "prefill_attention_tc")
         return out
 
@@ -562,12 +569,12 @@ class Ops:
                   write_cache=True):
         """Write the step's keys and values into the pages, then attend from the pages."""
         if write_cache:
-            self.kv_append(k, v, ctx.token_item, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
+            self.kv_append(k, v, ctx.token_slot, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
                            layer.page_stride, n_kv_heads, head_dim, layer.page_size)
         if self.dtype == torch.float32 or head_dim % 16 != 0:
             # the CUDA-core kernel takes every head size; the tensor-core kernels want multiples of 16
             return self.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride,
-                                             ctx.token_item, ctx.positions, layer.block_table, n_heads,
+                                             ctx.token_slot, ctx.positions, layer.block_table, n_heads,
                                              n_kv_heads, head_dim, layer.page_size, window, scale)
         from pagedserve_b200.kernels import tensorcore
 
@@ -600,13 +607,21 @@ class Ops:
         stream (the plain runtime call: a fraction of the host time of a tensor ``copy_``)."""
         _check(self.core.ps_copy_h2d(dst.data_ptr(), src_host_ptr, nbytes, _stream()), "copy_h2d")
 
-    def advance(self, sampled, token_ids, positions, kv_len, history, step_counter, max_steps, status=None,
-                status_index=None):
-        """Feed sampled tokens back as the next inputs of a decode-only batch and move it one position on.
-        ``status`` (device int32) is copied to ``history[status_index]`` for the host to read with the tokens."""
+    def step_begin(self, slots, layout, meta, status=None):
+        """The first kernel of a step: apply the uploaded corrections to the slot store (``slots``, a
+        :class:`pagedserve_b200.cache.slots.SlotStore`) and derive the step's per-token and per-item arrays
+        in ``meta`` (the packed metadata buffer laid out by ``layout``) from the slots' state."""
+        self.launches += 1
+        _check(self.core.ps_step_begin(_ptr(slots.store), slots.layout_words.ctypes.data, _ptr(meta),
+                                       layout.words.ctypes.data, _ptr(status), _stream()), "step_begin")
+
+    def step_end(self, slots, layout, meta, sampled, history, max_steps, status=None, status_index=None):
+        """The last kernel of a decode step that sampled on the device: the sampled tokens go into the slots
+        (the next step's inputs if it feeds back) and into ``history``; ``status`` (device int32) is copied to
+        ``history[status_index]`` for the host to read with the tokens."""
         B = sampled.numel()
         self.launches += 1
         copy_to = None if status is None else _ptr(history) + 4 * status_index
-        _check(self.core.ps_advance(_ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(kv_len), _ptr(history),
-                                    _ptr(step_counter), B, max_steps, _ptr(status), copy_to, _stream()),
-               "advance")
+        _check(self.core.ps_step_end(_ptr(slots.store), slots.layout_words.ctypes.data, _ptr(meta),
+                                     layout.words.ctypes.data, _ptr(sampled), _ptr(history), B, max_steps,
+                                     _ptr(status), copy_to, _stream()), "step_end")

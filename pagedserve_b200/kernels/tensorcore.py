@@ -46,7 +46,8 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
         ops.paged_attention_decode(q[:short_tokens], out[:short_tokens], layer.k_pool, layer.v_pool,
                                    layer.page_stride, ctx.token_item[:short_tokens], ctx.positions[:short_tokens],
                                    layer.block_table, n_heads, n_kv_heads, head_dim, layer.page_size, window, scale,
-                                   ctx.max_kv_len, status=ctx.status, q_start=ctx.q_start, kv_len=ctx.kv_len, merge=merge)
+                                   ctx.max_kv_len, status=ctx.status, q_start=ctx.q_start, kv_len=ctx.kv_len, merge=merge,
+                                   token_row=ctx.token_slot[:short_tokens])
     if long_items:
         if ops.prefill_tc_ok(head_dim, layer.page_size, q, out, getattr(layer, "pool", None)):
             # blocks of 128 queries: never more than the count of 64-query blocks
@@ -57,9 +58,9 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
             ops.prefill_attention_tc(q, out, layer.pool, layer.pool_layer, ctx.q_start, ctx.kv_len, layer.block_table,
                                      ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads, n_kv_heads,
                                      head_dim, layer.page_size, window, scale, status=ctx.status,
-                                     row_threads=2 if two else 1)
+                                     row_threads=2 if two else 1, item_row=ctx.item_slot)
         else:
             ops.prefill_attention(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.q_start, ctx.kv_len,
                                   layer.block_table, ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads,
-                                  n_kv_heads, head_dim, layer.page_size, window, scale)
+                                  n_kv_heads, head_dim, layer.page_size, window, scale, item_row=ctx.item_slot)
     return out

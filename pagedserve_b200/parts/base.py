@@ -55,7 +55,7 @@ class LayerContext:
     page_size: int = 0
     pool: Optional[torch.Tensor] = None        # the group's whole pool [pages, layers, 2, kv heads, page, head dim]
     pool_layer: int = 0                        # index of this cache layer inside the pool
-    block_table: Optional[torch.Tensor] = None  # int32 [items, max pages] of the layer's group
+    block_table: Optional[torch.Tensor] = None  # int32 [slots + 1, max pages] of the layer's group, by request slot
     state: Optional[torch.Tensor] = None        # [max slots, *state shape] of this cache layer
 
 

@@ -128,17 +128,24 @@ def test_padded_shape_depends_on_rounded_sizes_only():
 
 
 def test_packed_sections_do_not_overlap_and_are_aligned():
-    layout = BatchLayout(37, 5, 3, [7, 11])
-    names = ["token_ids", "positions", "token_item", "item_slot", "q_start", "kv_len", "logit_rows", "temperature",
-             "seed", "counter"]
-    sizes = [37, 37, 37, 5, 6, 5, 3, 5, 10, 1]
-    spans = [(getattr(layout, name), getattr(layout, name) + size) for name, size in zip(names, sizes)]
-    spans += [(offset, offset + 5 * width) for offset, width in zip(layout.tables, layout.table_widths)]
-    spans.sort()
+    layout = BatchLayout(37, 5, 3, update_capacity=9)
+    names = ["header", "item_slot", "q_start", "logit_rows", "updates", "token_ids", "positions", "token_item",
+             "token_slot", "kv_len", "temperature", "seed"]
+    sizes = [4, 5, 6, 3, 18, 37, 37, 37, 37, 5, 5, 10]
+    spans = sorted((getattr(layout, name), getattr(layout, name) + size) for name, size in zip(names, sizes))
     for (start, end), (next_start, _) in zip(spans, spans[1:]):
         assert end <= next_start
     assert all(start % 4 == 0 for start, _ in spans)             # 16-byte sections: vector loads are legal
     assert spans[-1][1] <= layout.total
+    # what the host uploads comes first and ends with the token ids, so that a step whose tokens the device
+    # fed back uploads a prefix that stops after the corrections
+    uploaded = ["header", "item_slot", "q_start", "logit_rows", "updates", "token_ids"]
+    assert max(getattr(layout, name) for name in uploaded) == layout.token_ids < layout.uploaded
+    assert min(getattr(layout, name) for name in names if name not in uploaded) >= layout.uploaded
+    assert layout.updates < layout.token_ids and layout.counter == layout.header
+    assert layout.words.tolist() == [37, 5, layout.header, layout.item_slot, layout.q_start, layout.updates, 9,
+                                     layout.token_ids, layout.positions, layout.token_item, layout.token_slot,
+                                     layout.kv_len, layout.temperature, layout.seed]
 
 
 def test_step_entry_checks_and_normalises():

@@ -226,3 +226,72 @@ def test_batched_extend_refuses_what_extend_refuses():
     with pytest.raises(CacheError, match="nothing to commit"):
         cache.commit_many(["a"])
     cache.check_invariants()
+
+
+# ------------------------------------------------------------------ the slot store (device copy of per-request state)
+def _corrections(cache):
+    offsets, values = cache.slots.drain()
+    return dict(zip(offsets.tolist(), values.tolist()))
+
+
+def test_slot_store_queues_a_table_entry_only_when_a_page_boundary_is_crossed():
+    """What a step uploads of the block tables: nothing while the new tokens stay inside the request's last
+    page, one entry per group when they start a new page, and the -1s when pages go back."""
+    cache = CacheManager([KVNeed(2, 16), KVNeed(2, 16)], [None, None], page_size=4, num_pages=12, max_slots=3,
+                         max_model_len=32)
+    store = cache.slots
+    assert store.pending == 0
+    slot = cache.admit("a")
+    assert store.pending == 0                                   # a free slot's row is already all -1
+    cache.extend("a", 3)                                        # positions 0-2: the first page
+    base = store.tables[0] + slot * store.table_widths[0]
+    assert _corrections(cache) == {base: cache.groups[0].tables["a"][0]}
+    cache.commit("a")
+    for _ in range(1):                                          # position 3: still the first page
+        cache.extend("a", 1)
+        assert store.pending == 0 and _corrections(cache) == {}
+        cache.commit("a")
+    cache.extend("a", 1)                                        # position 4 starts the second page
+    assert _corrections(cache) == {base + 1: cache.groups[0].tables["a"][1]}
+    cache.commit("a")
+    cache.extend_many(["a"], [2])                               # positions 5, 6: inside it
+    assert store.pending == 0
+    cache.rollback("a")
+    assert store.pending == 0                                   # nothing had been taken, nothing goes back
+    cache.extend_many(["a"], [9])                               # positions 5-13: two more pages
+    got = _corrections(cache)
+    assert got == {base + 2: cache.groups[0].tables["a"][2], base + 3: cache.groups[0].tables["a"][3]}
+    cache.rollback("a")                                         # the step failed: the two entries are -1 again
+    assert _corrections(cache) == {base + 2: -1, base + 3: -1}
+    cache.free("a")
+    assert _corrections(cache) == {base: -1, base + 1: -1}
+    cache.check_invariants()                                    # the mirror equals the host's tables throughout
+
+
+def test_slot_store_corrections_carry_the_latest_value_once():
+    cache = CacheManager([KVNeed(1, 16)], [None], page_size=2, num_pages=8, max_slots=2, max_model_len=16)
+    store = cache.slots
+    slot = cache.admit("r")
+    cache.extend("r", 2)
+    cache.rollback("r")                                         # set and cleared before any step drained it:
+    assert _corrections(cache) == {store.tables[0] + slot * store.table_widths[0]: -1}     # one entry, latest value
+    cache.extend("r", 2)
+    page = cache.groups[0].tables["r"][0]
+    assert _corrections(cache) == {store.tables[0] + slot * store.table_widths[0]: page}
+    # lengths and sampling parameters: queued only where the device's copy differs
+    assert store.set_lengths(np.asarray([slot]), np.asarray([0])) == 0
+    assert store.set_lengths(np.asarray([slot]), np.asarray([5])) == 1
+    assert store.set_sampling(np.asarray([slot]), [0.0], [0]) == 0
+    assert store.set_sampling(np.asarray([slot]), [0.5], [2 ** 63 + 1]) == 3
+    got = _corrections(cache)                                   # the step's upload takes them ...
+    assert got[store.len + slot] == 5
+    store.device_advanced(np.asarray([slot]), 3)                # ... and the device moves the length on itself
+    assert store.lengths_of(np.asarray([slot])).tolist() == [8]
+    assert store.set_lengths(np.asarray([slot]), np.asarray([8])) == 0 and store.pending == 0
+    assert np.asarray([got[store.temp + slot]], dtype=np.int32).view(np.float32)[0] == 0.5
+    words = np.asarray([got[store.seed + 2 * slot], got[store.seed + 2 * slot + 1]], dtype=np.int32)
+    assert int(words.view(np.uint64)[0]) == 2 ** 63 + 1
+    drained = np.asarray(list(got), dtype=np.int64)
+    store.requeue(drained)                                      # a step that was prepared and dropped
+    assert set(_corrections(cache)) == set(got)
+    assert store.take_all() is store.mirror and store.pending == 0

@@ -217,7 +217,12 @@ def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
             out = torch.empty(count, K, dtype=torch.bfloat16, device=DEV)
             return ops.layernorm(x, self.weight, self.bias, 1e-5, out, rows=rows, has_mean=self.params["has_mean"])
 
-    FakeNorm.__name__ = "LayerNorm"
+        def fused_prologue(self):
+            # any norm, whatever its class, that says how a product can compute it in its prologue is folded in
+            from pagedserve_b200.parts.base import NormPrologue
+
+            return NormPrologue(self.weight, self.bias, 1e-5, self.params["has_mean"])
+
     for has_mean, has_bias, use_rows in ((True, True, False), (False, False, True), (True, True, True)):
         norm = FakeNorm(has_mean, has_bias)
         deferred = DeferredNorm(norm, x if use_rows else x[:M], rows if use_rows else None)
@@ -258,6 +263,7 @@ def test_gemm_skinny_with_fused_norm_and_cache_write(M, N, K):
 
         class Ctx:
             token_item = torch.arange(M, dtype=torch.int32, device=DEV)
+            token_slot = token_item                       # this table is by item: a token's row is its item
             positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
 
         class Layer:
@@ -331,6 +337,7 @@ def test_gemm_skinny_writes_the_cache(M, width, head_dim, K):
 
     class Ctx:
         token_item = torch.arange(M, dtype=torch.int32, device=DEV)
+        token_slot = token_item                           # this table is by item: a token's row is its item
         positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
 
     class Layer:

@@ -30,7 +30,9 @@ def build_engine(which, dtype, **options):
 def make_ctx(engine, entries):
     from pagedserve_b200.engine.batch import StepEntry
 
-    return engine.runner.prepare([StepEntry(*entry) for entry in entries])
+    ctx = engine.runner.prepare([StepEntry(*entry) for entry in entries])
+    engine.runner.begin(ctx)          # the step's first kernel: positions, lengths and table rows from the slots
+    return ctx
 
 
 # ------------------------------------------------------------------ parts alone
