@@ -429,3 +429,139 @@ def test_toy_position_encoding_and_routed_feed_forward(dtype, n_experts):
     engine.finish("a")
     engine.finish("b")
     engine.cache.check_invariants()
+
+
+# ----------------------------------------------------------------------------------------------
+# A mixer with state of its own that runs on the device alone (its steps are captured as CUDA graphs):
+# the runner must not launch a step ahead of its tokens for such a model, because a step that is launched
+# and then dropped (a request ended on an end-of-sequence token) would have moved the slots' state on.
+# ----------------------------------------------------------------------------------------------
+def register_device_state_toy():
+    from pagedserve_b200.cache.manager import StateNeed
+    from pagedserve_b200.config.registry import ModelConfig, register_architecture
+    from pagedserve_b200.models.spec import LayerSpec, ModelSpec, PartSpec
+    from pagedserve_b200.parts.base import Mixer, register_part
+    from pagedserve_b200.weights.loader import ParamSpec
+
+    @register_part("mixer", "toy_device_running_sum", replace=True)
+    class DeviceRunningSum(Mixer):
+        """y_t = s_t W with s_t = decay * s_{t-1} + x_t per request, s kept in the request's slot; computed
+        from the step's device arrays only (no host logic), so the step can be a CUDA graph."""
+
+        graph_safe = True
+
+        def state_need(self):
+            return StateNeed((self.params["width"],), "float32")
+
+        def param_specs(self):
+            width = self.params["width"]
+            return [(ParamSpec(self._n("mix.weight"), (width, width), "matmul"), ("normal", 0.05))]
+
+        def bind(self, tensors):
+            self.weight = tensors[self._n("mix.weight")]
+
+        def forward(self, x, residual, ctx, layer):
+            decay = self.params["decay"]
+            tokens = x.shape[0]
+            item, slot = ctx.token_item.long(), ctx.token_slot.long()
+            index = torch.arange(tokens, device=x.device)
+            first = ctx.q_start.long()[item]                                  # first token of each token's entry
+            gap = (index[:, None] - index[None, :]).clamp(min=0).to(torch.float32)
+            weights = torch.where((item[:, None] == item[None, :]) & (index[None, :] <= index[:, None]),
+                                  decay ** gap, torch.zeros_like(gap))
+            carried = (decay ** (index - first + 1).to(torch.float32))[:, None] * layer.state[slot]
+            sums = weights @ x.to(torch.float32) + carried                    # the state after every token
+            last = (ctx.q_start.long()[1:] - 1).clamp(min=0)                  # last token of every entry
+            layer.state[ctx.item_slot.long()] = sums[last]
+            self.env.ops.linear(sums.to(self.env.dtype), self.weight, None, residual, accumulate=True)
+
+    @dataclass
+    class StateToyConfig(ModelConfig):
+        width: int = 32
+        vocab: int = 61
+        max_len: int = 48
+        decay: float = 0.6
+
+        @classmethod
+        def from_dict(cls, values):
+            return cls(values["width"], values["vocab"], values["max_len"], values["decay"])
+
+        def to_dict(self):
+            return {"architectures": ["ToyDeviceStateLM"], "width": self.width, "vocab": self.vocab,
+                    "max_len": self.max_len, "decay": self.decay}
+
+        architecture = property(lambda self: "ToyDeviceStateLM")
+        vocabulary_size = property(lambda self: self.vocab)
+        max_model_len = property(lambda self: self.max_len)
+
+    def build(config):
+        width = config.width
+        norm = dict(width=width, eps=1e-5, has_mean=False, has_bias=False, init_std=0.02)
+        layer = LayerSpec(
+            PartSpec("pre_norm"), PartSpec("toy_device_running_sum", dict(width=width, decay=config.decay), "l0."),
+            PartSpec("dense_mlp", dict(hidden_size=width, inner_size=40, activation="gelu_tanh", has_bias=False,
+                                       stored_in_out=False, up_name="up", down_name="down"), "l0."),
+            {"pre_mixer": PartSpec("layernorm", dict(norm, name="n1"), "l0."),
+             "pre_feed_forward": PartSpec("layernorm", dict(norm, name="n2"), "l0.")})
+        return ModelSpec(
+            architecture="ToyDeviceStateLM", hidden_size=width, vocab_size=config.vocab,
+            max_model_len=config.max_len,
+            embedding=PartSpec("token_embedding", dict(vocab_size=config.vocab, hidden_size=width, name="emb")),
+            positions=PartSpec("none"), layers=[layer], schedule=[],
+            final_norm=PartSpec("layernorm", dict(norm, name="norm_f")),
+            head=PartSpec("lm_head", dict(vocab_size=config.vocab, hidden_size=width, tied=True, name="head")))
+
+    register_architecture("ToyDeviceStateLM", StateToyConfig, build, replace=True)
+    return StateToyConfig
+
+
+def device_state_toy_generate(tensors, config, prompt, count):
+    """Greedy tokens of the toy model above, whole sequence each time, float64."""
+    w = {name: t.double() for name, t in tensors.items()}
+    rms = lambda x, gain: x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * gain
+    tokens, produced = list(prompt), []
+    for _ in range(count):
+        h = w["emb.weight"][torch.tensor(tokens)]
+        state, sums = torch.zeros(config.width, dtype=torch.float64), []
+        for row in rms(h, w["l0.n1.weight"]):
+            state = config.decay * state + row
+            sums.append(state)
+        h = h + torch.stack(sums) @ w["l0.mix.weight"].T
+        inner = plain_gpt2.activation(rms(h, w["l0.n2.weight"]) @ w["l0.up.weight"].T, "gelu_new")
+        h = h + inner @ w["l0.down.weight"].T
+        logits = rms(h[-1], w["norm_f.weight"]) @ w["emb.weight"].T
+        tokens.append(int(torch.argmax(logits)))
+        produced.append(tokens[-1])
+    return produced
+
+
+def test_graph_safe_mixer_with_slot_state_survives_a_request_that_ends_early():
+    from pagedserve_b200.config.engine_config import EngineConfig
+    from pagedserve_b200.engine.engine import Engine
+    from pagedserve_b200.weights.random_init import write_random_model
+    from pagedserve_b200.weights.safetensors_io import read_safetensors
+
+    StateToyConfig = register_device_state_toy()
+    config = StateToyConfig()
+    with tempfile.TemporaryDirectory() as folder:
+        write_random_model(folder, config, seed=11)
+        tensors = read_safetensors(folder + "/model.safetensors")
+        engine = Engine.from_folder(folder, EngineConfig(dtype="float32", block_size=4, num_blocks=8, max_num_seqs=4))
+    assert engine.model.graph_safe and engine.runner.enable_cuda_graphs
+    assert list(engine.cache.state) == [0] and not engine.cache.groups     # slot state only, no pages at all
+    prompts = [helpers.random_tokens(config.vocab, n, seed=60 + n) for n in (5, 9, 12)]
+    want = [device_state_toy_generate(tensors, config, prompt, 14) for prompt in prompts]
+    eos = want[1][4]                                                   # request 1 ends on its fifth token
+    for produced in want:
+        if eos in produced:
+            del produced[produced.index(eos) + 1:]
+    assert len(want[1]) == 5 and max(len(produced) for produced in want) > 8
+    scheduler = engine.make_scheduler(strategy="orca", max_num_seqs=4, eos_token_id=eos)
+    ids = [scheduler.add_token_request(prompt, max_new_tokens=14) for prompt in prompts]
+    while scheduler.waiting or scheduler.active:
+        scheduler.step()
+        staged = engine.runner._staged
+        assert staged is None or not staged.launched                    # prepared ahead at most, never launched
+    assert engine.runner.graph_replays > 0                              # the decode steps did run as graphs
+    assert [scheduler.finished[i].generated_token_ids for i in ids] == want
+    engine.check_status()
