@@ -94,6 +94,17 @@ __device__ __forceinline__ uint32_t ld_cluster_u32(const void* local, int rank) 
 __device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
     return __uint_as_float(ld_cluster_u32(local, rank));
 }
+// 16 bytes at once (local must be 16-byte aligned). Not volatile: independent loads may be in flight together;
+// the cluster barrier before them orders them behind the writes they read.
+__device__ __forceinline__ float4 ld_cluster_f32x4(const float* local, int rank) {
+    uint32_t remote;
+    float4 v;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;"
+        : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
 
 // Programmatic dependent launch (on unless PAGEDSERVE_B200_PDL=0). A kernel calls pdl_wait() before it
 // touches memory that an earlier kernel wrote: it returns when all earlier kernels have completed and their

@@ -1,6 +1,6 @@
 """Time one kernel in isolation (CUDA events, after warm-up), for tuning and for ncu captures.
 
-    python -m pagedserve_b200.kernels.microbench gemm --m 2048 --n 2304 --k 768 [--bn 0] [--impl tc|skinny|simt]
+    python -m pagedserve_b200.kernels.microbench gemm --m 2048 --n 2304 --k 768 [--bn 0] [--impl tc|skinny|rows|simt]
     python -m pagedserve_b200.kernels.microbench attention --batch 64 --context 640 [--heads 12 --head-dim 64]
 
 ``gemm`` prints achieved TFLOP/s and the bytes-per-second of streaming the weight once;
@@ -76,6 +76,8 @@ def bench_gemm(args):
             ops.linear_tc(a[j], w[j], bias, out, act=args.act, accumulate=acc, status=status, bn=args.bn)
         elif args.impl == "skinny":
             ops.linear_skinny(a[j], w[j], bias, out, act=args.act, accumulate=acc)
+        elif args.impl == "rows":
+            ops.linear_rows_tc(a[j], w[j], bias, out, act=args.act, accumulate=acc, status=status, splits=args.splits)
         else:
             ops.linear_simt(a[j], w[j], bias, out, act=args.act, accumulate=acc)
 
@@ -122,7 +124,8 @@ def main(argv=None):
     g.add_argument("--n", type=int, default=2304)
     g.add_argument("--k", type=int, default=768)
     g.add_argument("--bn", type=int, default=0)
-    g.add_argument("--impl", default="tc", choices=("tc", "skinny", "simt"))
+    g.add_argument("--impl", default="tc", choices=("tc", "skinny", "rows", "simt"))
+    g.add_argument("--splits", type=int, default=0, help="rows: CTAs per column tile (0: the kernel chooses)")
     g.add_argument("--act", default=None)
     g.add_argument("--out", default="bfloat16", choices=("bfloat16", "float32"))
     g.add_argument("--accumulate", action="store_true", help="add the product to what the output holds")

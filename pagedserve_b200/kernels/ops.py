@@ -97,6 +97,8 @@ _SIGNATURES = {
     },
     "tc": {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+        "ps_gemm_rows_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I,
+                            _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_gemm_tc_qkv": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
                                     _I, _I, _F, _I, _P, _P],
@@ -271,6 +273,32 @@ class Ops:
                                    1 if accumulate else 0, _ptr(status), bn, _stream()), "gemm_tc")
         return out
 
+    def linear_rows_tc(self, a, w, bias, out, act=None, accumulate=False, kv=None, status=None, splits=0):
+        """tcgen05 product for at most 64 rows of ``a`` with the operands swapped: weight rows on the 128-row
+        side of the MMA, K split over the CTAs of a thread-block cluster (csrc/gemm_rows_tc.cu).  ``kv`` as in
+        :meth:`linear_skinny`; ``splits`` 0 lets the kernel choose."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError("linear_rows_tc: shapes do not match")
+        _require(a, "a", torch.bfloat16)
+        _require(w, "w", torch.bfloat16)
+        _require(out, "out")
+        if bias is not None:
+            _require(bias, "bias", torch.float32)
+        if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("linear_rows_tc: innermost stride must be 1")
+        if self._tc is None:
+            self._tc = _declare(_load_library("tc"), "tc")
+        if status is None:
+            status = self.status_flag(a.device)
+        self.launches += 1
+        _check(self._tc.ps_gemm_rows_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
+                                        out.stride(0), M, N, K, dtype_code(out.dtype), _ACT_CODE[act],
+                                        1 if accumulate else 0, _ptr(status), splits,
+                                        *self._kv_arguments(kv, N), _stream()), "gemm_rows_tc")
+        return out
+
     @staticmethod
     def tc_ok(a, w):
         K = a.shape[1]
@@ -360,6 +388,10 @@ class Ops:
                 a = a.materialize()
             from pagedserve_b200.kernels import tensorcore
 
+            # a few dozen rows of a large matrix: the few-rows tcgen05 product writes the pages from its epilogue
+            if tensorcore.prefers_rows(self, a, w) and q_width % 4 == 0 and kv_width % 4 == 0:
+                self.linear_rows_tc(a, w, bias, out, kv=(ctx, layer, q_width, kv_width, head_dim))
+                return True
             # many rows: the tcgen05 product, whose TMA-store epilogue sends the key and value columns to the pages
             if tensorcore.prefers_tc(self, a, w):
                 if (q_width % 64 == 0 and head_dim % 8 == 0 and out.data_ptr() % 16 == 0

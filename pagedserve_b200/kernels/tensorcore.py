@@ -1,8 +1,10 @@
 """The bfloat16 paths of the matrix product and of attention.
 
 ``linear``    out = act(a @ w.T + bias) with bfloat16 operands and float32 accumulation:
-              at most 64 rows -> the weight-streaming kernel (csrc/gemm_skinny.cu), except 17 to 64
-                                 rows with 4,096 or more output columns;
+              at most 64 rows -> the weight-streaming kernel (csrc/gemm_skinny.cu), except
+                                 33 to 64 rows of a large matrix -> the few-rows tcgen05 kernel with the
+                                 operands swapped and K split over a cluster (csrc/gemm_rows_tc.cu), and
+                                 17 to 47 rows with 4,096 or more output columns -> the kernel below;
               more rows       -> the tcgen05 / TMA / TMEM kernel (csrc/gemm_tc.cu);
               shapes neither takes (K not a multiple of 8, unaligned rows) -> the CUDA-core kernel.
 ``attention`` causal attention over the paged cache for bfloat16 queries.
@@ -11,18 +13,37 @@
 from __future__ import annotations
 
 
+def prefers_rows(ops, a, w) -> bool:
+    """Whether the few-rows tcgen05 kernel takes this product.  Its cost hardly depends on the rows (about 5 us
+    of latency, then 64 tokens ride along with the weights), the mma.sync kernel's grows with every 8 rows and
+    with the matrix.  Measured on B200 (us, weight-streaming / few-rows tcgen05 / 128-row tcgen05):
+    64 x 2,304 x 768: 6.6 / 7.5 / 8.1;  64 x 768 x 3,072: 12.5 / 7.7 / 18.2;  56 x 768 x 3,072: 7.7 / 7.7 / 18.1;
+    48 x 2,304 x 768: 4.8 / 7.0 / 8.1;  64 x 4,096 x 1,024: 11.8 / 7.9 / 9.4;  64 x 1,024 x 4,096: 17.6 / 9.0 / 22.8;
+    64 x 4,800 x 1,600: 25.1 / 12.0 / 12.1;  64 x 1,600 x 6,400: 23.0 / 12.1 / 33.1;  33 x 4,800 x 1,600: 13.0 /
+    10.7 / 12.2;  64 x 50,257 x 768: 73.9 / 35.6 / 45.5;  33 x 50,257 x 768: 35.6 / 31.5 / 30.6.
+    The rule depends on the shapes alone, so that the same step always runs the same kernels."""
+    rows, columns, depth = a.shape[0], w.shape[0], a.shape[1]
+    if not (32 < rows <= 64) or not ops.tc_ok(a, w):
+        return False
+    if columns >= 4096:
+        return rows >= 48
+    return rows > 56 or columns * depth >= 2_500_000
+
+
 def prefers_tc(ops, a, w) -> bool:
     """Whether the tcgen05 kernel takes this product.  The weight-streaming kernel brings the rows of ``a`` to
     every CTA (16 output columns): from 17 rows on and 4,096 columns up (a vocabulary, the wide projections of
     large models) that traffic costs more than the half-empty 128-row tiles of the tcgen05 kernel (64 rows x
     50,257 x 768: 46 vs 85 us; 64 x 4,800 x 1,600: 12 vs 37 us; 16 rows: the streaming kernel wins at every
     shape)."""
-    if not ops.tc_ok(a, w):
+    if not ops.tc_ok(a, w) or prefers_rows(ops, a, w):
         return False
     return (a.shape[0] > 16 and w.shape[0] >= 4096) or not ops.skinny_ok(a, w)
 
 
 def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
+    if prefers_rows(ops, a, w):
+        return ops.linear_rows_tc(a, w, bias, out, act, accumulate, status=status)
     if prefers_tc(ops, a, w):
         return ops.linear_tc(a, w, bias, out, act, accumulate, status=status)
     if ops.skinny_ok(a, w):

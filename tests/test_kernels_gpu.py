@@ -349,7 +349,7 @@ def test_gemm_skinny_writes_the_cache(M, width, head_dim, K):
     out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
     assert ops.linear_qkv(a, w, bias, out, Ctx, Layer, width, width, head_dim, scatter=True)
     want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    ops.linear_skinny(a, w, bias, want)
+    ops.linear(a, w, bias, want)                              # the kernel that the dispatch picks for this shape
     assert torch.equal(out[:, :width], want[:, :width])       # the same kernel: the same sums in the same order
     assert float(out[:, width:].abs().max()) == 0.0           # keys and values did not go to the buffer
     for i, n in enumerate(lengths):
@@ -357,6 +357,93 @@ def test_gemm_skinny_writes_the_cache(M, width, head_dim, K):
         assert torch.equal(slot[0], want[i, width:2 * width])
         assert torch.equal(slot[1], want[i, 2 * width:])
     assert int((pool != 0).sum()) <= 2 * M * width             # nothing else was touched
+
+
+@pytest.mark.parametrize("M", [1, 16, 17, 33, 40, 48, 49, 64])
+@pytest.mark.parametrize("N,K", [(128, 64), (48, 8), (300, 328), (1003, 104), (2304, 768), (768, 3072), (1600, 6400),
+                                 (4800, 1600)])
+@pytest.mark.parametrize("splits", [0, 1, 2, 8])
+def test_gemm_rows_tcgen05(M, N, K, splits):
+    """The few-rows tcgen05 product (weight rows on the 128-row side of the MMA, K split over the CTAs of a
+    cluster) against float64 and the CUDA-core product: tails in N and K, every count of token rows, every
+    split (some CTAs then have no k-block at all), all epilogues."""
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    da, dw, db = a.to(DEV), w.to(DEV), bias.to(DEV)
+    for act, out_dtype, tol in ((None, torch.float32, 2e-5), ("gelu_tanh", torch.bfloat16, 6e-3),
+                                ("gelu_erf", torch.float32, 2e-5)):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        ops.linear_rows_tc(da, dw, db, out, act=act, status=status, splits=splits)
+        assert rel_err(out, gemm_reference(a, w, bias, act, None)) < tol, (act, out_dtype)
+    base = torch.randn(M, N, generator=g)
+    stream = base.clone().to(DEV)
+    ops.linear_rows_tc(da, dw, db, stream, accumulate=True, status=status, splits=splits)
+    assert rel_err(stream, gemm_reference(a, w, bias, None, base)) < 2e-5
+    simt = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    fast = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_simt(da, dw, None, simt)
+    ops.linear_rows_tc(da, dw, None, fast, status=status, splits=splits)
+    assert rel_err(fast, simt) < 2e-5                      # two float32 sums of up to 6,400 terms in different orders
+    # a row's result does not depend on the rows beside it, nor on how many there are
+    for rows in (1, min(M, 20)):
+        part = torch.empty(rows, N, dtype=torch.float32, device=DEV)
+        ops.linear_rows_tc(da[M - rows:].contiguous(), dw, None, part, status=status, splits=splits)
+        assert torch.equal(part, fast[M - rows:])
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("M", [17, 40, 64])
+@pytest.mark.parametrize("width,head_dim,K", [(96, 48, 96), (768, 64, 768), (160, 16, 264), (1600, 64, 1600)])
+def test_gemm_rows_tcgen05_writes_the_cache(M, width, head_dim, K):
+    """The packed q|k|v projection through the few-rows tcgen05 product: queries to the buffer, keys and values
+    into the pages of each token's request, nothing else touched."""
+    ops = ops_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(M + width + K)
+    N = 3 * width
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    kv_heads = width // head_dim
+    page = 8
+    lengths = [3 + 2 * i for i in range(M)]                 # every token is the last of its own request
+    pages = [-(-n // page) for n in lengths]
+    rows_of = torch.randperm(M + 3, generator=g)[:M]        # the table is kept by slot: token i uses row rows_of[i]
+    table = torch.full((M + 3, max(pages)), -1, dtype=torch.int32)
+    order = torch.randperm(sum(pages), generator=g)
+    cursor = 0
+    for i, count in enumerate(pages):
+        table[rows_of[i], :count] = order[cursor:cursor + count].to(torch.int32)
+        cursor += count
+    pool = torch.zeros(sum(pages), 1, 2, kv_heads, page, head_dim, dtype=torch.bfloat16, device=DEV)
+
+    class Ctx:
+        token_slot = rows_of.to(torch.int32).to(DEV)
+        positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+
+    class Layer:
+        k_pool, v_pool = pool[:, 0, 0], pool[:, 0, 1]
+        page_stride = 2 * kv_heads * page * head_dim
+        page_size = page
+        block_table = table.to(DEV)
+
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear_rows_tc(a, w, bias, out, kv=(Ctx, Layer, width, width, head_dim))
+    want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear_rows_tc(a, w, bias, want)
+    assert torch.equal(out[:, :width], want[:, :width])       # the same kernel: the same sums in the same order
+    assert float(out[:, width:].abs().max()) == 0.0           # keys and values did not go to the buffer
+    for i, n in enumerate(lengths):
+        slot = pool[int(table[rows_of[i], (n - 1) // page]), 0, :, :, (n - 1) % page, :].reshape(2, width)
+        assert torch.equal(slot[0], want[i, width:2 * width])
+        assert torch.equal(slot[1], want[i, 2 * width:])
+    assert int((pool != 0).sum()) <= 2 * M * width             # nothing else was touched
+    reference = gemm_reference(a.cpu(), w.cpu(), bias.cpu(), None, None)
+    assert rel_err(want, reference) < 6e-3
+    assert int(ops.status_flag(DEV).item()) == 0
 
 
 def test_gemm_skinny_refuses_what_it_cannot_take():
