@@ -126,13 +126,23 @@ __global__ void __launch_bounds__(256)
 layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gamma,
                       const float* __restrict__ beta, float eps, TOut* __restrict__ out, int n_rows, int H,
                       int has_mean) {
+    // the norm's scale and shift are weights: they are fetched before the wait on the kernel that writes x
+    const int lane = threadIdx.x & 31;
+    const int quads = H >> 2;
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    float4 g[WMAX], b[WMAX];
+#pragma unroll
+    for (int i = 0; i < WMAX; ++i) {
+        const int c = lane + 32 * i;
+        g[i] = c < quads ? g4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        b[i] = (beta && c < quads) ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     pdl_prologue();
     x = pdl_fresh(x);
-    const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= n_rows) return;
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
-    const int quads = H >> 2;
     float4 v[WMAX];
     float sum = 0.f;
 #pragma unroll
@@ -146,22 +156,18 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
 #pragma unroll
     for (int i = 0; i < WMAX; ++i) {
         if (lane + 32 * i < quads) {
-            float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
-            sq += (a * a + b * b) + (c * c + d * d);
+            float a = v[i].x - mean, b2 = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+            sq += (a * a + b2 * b2) + (c * c + d * d);
         }
     }
     const float rstd = rsqrtf(warp_sum(sq) / (float)H + eps);
-    const float4* g4 = reinterpret_cast<const float4*>(gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(beta);
     TOut* o = out + (size_t)r * H;
 #pragma unroll
     for (int i = 0; i < WMAX; ++i) {
         int c = lane + 32 * i;
         if (c < quads) {
-            float4 g = g4[c];
-            float4 b = beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-            float y0 = (v[i].x - mean) * rstd * g.x + b.x, y1 = (v[i].y - mean) * rstd * g.y + b.y;
-            float y2 = (v[i].z - mean) * rstd * g.z + b.z, y3 = (v[i].w - mean) * rstd * g.w + b.w;
+            float y0 = (v[i].x - mean) * rstd * g[i].x + b[i].x, y1 = (v[i].y - mean) * rstd * g[i].y + b[i].y;
+            float y2 = (v[i].z - mean) * rstd * g[i].z + b[i].z, y3 = (v[i].w - mean) * rstd * g[i].w + b[i].w;
             if constexpr (sizeof(TOut) == 2) {
                 __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
                 uint2 pack = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
@@ -177,12 +183,17 @@ template <typename TOut>
 int launch_layernorm(const float* x, const int* rows, int n_rows, int H, const float* gamma, const float* beta,
                      float eps, int has_mean, TOut* out, cudaStream_t s) {
     const bool aligned = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)beta | (uintptr_t)out) & 15) == 0;
-    if (n_rows >= 64 && aligned && H <= 32 * 4 * 16) {
-        dim3 grid((n_rows + 7) / 8);
+    // Which kernel runs depends on the width and the alignment alone, never on the number of rows: a row's
+    // result is the same bits whatever else is in the batch.
+    if (aligned && H <= 32 * 4 * 16) {
+        // a few dozen rows (a decode step): two rows per CTA, so that the rows spread over many SMs and each
+        // warp's trips to memory are short; many rows (a prompt): eight per CTA
+        const int warps = n_rows <= 256 ? 2 : 8;
+        dim3 grid((n_rows + warps - 1) / warps), block(32 * warps);
         if (H <= 32 * 4 * 8)
-            return launch_pdl(layernorm_warp_kernel<TOut, 8>, grid, dim3(256), 0, s, x, rows, gamma, beta, eps, out,
+            return launch_pdl(layernorm_warp_kernel<TOut, 8>, grid, block, 0, s, x, rows, gamma, beta, eps, out,
                               n_rows, H, has_mean);
-        return launch_pdl(layernorm_warp_kernel<TOut, 16>, grid, dim3(256), 0, s, x, rows, gamma, beta, eps, out,
+        return launch_pdl(layernorm_warp_kernel<TOut, 16>, grid, block, 0, s, x, rows, gamma, beta, eps, out,
                           n_rows, H, has_mean);
     }
     return launch_pdl(layernorm_kernel<TOut, 256>, dim3(n_rows), dim3(256), 0, s, x, rows, gamma, beta, eps, out, H,
