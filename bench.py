@@ -293,7 +293,7 @@ def _run_reference(args, ref):
                                  if key in ("captured_graphs", "graph_replays", "capture_failures")}
         result["roofline"]["frac"] = result["roofline"]["achieved"] / result["roofline"]["peak"]
         if not args.small and not args.skip_prefill:
-            result["prefill"] = measure_prefill()
+            result["prefill"] = measure_prefill(args.prefill_tokens)
         if not args.small and not args.skip_points:
             result["points"] = {"decode_b1": measure_decode(1, steps)["tok_s"],
                                 "decode_b64": measure_decode(64, steps)["tok_s"]}
@@ -315,6 +315,8 @@ def main():
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--small", action="store_true", help="profiling aid: only the default decode measurement")
     parser.add_argument("--prefill-only", action="store_true", help="profiling aid: only the prefill measurement")
+    parser.add_argument("--prefill-tokens", type=int, default=2048,
+                        help="tokens of the prefill step, in prompts of 1,024 (1024: one single prompt)")
     parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
                         help="instead of the decode measurement: this many requests (prompts U[64,1024), outputs "
                              "U[32,256]) through the scheduler, chunked prefill under a 2,048-token budget")
@@ -505,7 +507,7 @@ def main():
                 "step_ms_p90": step_ms[int(len(step_ms) * 0.9)], "step_ms_max": step_ms[-1]}
 
     if args.prefill_only:
-        print(json.dumps({"impl": "ours", "prefill": measure_prefill(repeats=3)}))
+        print(json.dumps({"impl": "ours", "prefill": measure_prefill(args.prefill_tokens, repeats=3)}))
         return 0
     if args.serving:
         print(json.dumps(measure_serving(args.serving)))
@@ -535,7 +537,7 @@ def main():
     }
     result["roofline"]["frac"] = result["roofline"]["achieved"] / result["roofline"]["peak"]
     if not args.small and not args.skip_prefill:
-        result["prefill"] = measure_prefill()
+        result["prefill"] = measure_prefill(args.prefill_tokens)
     if not args.small and not args.skip_points:
         result["points"] = {"decode_b1": measure_decode(1, steps)["tok_s"],
                             "decode_b64": measure_decode(64, steps)["tok_s"]}

@@ -60,7 +60,9 @@ class ModelRunner:
     STAGING_BUFFERS = 4
 
     MAX_DEVICE_STEPS = 1024          # most decode steps one ``decode`` call runs without the host
-    MAX_GRAPHS = 96
+    # Destroying a captured graph returns its memory to the device, which stalls the stream for tens of
+    # milliseconds: the limit is generous, and step shapes are bucketed so that few graphs are needed.
+    MAX_GRAPHS = 512
     # A capture costs about as much as two eager steps: a shape must come back before it is worth one.
     MIXED_SHAPE_SIGHTINGS = 2
     # Mixed steps are padded to recurring shapes so that their graphs are found again: short tokens to a
@@ -94,6 +96,8 @@ class ModelRunner:
         # padding needs the scratch slot's pages and positions 0 .. PAD_LONG - 1 to exist in the model
         self._pad_mixed = (self.enable_cuda_graphs and cache.scratch_tokens >= self.PAD_LONG
                            and self.max_model_len >= 2 * self.PAD_LONG)
+        # decode-only steps are padded too (1, 2, 4, 8, 16, 24, ... requests): one graph per bucket, not per count
+        self._pad_decode = self.enable_cuda_graphs and cache.scratch_tokens >= 1
         self._graphs = {}                 # (batch size, kind) or step shape -> _DecodeGraph
         self._shape_seen = {}             # step shape -> times seen (a shape is captured when it comes back)
         self.graph_replays = 0
@@ -288,25 +292,42 @@ class ModelRunner:
         cache.extend_many(requests, np.full(I, 1 + extra_tokens, dtype=np.int64))      # all or nothing
         self._admitted_in_step = []
 
-        layout, views, staging, host = self._stage(I, I, I)
+        # The step runs P >= I entries: the I requests, then entries of one token each at position 0 of the
+        # cache's scratch slot (their results are dropped), so that batch sizes share captured graphs.
+        P = self._decode_bucket(I)
+        layout, views, staging, host = self._stage(P, P, P)
         slots_store = self.slots
         slots_store.set_lengths(slots, starts)
         if sampling is not None:
             slots_store.set_sampling(slots, sampling[0], sampling[1])
-        ramp = self._ramp[:I + 1]
-        self._fill(layout, host, slots, ramp, ramp[:I], tokens, fed=0 if tokens is not None else 1)
+        ramp = self._ramp[:P + 1]
+        item_slot, kv_len, positions = slots, starts + 1, starts
+        token_ids = np.asarray(tokens, dtype=np.int32) if tokens is not None else np.zeros(I, dtype=np.int32)
+        if P > I:
+            item_slot = np.concatenate([slots, np.full(P - I, cache.scratch_slot, dtype=slots.dtype)])
+            kv_len = np.concatenate([kv_len, np.ones(P - I, dtype=kv_len.dtype)])
+            positions = np.concatenate([positions, np.zeros(P - I, dtype=positions.dtype)])
+            token_ids = np.concatenate([token_ids, np.zeros(P - I, dtype=np.int32)])
+        self._fill(layout, host, item_slot, ramp, ramp[:P], token_ids if tokens is not None else None,
+                   fed=0 if tokens is not None else 1)
         if tokens is not None:
             self._upload(layout, staging, record=False)
             slots_store.device_advanced(slots, 1 + extra_tokens)
-        kv_len = starts + 1
-        token_ids = np.asarray(tokens, dtype=np.int32) if tokens is not None else np.zeros(I, dtype=np.int32)
-        host_batch = HostBatch(token_ids, starts.astype(np.int32), ramp[:I], slots.astype(np.int32), ramp,
-                               kv_len.astype(np.int32), ramp[:I], list(requests))
+        host_batch = HostBatch(token_ids, positions.astype(np.int32), ramp[:P], item_slot.astype(np.int32), ramp,
+                               kv_len.astype(np.int32), ramp[:P], list(requests))
         ctx = StepContext(layout, self._device_buffer, host_batch, cache, self._status, 1,
-                          int(kv_len.max()), I, I, 0, views=views)
+                          int(kv_len.max()), P, P, 0, views=views)
         ctx.slots = slots
+        ctx.real_items = I
         ctx.drained = self._drained                        # corrections staged but not yet uploaded
         return ctx
+
+    def _decode_bucket(self, count: int) -> int:
+        """The number of entries a decode-only step of ``count`` requests runs with."""
+        if not self._pad_decode:
+            return count
+        bucket = next((small for small in (1, 2, 4, 8) if count <= small), -(-count // 8) * 8)
+        return bucket if bucket <= self.cache.max_slots else count      # buffers are sized for max_slots entries
 
     def _check_vocabulary(self, tokens: np.ndarray) -> None:
         low, high = int(tokens.min()), int(tokens.max())
@@ -426,9 +447,10 @@ class ModelRunner:
                 self._check_vocabulary(tokens)
                 layout = ctx.layout
                 host = self._staging_numpy[staged.turn]
-                host[layout.token_ids:layout.token_ids + layout.num_tokens] = tokens
+                host[layout.token_ids:layout.token_ids + tokens.size] = tokens
+                host[layout.token_ids + tokens.size:layout.token_ids + layout.num_tokens] = 0
                 host[layout.header + layout.FED] = 0
-                ctx.host.token_ids[:] = tokens
+                ctx.host.token_ids[:tokens.size] = tokens
                 self._staging_turn = staged.turn
                 self._upload(layout, self._staging[staged.turn], record=False)
                 self.slots.device_advanced(ctx.slots, 1)
@@ -466,7 +488,7 @@ class ModelRunner:
         # the step is on its way: what follows runs on the host while the device works
         self.cache.commit_many(requests)
         self.steps += steps
-        self.tokens_run += steps * B
+        self.tokens_run += steps * len(requests)
         if stage_next and steps == 1:
             self._staged = self._stage_ahead(requests, temperatures, seeds,
                                              launch_half=None if done is None else 1 - half)
@@ -476,7 +498,8 @@ class ModelRunner:
             torch.cuda.current_stream().synchronize()
         if self._history.array[self._status_index]:
             self.check_status()
-        result = self._history.array[half * B:(half + steps) * B].reshape(steps, B).copy()
+        # (B entries ran, the requests first; what the padding entries drew is dropped)
+        result = self._history.array[half * B:(half + steps) * B].reshape(steps, B)[:, :len(requests)].copy()
         if self._staged is not None and self._staged.launched:
             self._staged.fed_tokens = result[0]
         return result
