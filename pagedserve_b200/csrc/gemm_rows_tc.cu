@@ -213,6 +213,37 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         if (ok && my_kb > 0) umma_commit(acc_full);
         else mbar_arrive(acc_full);                     // nothing to wait for (no k-block here, or gave up)
     }
+    // ------------------------------------------------ everybody: the epilogue's constants, fetched while the weights arrive
+    // a thread finishes 4 consecutive columns of one token at a time: the S partial sums of the four come as
+    // S independent 16-byte loads (all in flight together), added in rank order
+    const int share = TILE_N / splits;                            // splits is 1, 2, 4 or 8: 128 .. 16 columns
+    const int groups = share >> 2;                                // groups of 4 columns in the share
+    const int c4 = (threadIdx.x % groups) * 4, first_token = threadIdx.x / groups, token_step = THREADS / groups;
+    const int column = rank * share + c4;
+    const int n = n0 + column;
+    float b[4] = {0.f, 0.f, 0.f, 0.f};
+    if (bias) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (n + j < N) b[j] = bias[n + j];
+    }
+    // where key / value columns go: which pool, head and offset inside the head (a group of 4 lies in one
+    // head: head sizes and the query width are multiples of 4 here, else the scalar path below is taken)
+    const bool whole = n + 3 < N;
+    bool to_pages = false;
+    __nv_bfloat16* pool = nullptr;
+    long long head_offset = 0;
+    if (kv.k_pool && n >= kv.q_width && n < N) {
+        to_pages = true;
+        int idx = n - kv.q_width;
+        pool = kv.k_pool;
+        if (idx >= kv.kv_width) { idx -= kv.kv_width; pool = kv.v_pool; }
+        const int head = idx / kv.head_dim;
+        head_offset = (long long)head * kv.page_size * kv.head_dim + (idx - head * kv.head_dim);
+    }
+    const bool kv_vector = to_pages && whole && (kv.head_dim & 3) == 0 && (kv.q_width & 3) == 0 &&
+                           (kv.kv_width & 3) == 0 && (kv.page_stride & 3) == 0;
+    const bool out_vector = whole && (ldo & 3) == 0 && (((uintptr_t)out) & 15) == 0;
     // ------------------------------------------------ everybody: accumulator -> partial[token][column]
     bool have = my_kb > 0;
     if (!mbar_wait(acc_full, 0, abort_flag)) {
@@ -243,36 +274,6 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (splits > 1) cluster_sync_all(); else __syncthreads();
     // ------------------------------------------------ this CTA's share of the tile's columns, all tokens
     {
-        // a thread finishes 4 consecutive columns of one token at a time: the S partial sums of the four come as
-        // S independent 16-byte loads (all in flight together), added in rank order
-        const int share = TILE_N / splits;                            // splits is 1, 2, 4 or 8: 128 .. 16 columns
-        const int groups = share >> 2;                                // groups of 4 columns in the share
-        const int c4 = (threadIdx.x % groups) * 4, first_token = threadIdx.x / groups, token_step = THREADS / groups;
-        const int column = rank * share + c4;
-        const int n = n0 + column;
-        float b[4] = {0.f, 0.f, 0.f, 0.f};
-        if (bias) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (n + j < N) b[j] = bias[n + j];
-        }
-        // where key / value columns go: which pool, head and offset inside the head (a group of 4 lies in one
-        // head: head sizes and the query width are multiples of 4 here, else the scalar path below is taken)
-        const bool whole = n + 3 < N;
-        bool to_pages = false;
-        __nv_bfloat16* pool = nullptr;
-        long long head_offset = 0;
-        if (kv.k_pool && n >= kv.q_width && n < N) {
-            to_pages = true;
-            int idx = n - kv.q_width;
-            pool = kv.k_pool;
-            if (idx >= kv.kv_width) { idx -= kv.kv_width; pool = kv.v_pool; }
-            const int head = idx / kv.head_dim;
-            head_offset = (long long)head * kv.page_size * kv.head_dim + (idx - head * kv.head_dim);
-        }
-        const bool kv_vector = to_pages && whole && (kv.head_dim & 3) == 0 && (kv.q_width & 3) == 0 &&
-                               (kv.kv_width & 3) == 0 && (kv.page_stride & 3) == 0;
-        const bool out_vector = whole && (ldo & 3) == 0 && (((uintptr_t)out) & 15) == 0;
         for (int t = first_token; t < M; t += token_step) {
             float v[4] = {0.f, 0.f, 0.f, 0.f};
             const float* mine = &partial[t * TILE_N + column];
