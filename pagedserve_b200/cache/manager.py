@@ -314,17 +314,22 @@ class CacheManager:
         except CacheFull:
             for index, group, fresh, old_len in taken:
                 del group.tables[request][old_len:]
-                self._set_rows(index, slot, old_len, [-1] * len(fresh))
+                self._set_rows(index, slot, old_len, [-1] * len(fresh), device=False)
                 for page in reversed(fresh):
                     group.allocator.release(page)
             raise
         self.pending[slot] = new_tokens
 
-    def _set_rows(self, group_index: int, slot: int, first_column: int, pages) -> None:
-        """Write page ids into a slot's table row: the host array and, queued, the device's."""
+    def _set_rows(self, group_index: int, slot: int, first_column: int, pages, device: bool = True) -> None:
+        """Write page ids into a slot's table row: the host array and, queued, the device's.
+
+        ``device=False`` leaves the device's copy as it is: entries that are taken back (a request freed, an
+        extension undone) lie beyond every length a kernel is given, so nothing reads them, and a step's
+        corrections stay bounded by the pages its own tokens start."""
         if len(pages):
             self.groups[group_index].rows[slot, first_column:first_column + len(pages)] = pages
-            self.slots.set_table(group_index, slot, first_column, pages)
+            if device:
+                self.slots.set_table(group_index, slot, first_column, pages)
 
     def extend_many(self, requests: Sequence[Hashable], counts: Sequence[int]) -> None:
         """``extend`` for several requests at once (each at most once), all or nothing.
@@ -395,7 +400,7 @@ class CacheManager:
             for page in reversed(table[keep:]):
                 if page >= 0:
                     group.allocator.release(page)
-            self._set_rows(index, slot, keep, [-1] * (len(table) - keep))
+            self._set_rows(index, slot, keep, [-1] * (len(table) - keep), device=False)
             del table[keep:]
         self.pending[slot] = 0
 
@@ -432,7 +437,7 @@ class CacheManager:
                 raise CacheError("request holds a page twice")
             for page in live:
                 group.allocator.release(page)
-            self._set_rows(index, slot, 0, [-1] * len(table))
+            self._set_rows(index, slot, 0, [-1] * len(table), device=False)
         del self.slot_of[request]
         self.lengths[slot] = 0
         self._free_slots.append(slot)
@@ -467,8 +472,10 @@ class CacheManager:
         for index, group in enumerate(self.groups):
             base, width = self.slots.tables[index], self.slots.table_widths[index]
             mirrored = self.slots.mirror[base:base + group.rows.size].reshape(group.rows.shape)
-            if not np.array_equal(mirrored, group.rows):
-                raise CacheError("the slot store's block tables differ from the host's")
+            for request, table in group.tables.items():        # what a kernel may read: the live requests' entries
+                slot = self.slot_of[request]
+                if mirrored[slot, :len(table)].tolist() != table:
+                    raise CacheError(f"the slot store's block table of request {request!r} differs from the host's")
             free_rows = [slot for slot in self._free_slots]
             if free_rows and (group.rows[free_rows] != -1).any():
                 raise CacheError("a free slot still has pages in its table row")

@@ -261,11 +261,15 @@ def test_slot_store_queues_a_table_entry_only_when_a_page_boundary_is_crossed():
     cache.extend_many(["a"], [9])                               # positions 5-13: two more pages
     got = _corrections(cache)
     assert got == {base + 2: cache.groups[0].tables["a"][2], base + 3: cache.groups[0].tables["a"][3]}
-    cache.rollback("a")                                         # the step failed: the two entries are -1 again
-    assert _corrections(cache) == {base + 2: -1, base + 3: -1}
+    cache.rollback("a")                                         # the step failed: its pages go back on the host;
+    assert cache.groups[0].rows[slot, 2:4].tolist() == [-1, -1]
+    assert _corrections(cache) == {}                            # the device's stale entries lie beyond every length
+    cache.extend_many(["a"], [9])                               # the same pages come back (the free list is LIFO):
+    assert _corrections(cache) == {}                            # the device has them already
+    cache.commit("a")
     cache.free("a")
-    assert _corrections(cache) == {base: -1, base + 1: -1}
-    cache.check_invariants()                                    # the mirror equals the host's tables throughout
+    assert _corrections(cache) == {}                            # a free slot's row is read by nobody
+    cache.check_invariants()                                    # live requests' entries equal the host's throughout
 
 
 def test_slot_store_corrections_carry_the_latest_value_once():
@@ -273,11 +277,17 @@ def test_slot_store_corrections_carry_the_latest_value_once():
     store = cache.slots
     slot = cache.admit("r")
     cache.extend("r", 2)
-    cache.rollback("r")                                         # set and cleared before any step drained it:
-    assert _corrections(cache) == {store.tables[0] + slot * store.table_widths[0]: -1}     # one entry, latest value
-    cache.extend("r", 2)
+    first = cache.groups[0].tables["r"][0]
+    cache.rollback("r")                                         # taken back before any step drained it
+    other = cache.admit("s")
+    cache.extend("s", 2)                                        # the page goes to another request ...
+    assert cache.groups[0].tables["s"] == [first]
+    cache.extend("r", 2)                                        # ... and "r" gets a different one
     page = cache.groups[0].tables["r"][0]
-    assert _corrections(cache) == {store.tables[0] + slot * store.table_widths[0]: page}
+    assert page != first
+    got = _corrections(cache)                                   # each entry once, with its latest value
+    assert got == {store.tables[0] + slot * store.table_widths[0]: page,
+                   store.tables[0] + other * store.table_widths[0]: first}
     # lengths and sampling parameters: queued only where the device's copy differs
     assert store.set_lengths(np.asarray([slot]), np.asarray([0])) == 0
     assert store.set_lengths(np.asarray([slot]), np.asarray([5])) == 1
