@@ -177,9 +177,21 @@ int pick_warps(const void* A, int lda, const void* W, int ldw, const float* bias
         if (steps <= 64) PS_SKINNY(8, 6);
         PS_SKINNY(16, 6);
     } else {
-        if (steps <= 24) PS_SKINNY(4, 6);
+        // One CTA per 16 output columns. The (8, 8) instance keeps 2 CTAs on an SM (128 registers), the (8, 4)
+        // instance 3 (80 registers) at the price of a second round of loads: it wins wherever the grid is more
+        // than the 296 CTAs of one wave of the former (8 x 4,800 x 1,600: 300 CTAs, 5.2 -> 4.2 us; 8 x 6,400 x
+        // 1,600: 5.8 -> 4.7 us) and for short K (8 x 2,304 x 768: 2.02 -> 1.86 us), but not for a vocabulary's
+        // thousands of CTAs at short K (15.0 vs 15.9 us).
+        const int ctas = (N + 15) / 16;
+        if (steps <= 24) {
+            if (ctas <= 444) PS_SKINNY(8, 4);
+            PS_SKINNY(4, 6);
+        }
         if (steps <= 32) PS_SKINNY(8, 4);
-        if (steps <= 64) PS_SKINNY(8, 8);
+        if (steps <= 64) {
+            if (ctas > 296) PS_SKINNY(8, 4);
+            PS_SKINNY(8, 8);
+        }
         if (steps <= 96) PS_SKINNY(16, 6);
         PS_SKINNY(16, 8);
     }
