@@ -252,7 +252,7 @@ class StepContext:
                  max_q_len: int, max_kv_len: int, num_short_items: int = None, num_short_tokens: int = None,
                  num_long_blocks: int = 0, views: "DeviceViews" = None):
         self.layout = layout
-        self.host = host
+        self._host = host            # a HostBatch, or a function that makes it when somebody asks
         self.cache = cache
         self.status = status
         self.num_tokens = layout.num_tokens
@@ -279,6 +279,13 @@ class StepContext:
         self.step_counter = views.step_counter
         self.block_tables = cache.slots.table_views
         self.decode_only = (layout.num_tokens == layout.num_items)
+
+    @property
+    def host(self) -> HostBatch:
+        """The step as host arrays (computed on first use: only parts with host logic and tests ask)."""
+        if callable(self._host):
+            self._host = self._host()
+        return self._host
 
 
 class DeviceViews:

@@ -152,8 +152,7 @@ class ModelRunner:
         if len(set(requests)) != I:
             raise StepError("a request can appear only once in a step")       # reference: iteration.py:62-63
         counts = np.fromiter((len(entry.tokens) for entry in entries), dtype=np.int64, count=I)
-        order, num_short_items = layout_order(counts, StepContext.LONG_ENTRY)
-        tokens = np.concatenate([entries[source].tokens for source in order])
+        tokens = np.concatenate([entry.tokens for entry in entries]) if I > 1 else entries[0].tokens
         self._check_vocabulary(tokens)
 
         admitted: List[Hashable] = []
@@ -163,12 +162,12 @@ class ModelRunner:
                 if request not in slot_of:
                     cache.admit(request)
                     admitted.append(request)
-            slots = np.fromiter((slot_of[requests[source]] for source in order), dtype=np.int64, count=I)
-            starts = cache.lengths[slots].astype(np.int64)             # cached length of each laid-out item
-            beyond = np.flatnonzero(starts + counts[order] > self.max_model_len)
+            slots = np.fromiter((slot_of[request] for request in requests), dtype=np.int64, count=I)
+            starts = cache.lengths[slots].astype(np.int64)             # cached length of each entry's request
+            beyond = np.flatnonzero(starts + counts > self.max_model_len)
             if beyond.size:
                 # reference: src/model/paged_decoder.py:521-522
-                raise StepError(f"request {requests[int(order[beyond[0]])]!r} would pass the model's maximum "
+                raise StepError(f"request {requests[int(beyond[0])]!r} would pass the model's maximum "
                                 f"length {self.max_model_len}")
             cache.extend_many(requests, counts)                        # all or nothing
         except Exception:
@@ -176,25 +175,41 @@ class ModelRunner:
                 cache.free(request)
             raise
         self._admitted_in_step = admitted
-        batch = arrange_step(order, num_short_items, counts, tokens, slots, starts,
-                             [entry.want for entry in entries], pad=pad, pad_short=self.PAD_SHORT,
-                             pad_long=self.PAD_LONG, scratch_slot=cache.scratch_slot)
-        T, I, R = batch.num_tokens, batch.num_items, batch.num_rows
-        layout, views, staging, host = self._stage(T, I, R)
+        # The flat batch (short entries first, prompt portions after them, padding) is laid out natively:
+        # engine.batch.arrange_step is its specification and what ``ctx.host`` is computed with on demand.
+        wants = [entry.want for entry in entries]
+        want_counts = np.fromiter((len(want) for want in wants), dtype=np.int32, count=I)
+        flat_wants = np.fromiter((place for want in wants for place in want), dtype=np.int32,
+                                 count=int(want_counts.sum()))
+        ops, LONG = self.ops, StepContext.LONG_ENTRY
+        T, items, R, num_short_items, num_short_tokens, num_long_blocks, real_rows, max_q_len, max_kv_len = \
+            ops.step_shape(counts, starts, want_counts, LONG, pad, self.PAD_SHORT, self.PAD_LONG)
+        layout, views, staging, host = self._stage(T, items, R)
+        bad = ops.step_fill(counts, starts, want_counts, tokens, slots, flat_wants, LONG, pad, self.PAD_SHORT,
+                            self.PAD_LONG, cache.scratch_slot, self.vocab_size,
+                            self._staging_ptr[self._staging_turn], layout)
+        if bad is not None:                                # (checked above already: cannot happen)
+            self._abandon(entries)
+            raise StepError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
         # where the device's idea of a request's length differs from the host's, a correction goes up
         self.slots.set_lengths(slots, starts)
-        self._fill(layout, host, batch.item_slot, batch.q_start, batch.logit_rows, batch.token_ids, fed=0)
+        self._fill_corrections(layout, host, fed=0)
         self._upload(layout, staging)
-        self.slots.device_advanced(slots, counts[order])
-        as32 = lambda values: np.asarray(values, dtype=np.int32)
-        host_batch = HostBatch(as32(batch.token_ids), as32(batch.positions), as32(batch.token_item),
-                               as32(batch.item_slot), as32(batch.q_start), as32(batch.kv_len),
-                               as32(batch.logit_rows), [requests[source] for source in order])
-        laid_counts = np.diff(batch.q_start)
-        ctx = StepContext(layout, self._device_buffer, host_batch, cache, self._status, int(laid_counts.max()),
-                          int(batch.kv_len.max()), batch.num_short_items, batch.num_short_tokens,
-                          batch.num_long_blocks, views=views)
-        ctx.real_logit_rows = batch.real_rows
+        self.slots.device_advanced(slots, counts)
+
+        def host_batch():
+            order, short = layout_order(counts, LONG)
+            batch = arrange_step(order, short, counts, np.concatenate([entries[source].tokens for source in order]),
+                                 slots[order], starts[order], wants, pad=pad, pad_short=self.PAD_SHORT,
+                                 pad_long=self.PAD_LONG, scratch_slot=cache.scratch_slot)
+            as32 = lambda values: np.asarray(values, dtype=np.int32)
+            return HostBatch(as32(batch.token_ids), as32(batch.positions), as32(batch.token_item),
+                             as32(batch.item_slot), as32(batch.q_start), as32(batch.kv_len),
+                             as32(batch.logit_rows), [requests[source] for source in order])
+
+        ctx = StepContext(layout, self._device_buffer, host_batch, cache, self._status, max_q_len, max_kv_len,
+                          num_short_items, num_short_tokens, num_long_blocks, views=views)
+        ctx.real_logit_rows = real_rows
         return ctx
 
     def _fill(self, layout: BatchLayout, host: np.ndarray, item_slot, q_start, logit_rows, token_ids, fed: int):
@@ -206,6 +221,11 @@ class ModelRunner:
         host[layout.logit_rows:layout.logit_rows + len(logit_rows)] = logit_rows
         if token_ids is not None:
             host[layout.token_ids:layout.token_ids + layout.num_tokens] = token_ids
+        self._fill_corrections(layout, host, fed)
+
+    def _fill_corrections(self, layout: BatchLayout, host: np.ndarray, fed: int):
+        """The header and the queued corrections of the slot store into the staging buffer (if more wait than
+        the shape has room for, the whole store is copied first)."""
         if self._needs_resync or self.slots.pending > layout.update_capacity:
             self._resync()
         offsets, values = self.slots.drain()

@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 
 # library name -> sources (relative to csrc/)
 LIBRARIES: Dict[str, List[str]] = {
-    "core": ["embed_norm.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu", "host_io.cu", "step_state.cu"],
+    "core": ["embed_norm.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu", "host_io.cu", "step_state.cu", "step_build.cu"],
     "bf16": ["gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu"],
     "tc": ["gemm_tc.cu", "gemm_rows_tc.cu", "attention_prefill_tc.cu"],
 }

@@ -77,6 +77,8 @@ _SIGNATURES = {
         "ps_kv_append": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P],
         "ps_paged_attention_simt": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
+        "ps_step_shape": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
+        "ps_step_fill": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _P, _I, _I, _I, _I, _P],
         "ps_step_begin": [_P, _P, _P, _P, _P, _P],
         "ps_step_end": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P],
         "ps_host_alloc_mapped": [_L, _P, _P],
@@ -638,6 +640,33 @@ class Ops:
         """One asynchronous copy of ``nbytes`` from page-locked host memory into ``dst`` on the current
         stream (the plain runtime call: a fraction of the host time of a tensor ``copy_``)."""
         _check(self.core.ps_copy_h2d(dst.data_ptr(), src_host_ptr, nbytes, _stream()), "copy_h2d")
+
+    # ------------------------------------------------------------------ the host side of a step, natively
+    def step_shape(self, counts, starts, want_counts, long_entry, pad, pad_short, pad_long):
+        """(T, I, R, short items, short tokens, long blocks, real rows, longest entry, longest context) of the
+        flat batch that ``engine.batch.arrange_step`` would lay out; ``counts`` / ``starts`` int64 and
+        ``want_counts`` int32 per entry in the caller's order (host arrays, no device work)."""
+        shape = np.empty(9, dtype=np.int32)
+        _check(self.core.ps_step_shape(len(counts), counts.ctypes.data, starts.ctypes.data, want_counts.ctypes.data,
+                                       long_entry, 1 if pad else 0, pad_short, pad_long, shape.ctypes.data),
+               "step_shape")
+        return shape.tolist()
+
+    def step_fill(self, counts, starts, want_counts, tokens, slots, wants, long_entry, pad, pad_short, pad_long,
+                  scratch_slot, vocab_size, staging_ptr, layout):
+        """Write slots, item starts, wanted rows and token ids of the flat batch into the step's staging buffer
+        (``staging_ptr``: host address) at ``layout``'s offsets.  Returns None, or the first token id outside
+        the vocabulary."""
+        bad = ctypes.c_longlong(0)
+        status = self.core.ps_step_fill(len(counts), counts.ctypes.data, starts.ctypes.data, want_counts.ctypes.data,
+                                        tokens.ctypes.data, slots.ctypes.data, wants.ctypes.data, long_entry,
+                                        1 if pad else 0, pad_short, pad_long, scratch_slot, vocab_size, staging_ptr,
+                                        layout.item_slot, layout.q_start, layout.logit_rows, layout.token_ids,
+                                        ctypes.addressof(bad))
+        if status == 1 and (bad.value < 0 or bad.value >= vocab_size):
+            return bad.value
+        _check(status, "step_fill")
+        return None
 
     def step_begin(self, slots, layout, meta, status=None):
         """The first kernel of a step: apply the uploaded corrections to the slot store (``slots``, a

@@ -164,3 +164,52 @@ def test_step_entry_checks_and_normalises():
     for want in ([3], [-1], [0, 5]):
         with pytest.raises(ValueError, match="outside the entry"):
             StepEntry("r", [1, 2, 3], want)
+
+
+# ------------------------------------------------------------------ the native builder against its specification
+def _native():
+    """The host-only entry points of the kernel library (compiled with nvcc, loaded without a GPU)."""
+    import torch
+    from pagedserve_b200.kernels.ops import Ops
+
+    return Ops(torch.float32)
+
+
+@pytest.mark.parametrize("pad", [False, True])
+@pytest.mark.parametrize("seed", range(25))
+def test_native_step_builder_equals_arrange_step(seed, pad):
+    """``ps_step_shape`` / ``ps_step_fill`` (csrc/step_build.cu) lay a step out exactly as ``arrange_step`` does:
+    the same shape, and the same slots, item starts, wanted rows and token ids in the staging buffer."""
+    ops = _native()
+    rng = np.random.default_rng(1000 + seed)
+    entries, slots, starts = random_step(rng, int(rng.integers(1, 14)), 300)
+    if seed % 5 == 0:                                                    # only decodes / only long portions
+        keep = [i for i, entry in enumerate(entries) if (len(entry.tokens) < LONG) == (seed % 2 == 0)] or [0]
+        entries, slots, starts = [entries[i] for i in keep], slots[keep], starts[keep]
+    order, batch = arrange(entries, slots, starts, pad=pad, pad_short=16, pad_long=128)
+    counts = np.asarray([len(entry.tokens) for entry in entries], dtype=np.int64)
+    want_counts = np.asarray([len(entry.want) for entry in entries], dtype=np.int32)
+    wants = np.asarray([place for entry in entries for place in entry.want], dtype=np.int32)
+    tokens = np.concatenate([entry.tokens for entry in entries])
+    slots64, starts64 = slots.astype(np.int64), starts.astype(np.int64)
+    shape = ops.step_shape(counts, starts64, want_counts, LONG, pad, 16, 128)
+    laid = np.diff(batch.q_start)
+    assert shape == [batch.num_tokens, batch.num_items, batch.num_rows, batch.num_short_items, batch.num_short_tokens,
+                     batch.num_long_blocks, batch.real_rows, int(laid.max()), int(batch.kv_len.max())]
+    layout = BatchLayout(shape[0], shape[1], shape[2], update_capacity=5)
+    staging = np.full(layout.total, -7, dtype=np.int32)
+    assert ops.step_fill(counts, starts64, want_counts, tokens, slots64, wants, LONG, pad, 16, 128, SCRATCH, 1000,
+                         staging.ctypes.data, layout) is None
+    T, I, R = shape[:3]
+    assert staging[layout.item_slot:layout.item_slot + I].tolist() == batch.item_slot.tolist()
+    assert staging[layout.q_start:layout.q_start + I + 1].tolist() == batch.q_start.tolist()
+    assert staging[layout.logit_rows:layout.logit_rows + R].tolist() == batch.logit_rows.tolist()
+    assert staging[layout.token_ids:layout.token_ids + T].tolist() == batch.token_ids.tolist()
+    untouched = np.ones(layout.total, dtype=bool)
+    for offset, count in ((layout.item_slot, I), (layout.q_start, I + 1), (layout.logit_rows, R), (layout.token_ids, T)):
+        untouched[offset:offset + count] = False
+    assert (staging[untouched] == -7).all()                             # nothing else was written
+    # a token outside the vocabulary is reported, not written
+    tokens[len(tokens) // 2] = 1000
+    assert ops.step_fill(counts, starts64, want_counts, tokens, slots64, wants, LONG, pad, 16, 128, SCRATCH, 1000,
+                         staging.ctypes.data, layout) == 1000
