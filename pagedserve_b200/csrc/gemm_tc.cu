@@ -128,10 +128,17 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 
 template <int BN> struct Config {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 5 : 6);
+    static constexpr int STAGES = BN > 128 ? 4 : (BN >= 96 ? 5 : 6);
     // two accumulators of BN columns; an allocation is a power of two of at least 32 columns
     static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
-    static constexpr int STAGING_BYTES = 2 * BM * 128;           // two buffers of 128 rows x 128 bytes
+    // Results on their way out: buffers of 128 rows x 128 bytes, STAGING_BUFS for each of the two epilogue teams,
+    // so that a team fills one while TMA still reads the one before (256-wide tiles have no room for that)
+    static constexpr int STAGING_BUFS = BN == 256 ? 1 : 2;
+    static constexpr int STAGING_BYTES = 2 * STAGING_BUFS * BM * 128;
+    // column groups (128 bytes of output per row) that one of the two epilogue teams takes, at most: 32-column
+    // groups of float32 results (the narrower kind), every other one; and 32-column reads per group, at most
+    static constexpr int GROUPS_PER_TEAM = (BN / 32 + 1) / 2;
+    static constexpr int HALVES_MAX = 2;
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
@@ -239,6 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31
         const int team = (warp - 2) >> 2;                   // which column groups this warp takes
         uint32_t local = 0;
+        [[maybe_unused]] uint32_t chunk = 0;                // column groups this team has sent out so far
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
@@ -254,6 +262,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (page >= 0) kv_base = (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim;
                 }
             }
+            // The bias of this team's column groups, fetched while the tile is still being computed: lane j
+            // holds the values of columns j, 32 + j, ... of each group and hands them out by shuffle below (a
+            // first touch of these lines after the accumulator is complete costs about a microsecond per group).
+            [[maybe_unused]] float bias_lane[TMA_OUT ? Cfg::GROUPS_PER_TEAM * Cfg::HALVES_MAX : 1];
+            if constexpr (TMA_OUT) {
+                constexpr int COLS = 128 / (int)sizeof(TOut);
+#pragma unroll
+                for (int g = 0; g < Cfg::GROUPS_PER_TEAM * (COLS / 32); ++g) {
+                    const int n = n0 + (team + 2 * (g / (COLS / 32))) * COLS + 32 * (g % (COLS / 32)) + lane;
+                    bias_lane[g] = (bias && n < N && (team + 2 * (g / (COLS / 32))) * COLS < BN) ? bias[n] : 0.f;
+                }
+            }
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) { ok = false; if (lane == 0) atomicExch(status, 14); break; }
             tc_fence_after();
             const int m = m0 + quarter * 32 + lane;
@@ -263,11 +283,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 constexpr int COLS = 128 / (int)sizeof(TOut);
                 const int r = quarter * 32 + lane;                        // row of the tile = row of the buffer
                 const bool leader = (quarter == 2 && lane == 0);          // first warp of the team (warps 2 and 6)
-                unsigned char* stage_buf = staging + (size_t)team * (BM * 128);
                 bool released = false;
-#pragma unroll 1
-                for (int c = team * COLS; c < BN; c += 2 * COLS) {
-                    if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the buffer is free
+#pragma unroll
+                for (int group = 0; group < Cfg::GROUPS_PER_TEAM; ++group) {
+                    const int c = (team + 2 * group) * COLS;
+                    if (c >= BN) break;
+                    unsigned char* stage_buf =
+                        staging + (size_t)(team * Cfg::STAGING_BUFS + chunk % Cfg::STAGING_BUFS) * (BM * 128);
+                    ++chunk;
+                    // the buffer is free once TMA has read the group sent from it (one group per chunk)
+                    if (leader) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Cfg::STAGING_BUFS - 1) : "memory");
                     team_sync(team);
 #pragma unroll
                     for (int half = 0; half < COLS / 32; ++half) {
@@ -284,9 +309,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
                         if (bias) {
+                            const float mine = bias_lane[group * (COLS / 32) + half];
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (n + j < N) v[j] += bias[n + j];
+                            for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
                         }
                         if (act == PS_ACT_GELU_TANH) {
 #pragma unroll
@@ -427,7 +452,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     }
-    if (TMA_OUT && (warp == 2 || warp == 6) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    // shared memory must outlive TMA's reads of it; the writes themselves are complete when the grid is
+    if (TMA_OUT && (warp == 2 || warp == 6) && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -529,7 +555,12 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
         // widest tile that still gives the SMs enough tiles (measured on B200: 128 wide wins until the
         // grid falls below half the SMs; 256 wide needs two full waves)
         const int t128 = tiles_m * ((N + 127) / 128), t96 = tiles_m * ((N + 95) / 96);
-        if (tiles_m * ((N + 255) / 256) >= 2 * sm_count()) bn = 256;
+        const int t256 = tiles_m * ((N + 255) / 256);
+        if (t256 >= 2 * sm_count()) bn = 256;
+        // bfloat16 output whose 256-wide tiles are one wave while 128-wide ones would be two rounds per CTA: an
+        // MMA of 128 x N x 16 takes about 130 clocks whatever N is, so one wide tile costs half of two narrow
+        // ones (2,048 x 2,304 x 768: 12.4 -> 9.9 us inside a prefill step)
+        else if (sizeof(TOut) == 2 && t256 <= sm_count() && t128 > sm_count()) bn = 256;
         // float32 output (the products that add into the residual stream, N = the model width): 96 wide when
         // that fills more of one wave (2,048 x 768: 128 CTAs instead of 96)
         else if (sizeof(TOut) == 4 && t128 < sm_count() && t96 <= sm_count() && t96 > t128 && 2 * t128 >= sm_count())
@@ -538,6 +569,7 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
         else bn = 64;
     }
     if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+    if (bn == 192) return launch<192, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
     if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
     if constexpr (sizeof(TOut) == 4) {      // 96 columns are three 32-column groups of float32; bfloat16 groups are 64 wide
         if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
@@ -550,7 +582,7 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
 }  // namespace ps
 
 // status: device int32 that a bounded wait sets when it runs out (must not be null).
-// bn: 0 = choose, else 64, 128 or 256 (the N extent of the MMA tile).
+// bn: 0 = choose, else 64, 96 (float32 output only), 128, 192 or 256 (the N extent of the MMA tile).
 static int gemm_tc_entry(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
                          int N, int K, int out_dtype, int act, int accumulate, int* status, int bn,
                          const ps::KvScatter& kv, void* stream) {
