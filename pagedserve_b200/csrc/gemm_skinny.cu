@@ -83,6 +83,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
             prev[j] = (accumulate && e < 16 * TOK && m < M && n < N) ? to_float(out[(size_t)m * ldo + n]) : 0.f;
         }
     };
+    // the bias of this thread's output column (the same in every epilogue round: the CTA's thread count is a
+    // multiple of 16), fetched before the wait: its line was last touched a step ago and comes from DRAM
+    const float bias_mine = bias ? bias[min(n0 + (int)(threadIdx.x & 15), N - 1)] : 0.f;
     const int steps = (K + 31) >> 5;
     bool waited = false;
     for (int s0 = warp; s0 < steps; s0 += WARPS * UNROLL) {
@@ -136,7 +139,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * 16 * TOK + r * TOK + m];
-        if (bias) v += bias[n];
+        v += bias_mine;
         v = apply_act(v, act);
         if (kv.k_pool && n >= kv.q_width) {        // a key or value column: into the row's page
             int c = n - kv.q_width;
@@ -271,6 +274,7 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         wa[u] = ok ? ldg_stream(w0 + k) : make_uint4(0, 0, 0, 0);
         wb[u] = ok ? ldg_stream(w1 + k) : make_uint4(0, 0, 0, 0);
     }
+    const float bias_mine = bias ? bias[min(n0 + (int)(threadIdx.x & 15), N - 1)] : 0.f;   // as in the kernel above
     {
         const float4* g4 = reinterpret_cast<const float4*>(in.gamma);
         const float4* b4 = reinterpret_cast<const float4*>(in.beta);
@@ -426,7 +430,7 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * 16 * TOK + r * TOK + m];
-        if (bias) v += bias[n];
+        v += bias_mine;
         v = apply_act(v, act);
         if (kv.k_pool && n >= kv.q_width) {
             int c = n - kv.q_width;
