@@ -343,18 +343,44 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         // every CTA of the cluster has published (max, sum, acc) in its shared memory (idle ones: -inf, 0, 0)
         cluster_sync_all();
         if (split == first_split) {
-            float M = -INFINITY;
-            for (int r = first_split; r <= last_split; ++r) M = fmaxf(M, ld_cluster_f32(&ml_pub[0], r));
-            float L = 0.f;
-            for (int r = first_split; r <= last_split; ++r)
-                L += ld_cluster_f32(&ml_pub[1], r) * exp2f(ld_cluster_f32(&ml_pub[0], r) - M);
-            const float inv = L > 0.f ? 1.f / L : 0.f;
-            for (int d = tid; d < head_dim; d += DEC_THREADS) {
-                float o = 0.f;
-                for (int r = first_split; r <= last_split; ++r)
-                    o += ld_cluster_f32(&o_s[d], r) * exp2f(ld_cluster_f32(&ml_pub[0], r) - M);
-                out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o * inv);
+            // everything the merge needs is asked for at once (a portable cluster has at most 8 CTAs): one trip
+            // through distributed shared memory instead of one per value
+            constexpr int MAXC = 8;
+            float mr[MAXC], lr[MAXC], ov[MAXC];
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) {
+                const int r = first_split + i;
+                const bool on = r <= last_split;
+                mr[i] = on ? ld_cluster_f32(&ml_pub[0], r) : -INFINITY;
+                lr[i] = on ? ld_cluster_f32(&ml_pub[1], r) : 0.f;
+                ov[i] = (on && tid < head_dim) ? ld_cluster_f32(&o_s[tid], r) : 0.f;
             }
+            float M = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) M = fmaxf(M, mr[i]);
+            float L = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) {
+                mr[i] = (mr[i] == -INFINITY) ? 0.f : exp2f(mr[i] - M);        // now the weight of split i
+                L += lr[i] * mr[i];
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) o += ov[i] * mr[i];
+            float more = 0.f;                                         // head dim tid + 128 (head_dim <= 256)
+            if (tid + DEC_THREADS < head_dim) {
+#pragma unroll
+                for (int i = 0; i < MAXC; ++i)
+                    if (first_split + i <= last_split) more += ld_cluster_f32(&o_s[tid + DEC_THREADS], first_split + i) * mr[i];
+            }
+            // the others' shared memory has been read: they may leave while the result is written
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            if (tid < head_dim) out[(size_t)t * out_stride + h * head_dim + tid] = __float2bfloat16_rn(o * inv);
+            if (tid + DEC_THREADS < head_dim)
+                out[(size_t)t * out_stride + h * head_dim + tid + DEC_THREADS] = __float2bfloat16_rn(more * inv);
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            return;
         }
         cluster_sync_all();                                   // nobody's shared memory goes away before it was read
         return;
@@ -372,7 +398,8 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     __syncthreads();
     if (!last_flag) return;
-    __threadfence();
+    // (no fence on this side: the partial states below are read with ld.global.cg, from L2, where the other
+    // CTAs' stores were performed before their fences let their counter increments through)
     const size_t base = ((size_t)t * n_heads + h) * n_splits + first_split;
     // the partial accumulators are asked for first (they do not depend on the maxima), then the (max, sum)
     // pairs; the weight of each split is computed once and shared
