@@ -105,8 +105,13 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // q_start / kv_len (both or neither): with them the kernel knows which keys of a request are older than
 // this step (positions below kv_len - new tokens). A first chunk made of such keys only is fetched BEFORE
 // the wait for the kernel that writes this step's q, k and v, so the fetch overlaps that kernel.
-template <int KS>
-__global__ void __launch_bounds__(DEC_THREADS, KS == 4 ? 6 : (KS == 8 ? 4 : 2))
+// GROUPS > 1: the CTA is GROUPS teams of 128 threads with chunk buffers of their own; team i takes chunks
+// first + i, first + i + GROUPS, ... of the CTA's range, all teams at once, and the teams' states are merged
+// through shared memory behind one barrier. With few (token, head) pairs (at most one per SM) the whole context
+// of a pair is then one CTA (n_splits = 1) and nothing is handed over through global memory: publishing a
+// partial state, the fence, the counter and the last CTA's reads cost about 2.5 us per layer at batch 8.
+template <int KS, int GROUPS = 1>
+__global__ void __launch_bounds__(DEC_THREADS * GROUPS, GROUPS > 1 ? 1 : (KS == 4 ? 6 : (KS == 8 ? 4 : 2)))
 paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               __nv_bfloat16* __restrict__ out, int out_stride,
                               const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
@@ -127,18 +132,33 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int unit_elems = attention_unit_stride(unit, head_dim);                    // padded unit, elements
     // One stage of chunk buffers: measured on B200, a second stage (copying the next chunk during the
     // compute of this one) halves the CTAs per SM and was slower at every batch size (batch 64: 44 vs 36 us).
-    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [n_units][unit_elems]
+    constexpr int THREADS = DEC_THREADS * GROUPS;
+    const int tid_all = threadIdx.x;                                                 // thread of the CTA
+    const int grp = GROUPS > 1 ? tid_all / DEC_THREADS : 0;                          // its team
+    const int tid = GROUPS > 1 ? tid_all % DEC_THREADS : tid_all;                    // thread of the team
+    const size_t team_elems = (size_t)2 * n_units * unit_elems + chunk_keys;         // K, V, probabilities
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw) + grp * team_elems;   // [n_units][unit_elems]
     __nv_bfloat16* v_s = k_s + (size_t)n_units * unit_elems;
     __nv_bfloat16* p_s = v_s + (size_t)n_units * unit_elems;                         // [chunk_keys] probabilities
-    float* o_s = reinterpret_cast<float*>(p_s + chunk_keys);                         // [head_dim] merged output
-    __shared__ float red_a[DEC_WARPS], red_b[DEC_WARPS];
+    // [GROUPS][head_dim] accumulators; the first row becomes the CTA's merged output
+    float* o_all = reinterpret_cast<float*>(reinterpret_cast<__nv_bfloat16*>(smem_raw) + GROUPS * team_elems);
+    float* o_s = o_all;
+    __shared__ float red_a_all[GROUPS][DEC_WARPS], red_b_all[GROUPS][DEC_WARPS];
+    float* red_a = red_a_all[grp];
+    float* red_b = red_b_all[grp];
+    __shared__ float ml_team[GROUPS][2];                                             // (max, sum) of each team
     __shared__ float ml_pub[2];                                                      // (max, sum) for the cluster
-    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t bar_all[GROUPS];
+    uint64_t& bar = bar_all[grp];
     __shared__ int last_flag;
+    auto team_sync = [&]() {                                                         // the 128 threads of a team
+        if constexpr (GROUPS == 1) __syncthreads();
+        else asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory");
+    };
 
     // ---- before the wait: only what no kernel of this step writes (positions, tables, older keys)
     const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, tq = lane & 3;
     const int p = positions[t];
     const int item = token_item[t];
@@ -157,7 +177,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const bool active = split >= first_split && split <= last_split;
     const bool by_cluster = cluster > 1 && n_active > 1;
     if (!active && !by_cluster) return;                                // no keys here and nobody waits for us
-    const int chunk_lo = active ? max(first_chunk, split * split_chunks) : 1;
+    const int chunk_lo = (active ? max(first_chunk, split * split_chunks) : 1) + grp;   // this team's first chunk
     const int chunk_hi = active ? min(last_chunk, (split + 1) * split_chunks - 1) : 0;
 
     const int g = h / (n_heads / n_kv_heads);
@@ -190,14 +210,15 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     };
     // the first chunk's older units go out now, the rest of it after the wait
-    const bool early = active && (chunk_lo << chunk_log2) < first_new;
+    const bool mine = active && chunk_lo <= chunk_hi;                 // this team has a chunk at all
+    const bool early = mine && (chunk_lo << chunk_log2) < first_new;
     if (early) issue_chunk(chunk_lo, 0);
 
     pdl_prologue();
     q = pdl_fresh(q);
     k_pool = pdl_fresh(k_pool);
     v_pool = pdl_fresh(v_pool);
-    if (active) issue_chunk(chunk_lo, early ? 1 : 2);
+    if (mine) issue_chunk(chunk_lo, early ? 1 : 2);
 
     // the query as B fragments: lanes with g == 0 hold q[16 ks + 2 t .. +1] and q[16 ks + 2 t + 8 .. +9]
     const int ksteps = head_dim >> 4;                              // <= KS
@@ -229,7 +250,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     uint32_t phase = 0;
     bool ok = true;
 
-    for (int chunk = chunk_lo; chunk <= chunk_hi; ++chunk) {
+    for (int chunk = chunk_lo; chunk <= chunk_hi; chunk += GROUPS) {
         const int key0 = chunk << chunk_log2;
         const int j_lo = max(lo, key0) - key0, j_hi = min(p, key0 + chunk_keys - 1) - key0;   // valid keys of the chunk
         if (chunk != chunk_lo) issue_chunk(chunk, 2);
@@ -248,7 +269,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 for (int c = 0; c < (head_dim >> 3); ++c) { vz[c] = make_uint4(0, 0, 0, 0); kz[c] = make_uint4(0, 0, 0, 0); }
             }
         }
-        __syncthreads();
+        team_sync();
         // ---- scores: key tiles warp, warp + 4, ... ; lanes with t == 0 end up with keys g and g + 8
         float sc[2][2];                                           // [tile of this warp][row g / g+8]
         float wmax = -INFINITY;
@@ -277,7 +298,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
         wmax = warp_max(wmax);
         if (lane == 0) red_a[warp] = wmax;
-        __syncthreads();
+        team_sync();
         const float cmax = fmaxf(fmaxf(red_a[0], red_a[1]), fmaxf(red_a[2], red_a[3]));
         const float m_new = fmaxf(m_run, cmax);
         float wsum = 0.f;
@@ -294,7 +315,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
         wsum = warp_sum(wsum);
         if (lane == 0) red_b[warp] = wsum;
-        __syncthreads();
+        team_sync();
         const float csum = (red_b[0] + red_b[1]) + (red_b[2] + red_b[3]);
         const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
         l_run = l_run * corr + csum;
@@ -320,22 +341,44 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();                                      // the buffers may be overwritten now
+        team_sync();                                      // the buffers may be overwritten now
     }
     // column 0 of the accumulators is the output: lanes with t == 0 hold head dims 16 dt + g and + 8
 #pragma unroll
     for (int i = 0; i < OT; ++i) {
         const int dt = warp + DEC_WARPS * i;
         if (dt < ksteps && tq == 0) {
-            o_s[16 * dt + gq] = o_acc[i][0];
-            o_s[16 * dt + gq + 8] = o_acc[i][2];
+            o_all[grp * head_dim + 16 * dt + gq] = o_acc[i][0];
+            o_all[grp * head_dim + 16 * dt + gq + 8] = o_acc[i][2];
         }
     }
-    if (tid == 0) { ml_pub[0] = m_run; ml_pub[1] = l_run; }
+    if constexpr (GROUPS > 1) {
+        // the teams' states become the CTA's: weights from the maxima, then the weighted sums (team order)
+        if (tid == 0) { ml_team[grp][0] = m_run; ml_team[grp][1] = l_run; }
+        __syncthreads();
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < GROUPS; ++i) M = fmaxf(M, ml_team[i][0]);
+        float w[GROUPS], L = 0.f;
+#pragma unroll
+        for (int i = 0; i < GROUPS; ++i) {
+            w[i] = (ml_team[i][0] == -INFINITY) ? 0.f : exp2f(ml_team[i][0] - M);
+            L += ml_team[i][1] * w[i];
+        }
+        for (int d = tid_all; d < head_dim; d += THREADS) {
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < GROUPS; ++i) o += o_all[i * head_dim + d] * w[i];
+            o_all[d] = o;                                  // thread d alone reads and writes column d
+        }
+        m_run = M;
+        l_run = L;
+    }
+    if (tid_all == 0) { ml_pub[0] = m_run; ml_pub[1] = l_run; }
     __syncthreads();
     if (n_splits == 1 || n_active == 1) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        for (int d = tid; d < head_dim; d += DEC_THREADS)
+        for (int d = tid_all; d < head_dim; d += THREADS)
             out[(size_t)t * out_stride + h * head_dim + d] = __float2bfloat16_rn(o_s[d] * inv);
         return;
     }
@@ -353,7 +396,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 const bool on = r <= last_split;
                 mr[i] = on ? ld_cluster_f32(&ml_pub[0], r) : -INFINITY;
                 lr[i] = on ? ld_cluster_f32(&ml_pub[1], r) : 0.f;
-                ov[i] = (on && tid < head_dim) ? ld_cluster_f32(&o_s[tid], r) : 0.f;
+                ov[i] = (on && tid_all < head_dim) ? ld_cluster_f32(&o_s[tid_all], r) : 0.f;
             }
             float M = -INFINITY;
 #pragma unroll
@@ -368,17 +411,17 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             float o = 0.f;
 #pragma unroll
             for (int i = 0; i < MAXC; ++i) o += ov[i] * mr[i];
-            float more = 0.f;                                         // head dim tid + 128 (head_dim <= 256)
-            if (tid + DEC_THREADS < head_dim) {
+            float more = 0.f;                                         // head dim tid_all + 128 (head_dim <= 256)
+            if (tid_all + THREADS < head_dim) {
 #pragma unroll
                 for (int i = 0; i < MAXC; ++i)
-                    if (first_split + i <= last_split) more += ld_cluster_f32(&o_s[tid + DEC_THREADS], first_split + i) * mr[i];
+                    if (first_split + i <= last_split) more += ld_cluster_f32(&o_s[tid_all + THREADS], first_split + i) * mr[i];
             }
             // the others' shared memory has been read: they may leave while the result is written
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-            if (tid < head_dim) out[(size_t)t * out_stride + h * head_dim + tid] = __float2bfloat16_rn(o * inv);
-            if (tid + DEC_THREADS < head_dim)
-                out[(size_t)t * out_stride + h * head_dim + tid + DEC_THREADS] = __float2bfloat16_rn(more * inv);
+            if (tid_all < head_dim) out[(size_t)t * out_stride + h * head_dim + tid_all] = __float2bfloat16_rn(o * inv);
+            if (tid_all + THREADS < head_dim)
+                out[(size_t)t * out_stride + h * head_dim + tid_all + THREADS] = __float2bfloat16_rn(more * inv);
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
             return;
         }
@@ -387,11 +430,11 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     // several splits hold keys of this token: publish the partial state
     const size_t slot = ((size_t)t * n_heads + h) * n_splits + split;
-    for (int d = tid; d < head_dim; d += DEC_THREADS) part_acc[slot * head_dim + d] = o_s[d];
-    if (tid == 0) { part_ml[slot * 2] = m_run; part_ml[slot * 2 + 1] = l_run; }
+    for (int d = tid_all; d < head_dim; d += THREADS) part_acc[slot * head_dim + d] = o_s[d];
+    if (tid_all == 0) { part_ml[slot * 2] = m_run; part_ml[slot * 2 + 1] = l_run; }
     __threadfence();
     __syncthreads();
-    if (tid == 0) {
+    if (tid_all == 0) {
         int prev = atomicAdd(&counters[t * n_heads + h], 1);
         last_flag = (prev == n_active - 1);
         if (last_flag) counters[t * n_heads + h] = 0;
@@ -404,7 +447,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // the partial accumulators are asked for first (they do not depend on the maxima), then the (max, sum)
     // pairs; the weight of each split is computed once and shared
     constexpr int HOLD = 8;                                   // splits whose values a thread keeps in flight
-    const int d0 = tid;                                       // head dims d0, d0 + 128, ... belong to this thread
+    const int d0 = tid_all;                                       // head dims d0, d0 + 128, ... belong to this thread
     float held[HOLD];
     if (d0 < head_dim) {
 #pragma unroll
@@ -432,7 +475,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             L += lh[i] * mh[i];
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
-        for (int d = d0, round = 0; d < head_dim; d += DEC_THREADS, ++round) {
+        for (int d = d0, round = 0; d < head_dim; d += THREADS, ++round) {
             float o = 0.f;
 #pragma unroll
             for (int i = 0; i < HOLD; ++i) {
@@ -443,13 +486,13 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
         return;
     }
-    float* w_s = reinterpret_cast<float*>(k_s);               // the K buffer is free now: [n_active] weights
+    float* w_s = reinterpret_cast<float*>(smem_raw);          // the chunk buffers are free now: [n_active] weights
     float* ml_s = w_s + n_active;                             // then [n_active][2]
     const bool staged = 3 * n_active * 4 <= 2 * chunk_keys * head_dim;      // always, unless a huge split count
     if (staged) {
-        for (int i = tid; i < 2 * n_active; i += DEC_THREADS) ml_s[i] = ldcg_f32(part_ml + base * 2 + i);
+        for (int i = tid_all; i < 2 * n_active; i += THREADS) ml_s[i] = ldcg_f32(part_ml + base * 2 + i);
         __syncthreads();
-        if (warp == 0) {
+        if (tid_all < 32) {
             float M = -INFINITY;
             for (int i = lane; i < n_active; i += 32) M = fmaxf(M, ml_s[2 * i]);
             M = warp_max(M);
@@ -464,7 +507,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
         __syncthreads();
         const float inv = red_a[0];
-        for (int d = d0, round = 0; d < head_dim; d += DEC_THREADS, ++round) {
+        for (int d = d0, round = 0; d < head_dim; d += THREADS, ++round) {
             float o = 0.f;
             if (round == 0) {
 #pragma unroll
@@ -484,7 +527,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int i = 0; i < n_active; ++i)
         L += ldcg_f32(part_ml + (base + i) * 2 + 1) * exp2f(ldcg_f32(part_ml + (base + i) * 2) - M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int d = tid; d < head_dim; d += DEC_THREADS) {
+    for (int d = tid_all; d < head_dim; d += THREADS) {
         float o = 0.f;
         for (int i = 0; i < n_active; ++i)
             o += ldcg_f32(part_acc + (base + i) * head_dim + d) * exp2f(ldcg_f32(part_ml + (base + i) * 2) - M);
@@ -523,12 +566,43 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
         return PS_ERR_UNSUPPORTED;
     const int chunk_keys = ps::attention_chunk_keys(head_dim, page_size);
     if ((split_tiles * 32) % chunk_keys != 0) return PS_ERR_BAD_ARGUMENT;
-    const int split_chunks = split_tiles * 32 / chunk_keys;
-    dim3 grid(T, n_heads, n_splits);
+    int split_chunks = split_tiles * 32 / chunk_keys;
     const int unit = page_size < (chunk_keys >> 3) ? page_size : (chunk_keys >> 3);
-    size_t smem = (size_t)(chunk_keys / unit) * ps::attention_unit_stride(unit, head_dim) * 2 * 2 +
-                  (size_t)chunk_keys * 2 + (size_t)head_dim * 4;
+    const size_t team_bytes = (size_t)(chunk_keys / unit) * ps::attention_unit_stride(unit, head_dim) * 2 * 2 +
+                              (size_t)chunk_keys * 2;
+    // Few (token, head) pairs, at most one per SM: the whole context of a pair is one CTA of TEAMS teams that
+    // work on TEAMS chunks at once and merge through shared memory, instead of n_splits CTAs that merge
+    // through global memory. (Head sizes up to 64 only: the teams of one CTA share an SM's registers.)
+    constexpr int TEAMS = 6;
+    static int sm_count = 0;
+    if (!sm_count) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
+            sm_count = 1;
+    }
+    const bool teams = head_dim <= 64 && cluster <= 1 && n_splits > 1 && (long long)T * n_heads <= sm_count &&
+                       (long long)n_splits * split_chunks <= (1 << 20);
+    int groups = 1;
+    if (teams) {
+        groups = TEAMS;
+        split_chunks *= n_splits;
+        n_splits = 1;
+    }
+    dim3 grid(T, n_heads, n_splits);
+    size_t smem = (size_t)groups * (team_bytes + (size_t)head_dim * 4);
     cudaStream_t s = (cudaStream_t)stream;
+    if (teams) {
+        auto kernel = ps::paged_attention_decode_kernel<4, TEAMS>;
+        static size_t raised[ps::MAX_DEVICES] = {0};
+        if (!ps::ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
+        return ps::launch_pdl_cluster(kernel, grid, dim3(ps::DEC_THREADS * TEAMS), smem, s, 1,
+                                      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+                                      (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride,
+                                      token_item, positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim,
+                                      page_size, window, scale * 1.4426950408889634f, chunk_keys, split_chunks,
+                                      n_splits, part_acc, part_ml, counters, status, q_start, kv_len, 1, token_row);
+    }
 #define PS_DECODE_LAUNCH(KS)                                                                                          \
     {                                                                                                                \
         auto kernel = ps::paged_attention_decode_kernel<KS>;                                                         \

@@ -60,10 +60,12 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
     if long_items and head_dim > 128:
         short_tokens, long_items = ctx.num_tokens, 0
     if short_tokens:
-        # few (token, head) pairs: one thread-block cluster per pair merges its splits through shared memory
-        # (batch 1: 231 vs 250 us per step); from a few dozen pairs on, co-scheduling whole clusters costs
-        # more than the trip through global memory that it saves (batch 8: 354 vs 317 us)
-        merge = "cluster" if short_tokens * n_heads * 8 <= 148 else "global"
+        # The splits of a (token, head) pair merge through global memory. (With at most one pair per SM the
+        # kernel makes one CTA of six teams per pair instead and merges in shared memory: batch 8, 278 -> 259 us
+        # per step. One thread-block cluster per pair, which the kernel also offers, lost to both: co-scheduling
+        # whole clusters costs more than the trip through memory it saves, 354 vs 317 us at batch 8 when measured,
+        # and 4,636 vs 4,734 tokens/s at batch 1 against the teams.)
+        merge = "global"
         ops.paged_attention_decode(q[:short_tokens], out[:short_tokens], layer.k_pool, layer.v_pool,
                                    layer.page_stride, ctx.token_item[:short_tokens], ctx.positions[:short_tokens],
                                    layer.block_table, n_heads, n_kv_heads, head_dim, layer.page_size, window, scale,

@@ -614,6 +614,53 @@ def test_attention_decode_with_older_keys_fetched_early(heads, kv_heads, head_di
     assert rel_err(out, case.reference(window)[rows]) < 8e-3
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(12, 12, 64, 16), (4, 4, 16, 16), (6, 2, 48, 8),
+                                                          (12, 4, 64, 64)])
+@pytest.mark.parametrize("window", [None, 70, 700])
+def test_attention_decode_few_pairs_one_cta_of_teams_each(heads, kv_heads, head_dim, page, window):
+    """At most one (token, head) pair per SM and head sizes up to 64: the kernel runs one CTA of six teams per
+    pair, each team on a chunk of its own, merged in shared memory. Contexts of one chunk, of exactly six, of
+    seven (a second round for one team) and of twelve; windows that leave the first teams without keys; the
+    newest keys written right before the launch, the older ones fetched before the wait."""
+    ops = ops_for(torch.bfloat16)
+    lengths = [1, 127, 128, 129, 640, 768, 769, 1024, 1500]
+    fresh = [1, 1, 2, 1, 1, 1, 3, 1, 1]
+    assert sum(fresh) * heads <= 148
+    case = PagedCase(ops, torch.bfloat16, lengths, heads, kv_heads, head_dim, page, seed=23 + head_dim)
+    rows, item_of, q_start = [], [], [0]
+    start = 0
+    for item, (length, new) in enumerate(zip(lengths, fresh)):
+        rows += list(range(start + length - new, start + length))
+        item_of += [item] * new
+        q_start.append(q_start[-1] + new)
+        start += length
+    rows_dev = torch.tensor(rows, device=DEV)
+    q = case.q.to(DEV)[rows_dev].contiguous()
+    token_item = torch.tensor(item_of, dtype=torch.int32, device=DEV)
+    positions = case.positions[rows_dev].contiguous()
+    k_new, v_new = case.k.to(DEV)[rows_dev].contiguous(), case.v.to(DEV)[rows_dev].contiguous()
+    poison = torch.full_like(k_new, float("nan"))
+    reference = case.reference(window)[rows]
+    results = []
+    for target_ctas in (10 ** 7, 1):                       # a chunk per split (teams), one split (one team's walk)
+        ops.kv_append(poison, poison, token_item, positions, case.table, case.k_pool, case.v_pool, case.page_stride,
+                      kv_heads, head_dim, page)
+        torch.cuda.synchronize()
+        out = torch.full((len(rows), heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.kv_append(k_new, v_new, token_item, positions, case.table, case.k_pool, case.v_pool, case.page_stride,
+                      kv_heads, head_dim, page)
+        ops.paged_attention_decode(q, out, case.k_pool, case.v_pool, case.page_stride, token_item, positions,
+                                   case.table, heads, kv_heads, head_dim, page, window, head_dim ** -0.5,
+                                   max(lengths), target_ctas=target_ctas,
+                                   q_start=torch.tensor(q_start, dtype=torch.int32, device=DEV),
+                                   kv_len=torch.tensor(lengths, dtype=torch.int32, device=DEV))
+        assert torch.isfinite(out.float()).all()
+        assert rel_err(out, reference) < 8e-3
+        results.append(out.float())
+    # the two ways of cutting the keys agree far more closely with each other than with float64
+    assert rel_err(results[0], results[1].double()) < 4e-3
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 4, 16, 16), (2, 2, 48, 8), (12, 12, 64, 16),
                                                           (8, 2, 128, 32), (3, 1, 96, 64), (2, 2, 80, 4)])
 @pytest.mark.parametrize("window", [None, 70])
