@@ -69,7 +69,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
         if (threadIdx.x == 0) {
             float s = 0.f;
             for (int w = 0; w < NT / 32; ++w) s += red[w];
-            bcast = s / (float)H;
+            bcast = s * (1.0f / (float)H);
         }
         __syncthreads();
         mean = bcast;
@@ -95,7 +95,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     if (threadIdx.x == 0) {
         float s = 0.f;
         for (int w = 0; w < NT / 32; ++w) s += red[w];
-        bcast = rsqrtf(s / (float)H + eps);
+        bcast = rsqrtf(s * (1.0f / (float)H) + eps);
     }
     __syncthreads();
     float rstd = bcast;
@@ -129,6 +129,7 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     // the norm's scale and shift are weights: they are fetched before the wait on the kernel that writes x
     const int lane = threadIdx.x & 31;
     const int quads = H >> 2;
+    const float inv_h = 1.0f / (float)H;          // the division, before the wait
     const float4* g4 = reinterpret_cast<const float4*>(gamma);
     const float4* b4 = reinterpret_cast<const float4*>(beta);
     float4 g[WMAX], b[WMAX];
@@ -151,7 +152,7 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
         v[i] = c < quads ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
         sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
-    const float mean = has_mean ? warp_sum(sum) / (float)H : 0.f;
+    const float mean = has_mean ? warp_sum(sum) * inv_h : 0.f;
     float sq = 0.f;
 #pragma unroll
     for (int i = 0; i < WMAX; ++i) {
@@ -160,7 +161,7 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
             sq += (a * a + b2 * b2) + (c * c + d * d);
         }
     }
-    const float rstd = rsqrtf(warp_sum(sq) / (float)H + eps);
+    const float rstd = rsqrtf(warp_sum(sq) * inv_h + eps);
     TOut* o = out + (size_t)r * H;
 #pragma unroll
     for (int i = 0; i < WMAX; ++i) {

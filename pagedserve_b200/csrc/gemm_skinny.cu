@@ -30,6 +30,35 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
+// Where output column n of a packed q|k|v product goes inside a page: the pool and the offset of (head, 0, d)
+// from the row's place in the page; pool null for a query column (or no cache write at all). Integer
+// divisions, done once per thread before the wait: a thread's column is the same in every epilogue round.
+struct KvColumn {
+    int which;      // 0: not a cache column, 1: keys, 2: values
+    int offset;     // elements from the row's place in the page (a page of one layer is far below 2^31 elements)
+};
+__device__ __forceinline__ KvColumn kv_column(const KvScatter& kv, int n, int N) {
+    KvColumn col{0, 0};
+    if (kv.k_pool && n >= kv.q_width && n < N) {
+        int c = n - kv.q_width;
+        col.which = 1;
+        if (c >= kv.kv_width) { c -= kv.kv_width; col.which = 2; }
+        const int head = c / kv.head_dim, d = c - head * kv.head_dim;
+        col.offset = head * kv.page_size * kv.head_dim + d;
+    }
+    return col;
+}
+// position -> (page index, place in the page); pages are almost always a power of two long
+__device__ __forceinline__ void split_position(int p, int page_size, int* index, int* within) {
+    if ((page_size & (page_size - 1)) == 0) {
+        *index = p >> (31 - __clz(page_size));
+        *within = p & (page_size - 1);
+    } else {
+        *index = p / page_size;
+        *within = p - *index * page_size;
+    }
+}
+
 // MT: token tiles of 8. WARPS: warps per CTA. UNROLL: k steps whose loads a warp issues together (a round);
 // WARPS * UNROLL * 32 >= K makes it one round, so that the latency of the weights is paid once.
 template <int MT, int WARPS, int UNROLL, typename TOut>
@@ -69,9 +98,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         if (kv.k_pool) {
             // where a row's keys and values go: offset of (page, head 0, position in page, 0), or -1
             for (int m = threadIdx.x; m < M; m += WARPS * 32) {
-                const int p = kv.positions[m];
-                const int page = kv.block_table[(size_t)kv.token_row[m] * kv.bt_stride + p / kv.page_size];
-                dst_s[m] = page >= 0 ? (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim : -1;
+                int index, within;
+                split_position(kv.positions[m], kv.page_size, &index, &within);
+                const int page = kv.block_table[(size_t)kv.token_row[m] * kv.bt_stride + index];
+                dst_s[m] = page >= 0 ? (long long)page * kv.page_stride + (long long)within * kv.head_dim : -1;
             }
         }
 #pragma unroll
@@ -142,12 +172,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         v += bias_mine;
         v = apply_act(v, act);
         if (kv.k_pool && n >= kv.q_width) {        // a key or value column: into the row's page
-            int c = n - kv.q_width;
-            __nv_bfloat16* pool = kv.k_pool;
-            if (c >= kv.kv_width) { c -= kv.kv_width; pool = kv.v_pool; }
-            int head = c / kv.head_dim, d = c - head * kv.head_dim;
+            const KvColumn col = kv_column(kv, n, N);
             const long long base = dst_s[m];
-            if (base >= 0) pool[base + (long long)head * kv.page_size * kv.head_dim + d] = __float2bfloat16_rn(v);
+            if (base >= 0) (col.which == 1 ? kv.k_pool : kv.v_pool)[base + col.offset] = __float2bfloat16_rn(v);
             continue;
         }
         v += prev[j];
@@ -275,23 +302,36 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         wb[u] = ok ? ldg_stream(w1 + k) : make_uint4(0, 0, 0, 0);
     }
     const float bias_mine = bias ? bias[min(n0 + (int)(threadIdx.x & 15), N - 1)] : 0.f;   // as in the kernel above
-    {
-        const float4* g4 = reinterpret_cast<const float4*>(in.gamma);
-        const float4* b4 = reinterpret_cast<const float4*>(in.beta);
-        for (int c = threadIdx.x; c < quads; c += WARPS * 32) {
-            reinterpret_cast<float4*>(gamma_s)[c] = g4[c];
-            reinterpret_cast<float4*>(beta_s)[c] = in.beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    const float inv_k = 1.0f / (float)K;       // divisions and the like happen here, off the critical path
+    const KvColumn kv_col = kv_column(kv, n0 + (int)(threadIdx.x & 15), N);
+    // Nothing before the wait waits for memory itself: when the kernel in front has already ended, every
+    // microsecond here is on the step's critical path. Scale and shift go to shared memory by asynchronous
+    // copies that are waited for where the norm needs them; a row's position and block-table row are asked for
+    // here and used after the wait. (Positions and tables are written by the step's first kernel, never by the
+    // kernel directly in front of this one: only that one may still be running before the wait.)
+    for (int c = threadIdx.x; c < quads; c += WARPS * 32) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(gamma_s + 4 * c)),
+                     "l"(in.gamma + 4 * c) : "memory");
+        if (in.beta)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(beta_s + 4 * c)),
+                         "l"(in.beta + 4 * c) : "memory");
+        else
+            reinterpret_cast<float4*>(beta_s)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const bool kv_row = kv.k_pool && threadIdx.x < M;
+    int kv_p = 0, kv_table_row = 0;
+    if (kv_row) {
+        kv_p = kv.positions[threadIdx.x];
+        kv_table_row = kv.token_row[threadIdx.x];
     }
     pdl_prologue();            // the rows come from the kernel before this one
-    if (kv.k_pool && threadIdx.x < M) {
-        // where this row's keys and values go: offset of (page, head 0, position in page, 0), or -1
-        const int m = threadIdx.x;
-        const int p = kv.positions[m];
-        const int page = kv.block_table[(size_t)kv.token_row[m] * kv.bt_stride + p / kv.page_size];
-        dst_s[m] = page >= 0 ? (long long)page * kv.page_stride + (long long)(p % kv.page_size) * kv.head_dim : -1;
+    int kv_page = -1, kv_index = 0, kv_within = 0;
+    if (kv_row) {
+        split_position(kv_p, kv.page_size, &kv_index, &kv_within);
+        kv_page = kv.block_table[(size_t)kv_table_row * kv.bt_stride + kv_index];
     }
-    __syncthreads();
+    bool staged = false;       // scale and shift have arrived and every thread can see them
     // norm: one warp per row, two rows at a time so that their loads and reductions overlap; a row sits in
     // registers (float4 pieces, all loads issued at once) when K <= 1024, else its tail is read again from L1.
     // Statistics in two passes in float32, as the separate norm kernel does.
@@ -326,8 +366,8 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         }
         sum_a = warp_sum(sum_a);
         sum_b = warp_sum(sum_b);
-        const float mean_a = in.has_mean ? sum_a / (float)K : 0.f;
-        const float mean_b = in.has_mean ? sum_b / (float)K : 0.f;
+        const float mean_a = in.has_mean ? sum_a * inv_k : 0.f;
+        const float mean_b = in.has_mean ? sum_b * inv_k : 0.f;
         float sq_a = 0.f, sq_b = 0.f;
 #pragma unroll
         for (int i = 0; i < HOLD; ++i) {
@@ -348,8 +388,13 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         }
         sq_a = warp_sum(sq_a);
         sq_b = warp_sum(sq_b);
-        const float rstd_a = rsqrtf(sq_a / (float)K + in.eps);
-        const float rstd_b = rsqrtf(sq_b / (float)K + in.eps);
+        const float rstd_a = rsqrtf(sq_a * inv_k + in.eps);
+        const float rstd_b = rsqrtf(sq_b * inv_k + in.eps);
+        if (!staged) {         // every warp passes one such barrier: here, or below if it has no row
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            staged = true;
+        }
         auto put = [&](int m, int c, const float4& y, float mean, float rstd) {
             const float4 gm = reinterpret_cast<const float4*>(gamma_s)[c];
             const float4 bt = reinterpret_cast<const float4*>(beta_s)[c];
@@ -371,6 +416,13 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
             if (two) put(m1, c, xb[c], mean_b, rstd_b);
         }
     }
+    if (!staged) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+    }
+    // where this row's keys and values go: offset of (page, head 0, position in page, 0), or -1
+    if (kv_row)
+        dst_s[threadIdx.x] = kv_page >= 0 ? (long long)kv_page * kv.page_stride + (long long)kv_within * kv.head_dim : -1;
     __syncthreads();
 
     const __nv_bfloat16* arow[MT];
@@ -432,13 +484,9 @@ gemm_skinny_fused_kernel(NormInput in, const __nv_bfloat16* __restrict__ W, int 
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * 16 * TOK + r * TOK + m];
         v += bias_mine;
         v = apply_act(v, act);
-        if (kv.k_pool && n >= kv.q_width) {
-            int c = n - kv.q_width;
-            __nv_bfloat16* pool = kv.k_pool;
-            if (c >= kv.kv_width) { c -= kv.kv_width; pool = kv.v_pool; }
-            int head = c / kv.head_dim, d = c - head * kv.head_dim;
+        if (kv_col.which) {
             const long long base = dst_s[m];
-            if (base >= 0) pool[base + (long long)head * kv.page_size * kv.head_dim + d] = __float2bfloat16_rn(v);
+            if (base >= 0) (kv_col.which == 1 ? kv.k_pool : kv.v_pool)[base + kv_col.offset] = __float2bfloat16_rn(v);
             continue;
         }
         size_t o = (size_t)m * ldo + n;

@@ -62,10 +62,12 @@ def bench_gemm(args):
     if args.norm:
         from types import SimpleNamespace
 
+        from pagedserve_b200.parts.base import NormPrologue
         from pagedserve_b200.parts.norms import DeferredNorm
 
-        norm = SimpleNamespace(weight=torch.ones(K, device="cuda"), bias=torch.zeros(K, device="cuda"),
-                               params={"eps": 1e-5, "has_mean": True})
+        prologue = NormPrologue(weight=torch.ones(K, device="cuda"), bias=torch.zeros(K, device="cuda"),
+                                eps=1e-5, has_mean=True)
+        norm = SimpleNamespace(fused_prologue=lambda: prologue)
         x32 = [t.float() for t in a]
 
     def run(i):
