@@ -57,11 +57,23 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
     };
     int i = begin + threadIdx.x;
-    for (; i + 3 * NT < end; i += 4 * NT) {            // four loads in flight
-        const float v0 = row[i], v1 = row[i + NT], v2 = row[i + 2 * NT], v3 = row[i + 3 * NT];
-        take(v0, i); take(v1, i + NT); take(v2, i + 2 * NT); take(v3, i + 3 * NT);
+    constexpr int FLIGHT = 8;                          // loads in flight: a share of a wide row in three trips
+    for (; i + (FLIGHT - 1) * NT < end; i += FLIGHT * NT) {
+        float v[FLIGHT];
+#pragma unroll
+        for (int j = 0; j < FLIGHT; ++j) v[j] = row[i + j * NT];
+#pragma unroll
+        for (int j = 0; j < FLIGHT; ++j) take(v[j], i + j * NT);
     }
-    for (; i < end; i += NT) take(row[i], i);
+    {
+        // the rest, again all at once
+        float v[FLIGHT];
+#pragma unroll
+        for (int j = 0; j < FLIGHT; ++j) v[j] = (i + j * NT < end) ? row[i + j * NT] : 0.f;
+#pragma unroll
+        for (int j = 0; j < FLIGHT; ++j)
+            if (i + j * NT < end) take(v[j], i + j * NT);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, bv, o);
