@@ -109,7 +109,13 @@ class Model:
         """Run the tokens of ``ctx`` from the cache; return float32 logits ``[R, V]``."""
         hidden = self.embedding.forward(ctx, self.positions)
         cache = ctx.cache
+        # what a layer asks of the step arena is dead when the layer is done (the residual stream came first):
+        # every layer starts from the same place in it
+        arena = getattr(self.env.ops, "arena", None)
+        mark = arena.mark() if arena is not None else None
         for entry in self.spec.schedule:
+            if arena is not None:
+                arena.release(mark)
             layer = LayerContext(entry.layer, entry.cache_layer, self.positions)
             group_index = cache.group_of_layer.get(entry.cache_layer)
             if group_index is not None:
@@ -122,6 +128,8 @@ class Model:
                 layer.block_table = ctx.block_tables[group_index]
             layer.state = cache.state.get(entry.cache_layer)
             self.blocks[entry.layer].forward(hidden, ctx, layer)
+        if arena is not None:
+            arena.release(mark)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=hidden.device)
         if hasattr(self.final_norm, "defer"):

@@ -78,7 +78,7 @@ class CausalSelfAttention(Mixer):
         tokens = x.shape[0]
         from pagedserve_b200.parts.base import PositionEncoding
 
-        qkv = torch.empty((tokens, self.q_width + 2 * self.kv_width), dtype=self.env.dtype, device=x.device)
+        qkv = ops.empty((tokens, self.q_width + 2 * self.kv_width), self.env.dtype, x.device)
         write_cache = p.get("write_cache", True)
         # keys may go from the projection straight into the pages unless the position encoding
         # still has to transform them
@@ -90,7 +90,7 @@ class CausalSelfAttention(Mixer):
         v = qkv[:, self.q_width + self.kv_width:]
         if not no_rotation:
             layer.positions.rotate(q, k, ctx)
-        context = torch.empty((tokens, self.q_width), dtype=self.env.dtype, device=x.device)
+        context = ops.empty((tokens, self.q_width), self.env.dtype, x.device)
         ops.attention(q, k, v, context, ctx, layer, p["n_heads"], p["n_kv_heads"], p["head_dim"],
                       p.get("window"), float(p["scale"]), write_cache=write_cache and not written)
         ops.linear(context, self.w_out, self.b_out, residual, accumulate=True)

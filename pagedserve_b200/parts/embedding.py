@@ -26,8 +26,7 @@ class TokenEmbedding(Embedding):
         self.table = tensors[self._n(self.params["name"] + ".weight")]
 
     def forward(self, ctx, positions):
-        hidden = torch.empty((ctx.num_tokens, self.params["hidden_size"]), dtype=torch.float32,
-                             device=self.table.device)
+        hidden = self.env.ops.empty((ctx.num_tokens, self.params["hidden_size"]), torch.float32, self.table.device)
         position_table = positions.embedding_table()
         self.env.ops.embed(ctx.token_ids, ctx.positions, self.table, position_table, hidden, ctx.status)
         if position_table is None:
@@ -58,7 +57,7 @@ class LMHead(Head):
 
     def forward(self, x_rows, embedding):
         table = embedding.table if self.table is None else self.table
-        logits = torch.empty((x_rows.shape[0], table.shape[0]), dtype=torch.float32, device=x_rows.device)
+        logits = self.env.ops.empty((x_rows.shape[0], table.shape[0]), torch.float32, x_rows.device)
         if x_rows.shape[0] == 0:
             return logits
         return self.env.ops.linear(x_rows, table, None, logits)

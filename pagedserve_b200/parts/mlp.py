@@ -52,6 +52,6 @@ class DenseMLP(FeedForward):
     def forward(self, x, residual, ctx):
         p = self.params
         ops = self.env.ops
-        inner = torch.empty((x.shape[0], p["inner_size"]), dtype=self.env.dtype, device=x.device)
+        inner = ops.empty((x.shape[0], p["inner_size"]), self.env.dtype, x.device)
         ops.linear(x, self.w_up, self.b_up, inner, act=p["activation"])
         ops.linear(inner, self.w_down, self.b_down, residual, accumulate=True)

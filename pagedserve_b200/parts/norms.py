@@ -58,6 +58,6 @@ class LayerNorm(Norm):
     def forward(self, x, out=None, rows=None, out_dtype=None):
         n_rows = rows.numel() if rows is not None else x.shape[0]
         if out is None:
-            out = torch.empty((n_rows, x.shape[1]), dtype=out_dtype or self.env.dtype, device=x.device)
+            out = self.env.ops.empty((n_rows, x.shape[1]), out_dtype or self.env.dtype, x.device)
         return self.env.ops.layernorm(x, self.weight, self.bias, float(self.params["eps"]), out, rows=rows,
                                       has_mean=self.params.get("has_mean", True))
