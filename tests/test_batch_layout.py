@@ -213,3 +213,38 @@ def test_native_step_builder_equals_arrange_step(seed, pad):
     tokens[len(tokens) // 2] = 1000
     assert ops.step_fill(counts, starts64, want_counts, tokens, slots64, wants, LONG, pad, 16, 128, SCRATCH, 1000,
                          staging.ctypes.data, layout) == 1000
+
+
+def test_step_arena_hands_out_aligned_views_and_reuses_them():
+    """The arena that a step's activations come from: views of a few chunks, 256-byte aligned, the same places
+    again after ``reset`` and after ``release(mark)``, a new chunk when one is full, nothing shared between two
+    tensors that are alive at the same time."""
+    import torch
+
+    from pagedserve_b200.kernels.ops import StepArena
+
+    arena = StepArena()
+    arena.CHUNK_BYTES = 4096                      # small chunks so that the test crosses their edges
+    cpu = torch.device("cpu")
+    a = arena.empty((3, 5), torch.float32, cpu)
+    b = arena.empty((7,), torch.bfloat16, cpu)
+    assert a.shape == (3, 5) and a.dtype == torch.float32 and b.shape == (7,) and b.dtype == torch.bfloat16
+    assert a.data_ptr() % 256 == 0 and b.data_ptr() % 256 == 0
+    assert b.data_ptr() >= a.data_ptr() + a.numel() * 4
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert float(a.sum()) == 15.0                 # filling b did not touch a
+    mark = arena.mark()
+    c = arena.empty((900,), torch.float32, cpu)   # 3,600 bytes: does not fit behind a and b, goes to a new chunk
+    d = arena.empty((10,), torch.int32, cpu)
+    assert len(arena.chunks) == 2 and float(a.sum()) == 15.0
+    arena.release(mark)
+    c2 = arena.empty((900,), torch.float32, cpu)
+    d2 = arena.empty((10,), torch.int32, cpu)
+    assert c2.data_ptr() == c.data_ptr() and d2.data_ptr() == d.data_ptr() and len(arena.chunks) == 2
+    big = arena.empty((5000,), torch.float32, cpu)          # larger than a chunk: a chunk of its own
+    assert big.numel() == 5000 and len(arena.chunks) == 3
+    arena.reset()
+    again = arena.empty((3, 5), torch.float32, cpu)
+    assert again.data_ptr() == a.data_ptr() and len(arena.chunks) == 3
+    assert arena.empty((0, 8), torch.float32, cpu).numel() == 0
