@@ -4,12 +4,14 @@ reference: main.py:136-254 (``build_scheduler``) and :257-342 (``main``).  Optio
 keep the reference's names and meanings where it has them (``--model``,
 ``--strategy``, ``--prefill-chunk-size``, ``--max-batch-size``,
 ``--kv-cache-memory-mb``, ``--kv-cache-memory-utilization``, ``--kv-cache-safety-mb``,
-``--dtype``, ``--disable-cuda-graphs``).  ``--model`` is a
+``--dtype``, ``--decode-attention-backend``, ``--kv-cache-dtype``, ``--disable-cuda-graphs``).  ``--model`` is a
 folder with ``config.json`` and ``model.safetensors``, or the name of a size
 (``tiny-a``, ``tiny-b``, ``gpt2-124m``, ``gpt2-345m``, ``gpt2-1.5b``) to be filled with
-seeded random weights.  Dropped: the decode-attention backend switch and the INT8
-cache (one backend, no quantisation).  Prompts are
-token ids: there is no tokenizer in the engine.
+seeded random weights.  ``--decode-attention-backend`` names the implementation of
+single-token attention as in the reference (main.py:305-310); this engine has one, its
+own paged kernels (``cuda``), and says so when it is asked for ``torch`` or ``triton``.
+``--kv-cache-dtype`` is ``model`` (main.py:311-316); ``int8`` is refused: quantised
+caches are not built.  Prompts are token ids: there is no tokenizer in the engine.
 """
 
 from __future__ import annotations
@@ -26,6 +28,11 @@ from pagedserve_b200.config.engine_config import (
     SUPPORTED_DTYPES,
     SUPPORTED_SCHEDULING_STRATEGIES,
 )
+
+# reference: main.py:27-28. "cuda" is this engine's only implementation; the reference's two names are accepted
+# and answered with a note, so that its command lines keep working.
+SUPPORTED_DECODE_ATTENTION_BACKENDS = ("cuda", "torch", "triton")
+SUPPORTED_KV_CACHE_DTYPES = ("model", "int8")
 
 
 def build_engine(model: str, seed: int = 0, **engine_options):
@@ -46,8 +53,20 @@ def build_scheduler(model: str = "tiny-a", scheduling_strategy: str = ORCA_STRAT
                     kv_cache_safety_mb: int = DEFAULT_KV_SAFETY_MB,
                     execution_dtype: str = "float32", enable_cuda_graphs: bool = True, block_size: int = 16,
                     num_blocks: Optional[int] = None, max_num_batched_tokens: int = 2048, seed: int = 0,
-                    eos_token_id: Optional[int] = None):
+                    eos_token_id: Optional[int] = None, decode_attention_backend: str = "cuda",
+                    kv_cache_dtype: str = "model"):
     """reference: ``build_scheduler`` (main.py:136-254); returns a ready ``Scheduler``."""
+    if decode_attention_backend not in SUPPORTED_DECODE_ATTENTION_BACKENDS:      # reference: main.py:152-157
+        raise ValueError(f"Unknown decode attention backend '{decode_attention_backend}'. "
+                         f"Choose one of: {', '.join(SUPPORTED_DECODE_ATTENTION_BACKENDS)}")
+    if decode_attention_backend != "cuda":
+        print(f"note: decode attention backend '{decode_attention_backend}' is the reference's; this engine runs "
+              "its own paged CUDA kernels for every step", file=sys.stderr)
+    if kv_cache_dtype not in SUPPORTED_KV_CACHE_DTYPES:                          # reference: main.py:165-167
+        raise ValueError(f"Unknown KV cache dtype '{kv_cache_dtype}'. "
+                         f"Choose one of: {', '.join(SUPPORTED_KV_CACHE_DTYPES)}")
+    if kv_cache_dtype != "model":
+        raise ValueError("KV cache dtype 'int8' is not built: the cache is kept in the execution dtype")
     if max_batch_size is None:
         max_batch_size = 32                                  # reference: main.py:181-182 (CUDA default)
     if max_batch_size <= 0:
@@ -82,6 +101,10 @@ def main(argv=None) -> int:
     parser.add_argument("--num-blocks", type=int, help="explicit number of KV pages")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per KV page")
     parser.add_argument("--dtype", choices=SUPPORTED_DTYPES, default="float32", help="execution dtype")
+    parser.add_argument("--decode-attention-backend", choices=SUPPORTED_DECODE_ATTENTION_BACKENDS, default="cuda",
+                        help="single-token decode attention implementation (this engine has one: cuda)")
+    parser.add_argument("--kv-cache-dtype", choices=SUPPORTED_KV_CACHE_DTYPES, default="model",
+                        help="KV storage dtype; int8 is not built and is refused")
     parser.add_argument("--disable-cuda-graphs", action="store_true",
                         help="disable steady-state decode CUDA-graph replay")
     parser.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
@@ -96,7 +119,8 @@ def main(argv=None) -> int:
         args.model, scheduling_strategy=args.strategy, prefill_chunk_size=args.prefill_chunk_size,
         max_batch_size=args.max_batch_size, kv_cache_memory_mb=args.kv_cache_memory_mb,
         kv_cache_memory_utilization=args.kv_cache_memory_utilization, kv_cache_safety_mb=args.kv_cache_safety_mb,
-        execution_dtype=args.dtype, enable_cuda_graphs=not args.disable_cuda_graphs,
+        execution_dtype=args.dtype, decode_attention_backend=args.decode_attention_backend,
+        kv_cache_dtype=args.kv_cache_dtype, enable_cuda_graphs=not args.disable_cuda_graphs,
         block_size=args.block_size, num_blocks=args.num_blocks,
         max_num_batched_tokens=args.max_num_batched_tokens, seed=args.seed)
     prompts = [_parse_ids(text) for text in (args.prompt_ids or [])]

@@ -38,6 +38,7 @@ def test_defaults_follow_the_reference(monkeypatch, capsys):
     assert options["max_batch_size"] is None and options["kv_cache_memory_mb"] is None
     assert options["kv_cache_memory_utilization"] == 0.90 and options["kv_cache_safety_mb"] == 3072
     assert options["execution_dtype"] == "float32" and options["enable_cuda_graphs"] is True
+    assert options["decode_attention_backend"] == "cuda" and options["kv_cache_dtype"] == "model"
     assert [request[1] for request in seen["scheduler"].requests] == [8, 8]
     assert capsys.readouterr().out.count("request ") == 2
 
@@ -49,19 +50,22 @@ def test_options_reach_the_scheduler(monkeypatch, tmp_path):
         "--model", "gpt2-124m", "--strategy", "sarathi", "--prefill-chunk-size", "128", "--max-batch-size", "64",
         "--max-num-batched-tokens", "512", "--kv-cache-memory-mb", "2048", "--kv-cache-memory-utilization", "0.5",
         "--kv-cache-safety-mb", "100", "--block-size", "8", "--dtype", "bfloat16", "--disable-cuda-graphs",
+        "--decode-attention-backend", "triton", "--kv-cache-dtype", "model",
         "--temperature", "0.8", "--seed", "5", "--max-new-tokens", "3", "--prompt-ids", "7 8 9",
         "--prompt-file", str(prompts)])
     options = seen["options"]
     assert seen["model"] == "gpt2-124m"
     assert options == dict(scheduling_strategy="sarathi", prefill_chunk_size=128, max_batch_size=64,
                            kv_cache_memory_mb=2048, kv_cache_memory_utilization=0.5, kv_cache_safety_mb=100,
-                           execution_dtype="bfloat16", enable_cuda_graphs=False, block_size=8, num_blocks=None,
+                           execution_dtype="bfloat16", decode_attention_backend="triton", kv_cache_dtype="model",
+                           enable_cuda_graphs=False, block_size=8, num_blocks=None,
                            max_num_batched_tokens=512, seed=5)
     assert seen["scheduler"].requests == [([7, 8, 9], 3, 0.8, 5), ([1, 2, 3], 3, 0.8, 6), ([4, 5], 3, 0.8, 7)]
 
 
 def test_unknown_choices_are_refused(monkeypatch):
-    for argv in (["--strategy", "fifo"], ["--dtype", "float16"]):
+    for argv in (["--strategy", "fifo"], ["--dtype", "float16"], ["--decode-attention-backend", "flash"],
+                 ["--kv-cache-dtype", "fp8"]):
         with pytest.raises(SystemExit):
             run_cli(monkeypatch, argv)
 
@@ -71,3 +75,10 @@ def test_build_scheduler_checks_its_arguments():
         cli.build_scheduler("tiny-a", max_batch_size=0)
     with pytest.raises(ValueError, match="model folder or one of"):
         cli.build_engine("no-such-model")
+    # reference: main.py:152-157 and :165-167 (same messages); the int8 cache is not built
+    with pytest.raises(ValueError, match="Unknown decode attention backend 'flash'"):
+        cli.build_scheduler("tiny-a", decode_attention_backend="flash")
+    with pytest.raises(ValueError, match="Unknown KV cache dtype 'fp8'"):
+        cli.build_scheduler("tiny-a", kv_cache_dtype="fp8")
+    with pytest.raises(ValueError, match="'int8' is not built"):
+        cli.build_scheduler("tiny-a", kv_cache_dtype="int8")
