@@ -211,7 +211,8 @@ class Scheduler:
                 # every request brings one decoded token: forward and sampling run as one device step
                 # the same batch comes back next step unless a request reaches its limit now (an end-of-
                 # sequence token cannot be foreseen: then what was staged ahead is simply dropped)
-                comes_back = not self.waiting and all(
+                # (waiting requests cannot join while every sequence slot is taken)
+                comes_back = (not self.waiting or len(sampling) >= self.max_num_seqs) and all(
                     len(request.generated_token_ids) + 1 < request.max_new_tokens for request in sampling)
                 tokens = fused_decode(
                     [request.request_id for request in sampling],

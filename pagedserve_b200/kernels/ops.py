@@ -186,9 +186,10 @@ class StepArena:
         while True:
             if self.chunk < len(self.chunks):
                 chunk = self.chunks[self.chunk]
-                if chunk.device == torch.device(device) and self.offset + size <= chunk.numel():
-                    piece = chunk[self.offset:self.offset + nbytes]
-                    self.offset += size
+                start = self.offset + (-(chunk.data_ptr() + self.offset)) % self.ALIGN     # an aligned address
+                if chunk.device == torch.device(device) and start + size <= chunk.numel():
+                    piece = chunk[start:start + nbytes]
+                    self.offset = start + size
                     return piece.view(dtype).view(tuple(shape))
                 self.chunk += 1
                 self.offset = 0
@@ -197,7 +198,7 @@ class StepArena:
                 # a capture runs the step that an eager run made room for just before; if it asks for more
                 # all the same, the graph's own pool serves it
                 return torch.empty(tuple(shape), dtype=dtype, device=device)
-            self.chunks.append(torch.empty(max(self.CHUNK_BYTES, size), dtype=torch.uint8, device=device))
+            self.chunks.append(torch.empty(max(self.CHUNK_BYTES, size) + self.ALIGN, dtype=torch.uint8, device=device))
 
 
 class Ops:

@@ -267,3 +267,52 @@ def test_steps_equal_the_reference_schedulers(name):
         assert mine == theirs, f"pages of step {number} differ"
     assert [finished_after[index] for index in range(len(record["requests"]))] == record["finished_after_step"]
     assert sched.reserved_blocks == 0 and engine.cache.free_pages() == record["total_blocks"]
+
+
+class FusedDecodeEngine(FakeEngine):
+    """A fake engine with the fused decode entry: checks the scheduler's hint that the same batch comes back
+    against the scheduler's own state at the time of the call."""
+
+    def __init__(self, **options):
+        super().__init__(**options)
+        self.hints = []
+        self.scheduler = None
+
+    def decode_tokens(self, requests, tokens, temperatures, seeds, steps, stage_next):
+        sched = self.scheduler
+        states = [sched.active[r] for r in requests]
+        nobody_finishes = all(len(s.generated_token_ids) + 1 < s.max_new_tokens for s in states)
+        nobody_can_join = not sched.waiting or len(requests) >= sched.max_num_seqs
+        assert bool(stage_next) == (nobody_finishes and nobody_can_join)
+        self.hints.append(bool(stage_next))
+        for request in requests:
+            self.cache.extend(request, 1)
+            self.cache.commit(request)
+        return np.array([[self.cache.length(r) % self.vocab_size for r in requests]])
+
+
+@pytest.mark.parametrize("strategy", ["orca", "sarathi"])
+def test_decode_steps_are_announced_as_coming_back_only_when_nothing_can_change_the_batch(strategy):
+    """The hint that lets the engine launch the next decode step behind the running one: true when no request
+    reaches its limit in this step and no waiting request can join (none waits, or every sequence slot is
+    taken). Checked inside the fake engine at every decode-only step of two workloads."""
+    engine = FusedDecodeEngine(pages=64, page=4, slots=8)
+    sched = Scheduler(engine, max_num_seqs=2, strategy=strategy, prefill_chunk_size=8, max_num_batched_tokens=64)
+    engine.scheduler = sched
+    ids = [sched.add_token_request([1, 2, 3], max_new_tokens=5), sched.add_token_request([4, 5], max_new_tokens=7),
+           sched.add_token_request([6], max_new_tokens=4)]          # the third waits: both slots are taken
+    sched.run_until_complete()
+    assert sorted(sched.finished) == ids
+    assert True in engine.hints and False in engine.hints
+    waited_with_full_slots = engine.hints.count(True)
+    # a free slot and a waiting request that does not fit yet: the batch may change, no hint while it waits
+    engine = FusedDecodeEngine(pages=8, page=4, slots=8)
+    sched = Scheduler(engine, max_num_seqs=4, strategy=strategy, prefill_chunk_size=8, max_num_batched_tokens=64)
+    engine.scheduler = sched
+    small = sched.add_token_request([1, 2, 3], max_new_tokens=5)         # reserves 2 of the 8 pages
+    big = sched.add_token_request(list(range(20)), max_new_tokens=9)     # needs 8 pages: waits until small is done
+    while small not in sched.finished:
+        sched.step()
+    assert engine.hints and not any(engine.hints)
+    sched.run_until_complete()
+    assert sorted(sched.finished) == [small, big] and waited_with_full_slots > 0
