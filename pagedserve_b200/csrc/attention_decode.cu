@@ -581,8 +581,10 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
             sm_count = 1;
     }
+    // (a pair's chunks are walked in rounds of TEAMS: beyond two rounds, i.e. contexts of more than 12 chunks, the
+    // split form's parallelism over more SMs is worth its merge again)
     const bool teams = head_dim <= 64 && cluster <= 1 && n_splits > 1 && (long long)T * n_heads <= sm_count &&
-                       (long long)n_splits * split_chunks <= (1 << 20);
+                       (long long)n_splits * split_chunks <= 2 * TEAMS;
     int groups = 1;
     if (teams) {
         groups = TEAMS;
