@@ -442,7 +442,8 @@ def main():
         prompt_len = min(1024, context_len)
         count = tokens_total // prompt_len
         times = []
-        rehearsals = 3                     # the step shape is captured as a CUDA graph once it has come back
+        # the step shape is captured as a CUDA graph once it has come back a few times
+        rehearsals = max(3, getattr(engine.runner, "MIXED_SHAPE_SIGHTINGS", 2) + 1)
         for repeat in range(repeats + rehearsals):
             prompts = [rng.integers(0, config.vocab_size, prompt_len).tolist() for _ in range(count)]
             entries = [StepEntry(1000 + i, prompts[i], [prompt_len - 1]) for i in range(count)]
