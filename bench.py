@@ -470,8 +470,8 @@ def main():
     def measure_serving(requests, max_seqs=64):
         """Continuous batching: every request is queued at time 0; a step holds the decode tokens of the running
         requests and prompt portions of waiting ones under the token budget.  The last of three passes is
-        reported: the earlier ones meet most step shapes for the first time (a first sighting is a graph
-        capture of about 5 ms)."""
+        reported: the earlier ones meet most step shapes for the first few times (a shape that keeps coming
+        back is captured as a CUDA graph, a step of about 5 ms)."""
         import gc
 
         for _ in range(3):
