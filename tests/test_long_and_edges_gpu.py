@@ -213,3 +213,32 @@ def test_benchmark_sizes_match_plain():
                                      f"gpt2-124m/batch 8/request {i}")
         del engine
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_returned_logits_outlive_the_next_steps(dtype, graphs):
+    """A step's intermediate tensors and its logits lie in the step arena, which the next step writes over; what
+    ``Engine.step`` returns is a copy and must still hold the step's values after other steps have run (prompt
+    steps of other sizes, decode steps, a replayed graph)."""
+    from pagedserve_b200.engine.batch import StepEntry
+    from test_generation_gpu import make_engine
+
+    vocab = helpers.TINY["c"][0]["vocab_size"]
+    engine = make_engine("c", dtype, num_blocks=96, enable_cuda_graphs=graphs)
+    first_tokens = helpers.random_tokens(vocab, 70, seed=5)
+    first = engine.step([StepEntry("a", first_tokens, [0, 33, 69])])
+    kept = first.clone()
+    later = [engine.step([StepEntry("b", helpers.random_tokens(vocab, 120, seed=6), [119])]),
+             engine.step([StepEntry("a", [3], [0]), StepEntry("b", [4], [0])]),
+             engine.step([StepEntry("a", [5], [0]), StepEntry("b", [6], [0])]),
+             engine.step([StepEntry("c", helpers.random_tokens(vocab, 40, seed=7), list(range(40)))])]
+    assert bool((first == kept).all())
+    # and the later results are not views of one another either
+    snapshots = [tensor.clone() for tensor in later]
+    engine.step([StepEntry("a", [7], [0]), StepEntry("b", [8], [0]), StepEntry("c", [9], [0])])
+    for tensor, snapshot in zip(later, snapshots):
+        assert bool((tensor == snapshot).all())
+    for name in "abc":
+        engine.finish(name)
+    assert engine.cache.free_pages() == engine.cache.total_pages()
