@@ -131,7 +131,7 @@ def test_gemm_skinny(M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(65, 64, 64), (128, 256, 64), (130, 1003, 96), (300, 320, 328),
                                    (1024, 2304, 768), (257, 770, 3072), (2048, 96, 1600)])
-@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("bn", [0, 64, 128, 192, 256])
 def test_gemm_tcgen05(M, N, K, bn):
     """The tcgen05/TMA/TMEM product against the CUDA-core product on the same bfloat16 inputs (both
     accumulate in float32) and against float64: tails in M, N and K, every tile width, all epilogues."""
