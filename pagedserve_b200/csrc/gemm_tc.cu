@@ -561,6 +561,16 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
         // MMA of 128 x N x 16 takes about 130 clocks whatever N is, so one wide tile costs half of two narrow
         // ones (2,048 x 2,304 x 768: 12.4 -> 9.9 us inside a prefill step)
         else if (sizeof(TOut) == 2 && t256 <= sm_count() && t128 > sm_count()) bn = 256;
+        // bfloat16 output of a deep product (K of 1,024 and more, where the main loop outweighs what a CTA does
+        // once): rounds of tiles per CTA times what a tile of each width costs beside one of 128 (measured alone:
+        // 1,024 x 4,800 x 1,600 takes 30.1 / 26.7 / 28.4 us at 128 / 192 / 256 columns, 2,048 x 3,072 x 1,024
+        // 23.0 / 21.4 / 23.0, 2,048 x 4,096 x 1,024 28.9 / 28.4 / 23.9)
+        else if (sizeof(TOut) == 2 && K >= 1024 && t128 > sm_count()) {
+            const int t192 = tiles_m * ((N + 191) / 192);
+            auto rounds = [&](int tiles) { return (tiles + sm_count() - 1) / sm_count(); };
+            const int c128 = rounds(t128) * 100, c192 = rounds(t192) * 130, c256 = rounds(t256) * 145;
+            bn = (c128 <= c192 && c128 <= c256) ? 128 : (c192 <= c256 ? 192 : 256);
+        }
         // float32 output (the products that add into the residual stream, N = the model width): 96 wide when
         // that fills more of one wave (2,048 x 768: 128 CTAs instead of 96)
         else if (sizeof(TOut) == 4 && t128 < sm_count() && t96 <= sm_count() && t96 > t128 && 2 * t128 >= sm_count())
